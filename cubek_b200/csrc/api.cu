@@ -1,0 +1,642 @@
+// C ABI: argument validation (every `panic!` / `assert!` site of the reference becomes a
+// status code), launch geometry and dispatch.  Host-side counterpart of
+// `quantize::launch_ref` / `quantize_packed` / `quantize_native`
+// (crates/cubek-quant/src/quantize.rs:174-326), `dequantize::launch_ref` and helpers
+// (crates/cubek-quant/src/dequantize.rs:171-332) and `scales_layout`
+// (crates/cubek-quant/src/layout/scales.rs:220-258).
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <dlfcn.h>
+
+#include "dequantize_kernels.cuh"
+#include "misc_kernels.cuh"
+#include "quantize_kernels.cuh"
+
+namespace qk {
+
+cudaError_t launch_quantize_f32(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_f16(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_bf16(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f32(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f16(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
+
+cudaError_t launch_quantize(int fdt, int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg,
+                            cudaStream_t stream)
+{
+    switch (fdt) {
+    case QK_F32: return launch_quantize_f32(kind, dyn, args, cfg, stream);
+    case QK_F16: return launch_quantize_f16(kind, dyn, args, cfg, stream);
+    case QK_BF16: return launch_quantize_bf16(kind, dyn, args, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
+                                const LaunchCfg &cfg, cudaStream_t stream)
+{
+    switch (fdt) {
+    case QK_F32: return launch_block_scales_f32(in, scale_out, nchunks, lg, range, cfg, stream);
+    case QK_F16: return launch_block_scales_f16(in, scale_out, nchunks, lg, range, cfg, stream);
+    case QK_BF16: return launch_block_scales_bf16(in, scale_out, nchunks, lg, range, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+int unit_elems(int fdt, int kind)
+{
+    const int per16 = (fdt == QK_F32) ? 4 : 8;
+    return cmax(per16, kind_elems_per_u32(kind));
+}
+
+// ---- process-wide knobs (measurement only) and counters ------------------------------------
+enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_COUNT = 4 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {8}, {0}, {0}};
+static std::atomic<uint64_t> g_launches{0};
+static std::atomic<int> g_sm_count[64];
+
+static int sm_count_of_current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = g_sm_count[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
+static LaunchCfg current_cfg()
+{
+    LaunchCfg c;
+    c.threads = g_tune[TUNE_THREADS].load();
+    c.ctas_per_sm = g_tune[TUNE_CTAS_PER_SM].load();
+    c.force_exact = g_tune[TUNE_FORCE_EXACT].load();
+    c.sm_count = sm_count_of_current_device();
+    return c;
+}
+
+static inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? QK_OK : QK_ERR_CUDA + (int)e; }
+static inline void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// ---- scheme helpers ----------------------------------------------------------------------------
+static int dtype_size(int dt) { return dt == QK_F32 ? 4 : (dt == QK_F16 || dt == QK_BF16) ? 2 : 0; }
+
+static int value_bits(int value)
+{
+    switch (value) {
+    case QK_Q8F: case QK_Q8S: case QK_E4M3: case QK_E5M2: return 8;
+    case QK_Q4F: case QK_Q4S: case QK_E2M1: return 4;
+    case QK_Q2F: case QK_Q2S: return 2;
+    default: return 0;
+    }
+}
+
+static int num_quants(const QkScheme *s)
+{
+    const int bits = value_bits(s->value);
+    if (bits == 0) return 0;
+    if (s->store == QK_STORE_U32) return 32 / bits;
+    if (s->store == QK_STORE_NATIVE) return s->value == QK_E2M1 ? 2 : 1;
+    return 0;
+}
+
+static int kind_of(const QkScheme *s)
+{
+    if (s->store == QK_STORE_U32) {
+        const int bits = value_bits(s->value);
+        return bits == 8 ? KIND_PACK8 : bits == 4 ? KIND_PACK4 : KIND_PACK2;
+    }
+    switch (s->value) {
+    case QK_Q8F: case QK_Q8S: return KIND_I8;
+    case QK_E2M1: return KIND_E2M1;
+    case QK_E4M3: return KIND_E4M3;
+    case QK_E5M2: return KIND_E5M2;
+    default: return -1;
+    }
+}
+
+// The checks `launch_ref` performs by pattern matching (quantize.rs:185-220).
+static int check_scheme(const QkScheme *s)
+{
+    if (value_bits(s->value) == 0) return QK_ERR_UNSUPPORTED_SCHEME;
+    if (s->store != QK_STORE_U32 && s->store != QK_STORE_NATIVE) return QK_ERR_UNSUPPORTED_SCHEME;
+    if (s->mode != QK_MODE_SYMMETRIC) return QK_ERR_UNSUPPORTED_SCHEME;
+    if (dtype_size(s->param) == 0) return QK_ERR_UNSUPPORTED_SCHEME;
+    if (s->level != QK_LEVEL_TENSOR && s->level != QK_LEVEL_BLOCK) return QK_ERR_UNSUPPORTED_SCHEME;
+    if (s->store == QK_STORE_NATIVE && kind_of(s) < 0) return QK_ERR_UNSUPPORTED_SCHEME;  // Q4*/Q2* native
+    if (s->level == QK_LEVEL_BLOCK) {
+        if (s->block_rank < 1 || s->block_rank > 8) return QK_ERR_BLOCK_SIZE;
+        for (int i = 0; i < s->block_rank; ++i)
+            if (s->block[i] == 0) return QK_ERR_BLOCK_SIZE;
+    }
+    return QK_OK;
+}
+
+static long long numel(const QkTensor *t)
+{
+    long long n = 1;
+    for (int d = 0; d < t->rank; ++d) n *= t->shape[d];
+    return n;
+}
+
+static bool is_contiguous(const QkTensor *t)
+{
+    long long expect = 1;
+    for (int d = t->rank - 1; d >= 0; --d) {
+        if (t->shape[d] != 1 && t->strides[d] != expect) return false;
+        expect *= t->shape[d];
+    }
+    return true;
+}
+
+static int check_tensor(const QkTensor *t, int elem_size)
+{
+    if (!t || !t->shape || !t->strides) return QK_ERR_NULL;
+    if (t->rank < 1 || t->rank > QK_MAX_RANK) return QK_ERR_SHAPE;
+    for (int d = 0; d < t->rank; ++d)
+        if (t->shape[d] < 0) return QK_ERR_SHAPE;
+    if (t->elem_size != elem_size) return QK_ERR_DTYPE;
+    if (numel(t) > 0) {
+        if (!t->ptr) return QK_ERR_NULL;
+        if (reinterpret_cast<uintptr_t>(t->ptr) % (uintptr_t)elem_size) return QK_ERR_ALIGN;
+    }
+    return QK_OK;
+}
+
+// Everything the launchers need to know about one call, derived from the handles the way
+// `scales_layout` / `shape_divmod_quant` do (layout/scales.rs:220-258).
+struct Geometry {
+    int rank = 0, nq = 0, kind = 0;
+    long long n = 0;                 // unpacked elements
+    long long block[QK_MAX_RANK];    // left-padded with 1
+    long long shape[QK_MAX_RANK];    // unpacked shape
+    bool per_tensor = true;
+    bool last_dim_blocks = false;    // blocks only along the last dim, rows split evenly
+    long long B = 0;                 // block extent along the last dim
+    long long nscales = 1;
+};
+
+// `values` is the quantized tensor; `unpacked` the float one.  Shapes must agree as
+// unpacked = packed with the last dim multiplied by num_quants.
+static int build_geometry(Geometry &g, const QkScheme *s, const QkTensor *unpacked, const QkTensor *values)
+{
+    g.nq = num_quants(s);
+    g.kind = kind_of(s);
+    g.rank = unpacked->rank;
+    if (values && values->rank != unpacked->rank) return QK_ERR_SHAPE;
+    for (int d = 0; d < g.rank; ++d) {
+        g.shape[d] = unpacked->shape[d];
+        g.block[d] = 1;
+        if (values) {
+            const long long want = (d == g.rank - 1) ? values->shape[d] * g.nq : values->shape[d];
+            if (want != unpacked->shape[d]) return QK_ERR_SHAPE;
+        }
+    }
+    if (unpacked->shape[g.rank - 1] % g.nq != 0) return QK_ERR_SHAPE;
+    g.n = numel(unpacked);
+    g.per_tensor = (s->level == QK_LEVEL_TENSOR);
+    g.nscales = 1;
+    if (!g.per_tensor) {
+        if (s->block_rank > g.rank) return QK_ERR_BLOCK_SIZE;
+        for (int i = 0; i < s->block_rank; ++i) g.block[g.rank - s->block_rank + i] = s->block[i];
+        g.B = g.block[g.rank - 1];
+        g.last_dim_blocks = (g.shape[g.rank - 1] % g.B == 0);
+        for (int d = 0; d < g.rank - 1; ++d) g.last_dim_blocks = g.last_dim_blocks && g.block[d] == 1;
+        for (int d = 0; d < g.rank; ++d) g.nscales *= (g.shape[d] + g.block[d] - 1) / g.block[d];
+    }
+    return QK_OK;
+}
+
+// A scales tensor must hold one element per tensor, or one per block with the rank of the values.
+static int check_scales_shape(const Geometry &g, const QkTensor *sc)
+{
+    if (g.per_tensor) return numel(sc) == 1 ? QK_OK : QK_ERR_SHAPE;
+    if (sc->rank != g.rank) return QK_ERR_SHAPE;
+    for (int d = 0; d < g.rank; ++d)
+        if (sc->shape[d] != (g.shape[d] + g.block[d] - 1) / g.block[d]) return QK_ERR_SHAPE;
+    return QK_OK;
+}
+
+static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *scales, const QkTensor *out_scales)
+{
+    L.rank = g.rank;
+    L.per_tensor = g.per_tensor ? 1 : 0;
+    for (int d = 0; d < QK_MAX_RANK; ++d) {
+        L.shape[d] = d < g.rank ? g.shape[d] : 1;
+        L.block[d] = d < g.rank ? g.block[d] : 1;
+        L.scale_strides[d] = (!g.per_tensor && scales && d < g.rank) ? scales->strides[d] : 0;
+        L.out_scale_strides[d] = (!g.per_tensor && out_scales && d < g.rank) ? out_scales->strides[d] : 0;
+    }
+}
+
+static int log2_exact(long long v)
+{
+    if (v <= 0 || (v & (v - 1))) return -1;
+    int lg = 0;
+    while ((1ll << lg) < v) ++lg;
+    return lg;
+}
+
+static bool aligned(const void *p, unsigned a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// The streaming kernels need whole units, power-of-two blocks made of whole units along the
+// last dim, contiguous scales and vector-aligned bases.  Returns log2(units per block), -1 for
+// per tensor, or -2 when the call has to take the layout-general kernels.
+static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, const QkTensor *out,
+                            const QkTensor *scale, const QkTensor *out_scale)
+{
+    if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
+    const int U = unit_elems(fdt, g.kind);
+    if (g.n % U != 0) return -2;
+    if (!aligned(in->ptr, 16)) return -2;
+    const int out_words = U / kind_elems_per_u32(g.kind);
+    if (!aligned(out->ptr, 4 * out_words)) return -2;
+    if (g.per_tensor) return -1;
+    if (!g.last_dim_blocks) return -2;
+    if (g.B % U != 0) return -2;
+    const int lg = log2_exact(g.B / U);
+    if (lg < 0 || lg > 5) return -2;
+    if (scale && !is_contiguous(scale)) return -2;
+    if (out_scale && !is_contiguous(out_scale)) return -2;
+    return lg;
+}
+
+static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values, const QkTensor *out,
+                              const QkTensor *params)
+{
+    if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
+    const int E = dequant_unit_elems(fdt, g.kind);
+    if (g.n % E != 0) return -2;
+    const int in_words = E / kind_elems_per_u32(g.kind);
+    if (!aligned(values->ptr, 4 * in_words)) return -2;
+    if (!aligned(out->ptr, 16)) return -2;
+    if (g.per_tensor) return -1;
+    if (!g.last_dim_blocks) return -2;
+    if (g.B % E != 0) return -2;
+    const int lg = log2_exact(g.B / E);
+    if (lg < 0) return -2;
+    if (!is_contiguous(params)) return -2;
+    return lg;
+}
+
+static int quantize_common(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
+                           const QkTensor *out_scale, const float *absmax, bool dynamic, void *gen_scales,
+                           const QkScheme *scheme, int input_dtype, cudaStream_t stream);
+
+}  // namespace qk
+
+using namespace qk;
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+int qk_num_quants(const QkScheme *scheme) { return scheme ? num_quants(scheme) : 0; }
+
+int qk_value_range(int value, float *lo, float *hi)
+{
+    float l, h;
+    switch (value) {
+    case QK_Q8F: l = -128.f; h = 127.f; break;
+    case QK_Q8S: l = -127.f; h = 127.f; break;
+    case QK_Q4F: l = -8.f; h = 7.f; break;
+    case QK_Q4S: l = -7.f; h = 7.f; break;
+    case QK_Q2F: l = -2.f; h = 1.f; break;
+    case QK_Q2S: l = -1.f; h = 1.f; break;
+    case QK_E4M3: l = -448.f; h = 448.f; break;
+    case QK_E5M2: l = -57344.f; h = 57344.f; break;
+    case QK_E2M1: l = -6.f; h = 6.f; break;
+    default: return QK_ERR_UNSUPPORTED_SCHEME;
+    }
+    if (lo) *lo = l;
+    if (hi) *hi = h;
+    return QK_OK;
+}
+
+size_t qk_workspace_bytes(void) { return 256; }
+
+size_t qk_workspace_bytes_for(const QkTensor *input, const QkScheme *scheme, int input_dtype)
+{
+    // Per tensor: one absmax cell.  Per block: the fused kernel needs nothing; layouts that
+    // fall back to the general kernels stage F-typed scales behind the cell.
+    size_t bytes = 256;
+    if (!input || !scheme || dtype_size(input_dtype) == 0 || check_scheme(scheme) != QK_OK) return bytes;
+    if (!input->shape || input->rank < 1 || input->rank > QK_MAX_RANK) return bytes;
+    Geometry g;
+    if (build_geometry(g, scheme, input, nullptr) != QK_OK) return bytes;
+    if (!g.per_tensor) bytes += (size_t)g.nscales * (size_t)dtype_size(input_dtype);
+    return (bytes + 255) & ~(size_t)255;
+}
+
+int qk_quantize(const QkTensor *input, const QkTensor *output, const QkTensor *scale, const QkTensor *out_scale,
+                const QkScheme *scheme, int input_dtype, void *stream)
+{
+    if (!scale) return QK_ERR_NULL;
+    return quantize_common(input, output, scale, out_scale, nullptr, false, nullptr, scheme, input_dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor *params, const QkScheme *scheme,
+                  int output_dtype, void *stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!values || !output || !params || !scheme) return QK_ERR_NULL;
+    int rc = check_scheme(scheme);
+    if (rc) return rc;
+    const int fsize = dtype_size(output_dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    if ((rc = check_tensor(output, fsize))) return rc;
+    if ((rc = check_tensor(values, scheme->store == QK_STORE_U32 ? 4 : 1))) return rc;
+    if ((rc = check_tensor(params, dtype_size(scheme->param)))) return rc;
+    Geometry g;
+    if ((rc = build_geometry(g, scheme, output, values))) return rc;
+    if ((rc = check_scales_shape(g, params))) return rc;
+    if (!is_contiguous(values) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (g.n == 0) return QK_OK;
+
+    const LaunchCfg cfg = current_cfg();
+    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params);
+    if (lg >= -1) {
+        DequantArgs a;
+        a.values = values->ptr;
+        a.params = params->ptr;
+        a.out = output->ptr;
+        a.nunits = g.n / dequant_unit_elems(output_dtype, g.kind);
+        a.lg_units_per_block = lg;
+        a.param = scheme->param;
+        a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
+        count_launch();
+        return cuda_status(launch_dequantize(output_dtype, g.kind, a, cfg, stream));
+    }
+    GeneralDequantArgs a;
+    fill_layout(a.layout, g, params, nullptr);
+    a.values = values->ptr;
+    a.params = params->ptr;
+    a.out = output->ptr;
+    a.nitems = g.n / g.nq;
+    a.nq = g.nq;
+    a.kind = g.kind;
+    a.fdt = output_dtype;
+    a.param = scheme->param;
+    count_launch();
+    return cuda_status(launch_general_dequantize(a, cfg, stream));
+}
+
+int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkScheme *scheme, int input_dtype,
+                      void *workspace, size_t workspace_bytes, void *stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!input || !scale || !scheme) return QK_ERR_NULL;
+    int rc = check_scheme(scheme);
+    if (rc) return rc;
+    const int fsize = dtype_size(input_dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    if ((rc = check_tensor(input, fsize))) return rc;
+    if ((rc = check_tensor(scale, fsize))) return rc;
+    Geometry g;
+    if ((rc = build_geometry(g, scheme, input, nullptr))) return rc;
+    if ((rc = check_scales_shape(g, scale))) return rc;
+    if (!is_contiguous(input)) return QK_ERR_LAYOUT;
+    float lo, hi;
+    qk_value_range(scheme->value, &lo, &hi);
+    const float range = hi - lo;
+    const LaunchCfg cfg = current_cfg();
+
+    if (g.per_tensor) {
+        if (!workspace || workspace_bytes < sizeof(unsigned int)) return QK_ERR_WORKSPACE;
+        if (!aligned(workspace, 4)) return QK_ERR_ALIGN;
+        unsigned int *cell = static_cast<unsigned int *>(workspace);
+        count_launch(g.n > 0 ? 3 : 2);
+        cudaError_t e = launch_absmax(input_dtype, input->ptr, g.n, cell, cfg, stream);
+        if (e != cudaSuccess) return cuda_status(e);
+        return cuda_status(launch_finalize_scale(cell, scale->ptr, input_dtype, range, stream));
+    }
+    if (g.n == 0) return QK_OK;
+    const int per16 = 16 / fsize;
+    const int lg = (g.last_dim_blocks && g.B % per16 == 0) ? log2_exact(g.B / per16) : -1;
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && lg >= 0 && lg <= 5 && aligned(input->ptr, 16) && is_contiguous(scale)) {
+        count_launch();
+        return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / per16, lg, range, cfg, stream));
+    }
+    GeneralScalesArgs a;
+    fill_layout(a.layout, g, scale, nullptr);
+    a.in = input->ptr;
+    a.scale_out = scale->ptr;
+    a.nblocks = g.nscales;
+    a.fdt = input_dtype;
+    a.range = range;
+    count_launch();
+    return cuda_status(launch_general_scales(a, cfg, stream));
+}
+
+int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                        const QkScheme *scheme, int input_dtype, void *workspace, size_t workspace_bytes,
+                        void *stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!input || !scheme) return QK_ERR_NULL;
+    int rc = check_scheme(scheme);
+    if (rc) return rc;
+    if (scheme->level == QK_LEVEL_TENSOR) {
+        if (!workspace || workspace_bytes < sizeof(unsigned int)) return QK_ERR_WORKSPACE;
+        if (!aligned(workspace, 4)) return QK_ERR_ALIGN;
+        const int fsize = dtype_size(input_dtype);
+        if (fsize == 0) return QK_ERR_DTYPE;
+        if ((rc = check_tensor(input, fsize))) return rc;
+        if (!is_contiguous(input)) return QK_ERR_LAYOUT;
+        unsigned int *cell = static_cast<unsigned int *>(workspace);
+        const long long n = numel(input);
+        count_launch(n > 0 ? 2 : 1);
+        cudaError_t e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
+        if (e != cudaSuccess) return cuda_status(e);
+        return quantize_common(input, output, nullptr, out_scale, reinterpret_cast<const float *>(cell), false,
+                               nullptr, scheme, input_dtype, stream);
+    }
+    // Per block: fused kernel, or (general layouts) scales staged in the workspace.
+    void *gen_scales = nullptr;
+    if (workspace && workspace_bytes >= qk_workspace_bytes_for(input, scheme, input_dtype))
+        gen_scales = static_cast<char *>(workspace) + 256;
+    return quantize_common(input, output, nullptr, out_scale, nullptr, true, gen_scales, scheme, input_dtype, stream);
+}
+
+int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, void *stream)
+{
+    if (!input || !absmax_out) return QK_ERR_NULL;
+    const int fsize = dtype_size(input_dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    int rc = check_tensor(input, fsize);
+    if (rc) return rc;
+    if (!is_contiguous(input)) return QK_ERR_LAYOUT;
+    if (!aligned(absmax_out, 4)) return QK_ERR_ALIGN;
+    const long long n = numel(input);
+    count_launch(n > 0 ? 2 : 1);
+    return cuda_status(launch_absmax(input_dtype, input->ptr, n, reinterpret_cast<unsigned int *>(absmax_out),
+                                     current_cfg(), static_cast<cudaStream_t>(stream)));
+}
+
+int qk_quantize_from_absmax(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                            const float *absmax, const QkScheme *scheme, int input_dtype, void *stream)
+{
+    if (!absmax || !scheme) return QK_ERR_NULL;
+    if (scheme->level != QK_LEVEL_TENSOR) return QK_ERR_UNSUPPORTED_SCHEME;
+    return quantize_common(input, output, nullptr, out_scale, absmax, false, nullptr, scheme, input_dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+
+// ---- NCCL, resolved at run time so that the library has no link-time NCCL dependency -----------
+int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream)
+{
+    typedef int (*allreduce_fn)(const void *, void *, size_t, int, int, void *, cudaStream_t);
+    static std::atomic<allreduce_fn> cached{nullptr};
+    allreduce_fn fn = cached.load();
+    if (!fn) {
+        void *sym = dlsym(RTLD_DEFAULT, "ncclAllReduce");
+        if (!sym) {
+            void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (h) sym = dlsym(h, "ncclAllReduce");
+        }
+        if (!sym) return QK_ERR_NCCL;
+        fn = reinterpret_cast<allreduce_fn>(sym);
+        cached.store(fn);
+    }
+    if (!buf || !comm) return QK_ERR_NULL;
+    // ncclFloat32 = 7, ncclMax = 2 (nccl.h: ncclDataType_t, ncclRedOp_t)
+    const int rc = fn(buf, buf, count, 7, 2, comm, static_cast<cudaStream_t>(stream));
+    return rc == 0 ? QK_OK : QK_ERR_NCCL;
+}
+
+const char *qk_strerror(int status)
+{
+    switch (status) {
+    case QK_OK: return "ok";
+    case QK_ERR_UNSUPPORTED_SCHEME: return "unsupported quantization scheme";
+    case QK_ERR_BLOCK_SIZE: return "block size must be non-zero, fit the tensor rank and be divisible by num_quants";
+    case QK_ERR_SHAPE: return "shape mismatch (last dim must be a multiple of num_quants; scales must hold one value per block)";
+    case QK_ERR_DTYPE: return "element size does not match the declared element type";
+    case QK_ERR_LAYOUT: return "values, input and output must be contiguous";
+    case QK_ERR_ALIGN: return "pointer is not aligned to its element size";
+    case QK_ERR_NULL: return "null argument";
+    case QK_ERR_WORKSPACE: return "workspace missing or too small";
+    case QK_ERR_TOO_LARGE: return "size beyond what this entry point supports";
+    case QK_ERR_NCCL: return "NCCL call failed or NCCL not found";
+    default:
+        if (status >= QK_ERR_CUDA) return cudaGetErrorString((cudaError_t)(status - QK_ERR_CUDA));
+        return "unknown status";
+    }
+}
+
+const char *qk_version(void) { return "cubek-quant-b200 0.1.0 (sm_100a)"; }
+
+uint64_t qk_launch_count(void) { return g_launches.load(); }
+
+void qk_set_tuning(int key, int value)
+{
+    if (key >= 0 && key < TUNE_COUNT) g_tune[key].store(value);
+}
+int qk_get_tuning(int key) { return (key >= 0 && key < TUNE_COUNT) ? g_tune[key].load() : -1; }
+
+}  // extern "C"
+
+namespace qk {
+
+// Shared body of qk_quantize / qk_quantize_dynamic / qk_quantize_from_absmax.
+static int quantize_common(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
+                           const QkTensor *out_scale, const float *absmax, bool dynamic, void *gen_scales,
+                           const QkScheme *scheme, int input_dtype, cudaStream_t stream)
+{
+    if (!input || !output || !out_scale || !scheme) return QK_ERR_NULL;
+    int rc = check_scheme(scheme);
+    if (rc) return rc;
+    const int fsize = dtype_size(input_dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    if ((rc = check_tensor(input, fsize))) return rc;
+    if ((rc = check_tensor(output, scheme->store == QK_STORE_U32 ? 4 : 1))) return rc;
+    if (scale && (rc = check_tensor(scale, fsize))) return rc;
+    if ((rc = check_tensor(out_scale, dtype_size(scheme->param)))) return rc;
+    Geometry g;
+    if ((rc = build_geometry(g, scheme, input, output))) return rc;
+    // check_block_size_compat (crates/cubek-quant/src/lib.rs:20-33)
+    if (!g.per_tensor && g.B % g.nq != 0) return QK_ERR_BLOCK_SIZE;
+    if (scale && (rc = check_scales_shape(g, scale))) return rc;
+    if ((rc = check_scales_shape(g, out_scale))) return rc;
+    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (g.n == 0) return QK_OK;
+
+    float lo, hi;
+    qk_value_range(scheme->value, &lo, &hi);
+    const LaunchCfg cfg = current_cfg();
+    const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale);
+    if (lg >= -1) {
+        QuantArgs a;
+        a.in = input->ptr;
+        a.out = output->ptr;
+        a.scale_in = scale ? scale->ptr : nullptr;
+        a.out_scale = out_scale->ptr;
+        a.absmax = absmax;
+        a.nunits = g.n / unit_elems(input_dtype, g.kind);
+        a.lg_units_per_block = lg;
+        a.param = scheme->param;
+        a.lo = lo;
+        a.hi = hi;
+        a.range = hi - lo;
+        a.force_exact = cfg.force_exact;
+        a.aligned32 = aligned(input->ptr, 32) ? 1 : 0;
+        count_launch();
+        return cuda_status(launch_quantize(input_dtype, g.kind, dynamic, a, cfg, stream));
+    }
+
+    // Layout-general route.
+    GeneralQuantArgs a;
+    const void *scale_ptr = scale ? scale->ptr : nullptr;
+    QkTensor staged;
+    int64_t staged_strides[QK_MAX_RANK], staged_shape[QK_MAX_RANK];
+    if (dynamic) {
+        // Scales are computed first into caller-provided workspace (contiguous, F-typed).
+        if (!gen_scales) return QK_ERR_WORKSPACE;
+        int64_t st = 1;
+        for (int d = g.rank - 1; d >= 0; --d) {
+            staged_shape[d] = (g.shape[d] + g.block[d] - 1) / g.block[d];
+            staged_strides[d] = st;
+            st *= staged_shape[d];
+        }
+        staged.ptr = gen_scales;
+        staged.rank = g.rank;
+        staged.shape = staged_shape;
+        staged.strides = staged_strides;
+        staged.elem_size = fsize;
+        GeneralScalesArgs sa;
+        fill_layout(sa.layout, g, &staged, nullptr);
+        sa.in = input->ptr;
+        sa.scale_out = gen_scales;
+        sa.nblocks = g.nscales;
+        sa.fdt = input_dtype;
+        sa.range = hi - lo;
+        count_launch();
+        cudaError_t e = launch_general_scales(sa, cfg, stream);
+        if (e != cudaSuccess) return cuda_status(e);
+        scale_ptr = gen_scales;
+        fill_layout(a.layout, g, &staged, out_scale);
+    } else {
+        fill_layout(a.layout, g, scale, out_scale);
+    }
+    a.in = input->ptr;
+    a.out = output->ptr;
+    a.scale_in = scale_ptr;
+    a.out_scale = out_scale->ptr;
+    a.absmax = absmax;
+    a.nitems = g.n / g.nq;
+    a.nq = g.nq;
+    a.kind = g.kind;
+    a.fdt = input_dtype;
+    a.param = scheme->param;
+    a.lo = lo;
+    a.hi = hi;
+    a.range = hi - lo;
+    count_launch();
+    return cuda_status(launch_general_quantize(a, cfg, stream));
+}
+
+}  // namespace qk

@@ -1,0 +1,260 @@
+// Shared device helpers for the sm_100a quantize / dequantize kernels.
+//
+// Numeric contract (restating crates/cubek-quant/src/quantize.rs:19-31 and
+// dequantize.rs:22-25 of the reference): every operation on a line of float type F is
+// the correctly rounded result in F.  For f16 / bf16 that is the f32 operation followed
+// by one round-to-nearest-even narrowing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/cubek_quant_b200.h"
+
+namespace qk {
+
+// Stored-code kinds the kernels are specialised on.  Q8F/Q8S (and so on) share a kind and
+// differ only in the clamp bounds passed at launch.
+enum Kind : int {
+    KIND_PACK8 = 0,  // 4 x 8-bit two's-complement codes per u32
+    KIND_PACK4 = 1,  // 8 x 4-bit codes per u32
+    KIND_PACK2 = 2,  // 16 x 2-bit codes per u32
+    KIND_I8 = 3,     // native i8
+    KIND_E2M1 = 4,   // native fp4, two codes per byte (even element in the low nibble)
+    KIND_E4M3 = 5,   // native fp8 e4m3
+    KIND_E5M2 = 6,   // native fp8 e5m2
+    KIND_COUNT = 7
+};
+
+template <int FDT> struct ElemOf;
+template <> struct ElemOf<QK_F32> { using type = float; };
+template <> struct ElemOf<QK_F16> { using type = __half; };
+template <> struct ElemOf<QK_BF16> { using type = __nv_bfloat16; };
+
+template <int FDT> struct FInfo {
+    static constexpr int SIZE = (FDT == QK_F32) ? 4 : 2;
+    static constexpr int PER16 = 16 / SIZE;  // elements in one 128-bit access
+};
+
+// Elements that fill one 32-bit word of output for a kind.
+__host__ __device__ constexpr int kind_elems_per_u32(int kind)
+{
+    return (kind == KIND_PACK4 || kind == KIND_E2M1) ? 8 : (kind == KIND_PACK2) ? 16 : 4;
+}
+__host__ __device__ constexpr int kind_bits(int kind)
+{
+    return (kind == KIND_PACK4 || kind == KIND_E2M1) ? 4 : (kind == KIND_PACK2) ? 2 : 8;
+}
+__host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
+
+// A "unit" is the run of consecutive elements one thread turns into whole output words:
+// at least one 128-bit input access and at least one 32-bit output word.
+template <int FDT, int KIND> struct Unit {
+    static constexpr int ELEMS = cmax(FInfo<FDT>::PER16, kind_elems_per_u32(KIND));
+    static constexpr int IN_BYTES = ELEMS * FInfo<FDT>::SIZE;             // 16, 32 or 64
+    static constexpr int OUT_WORDS = ELEMS / kind_elems_per_u32(KIND);    // 1 or 2
+    static constexpr int IN_VEC16 = IN_BYTES / 16;
+};
+
+// ---- raw memory access ----------------------------------------------------------------
+
+struct alignas(16) Vec16 { uint32_t w[4]; };
+struct alignas(32) Vec32 { uint32_t w[8]; };
+
+// Streaming 128-bit load: read-only path, do not keep the line in L1.
+__device__ __forceinline__ Vec16 ldg128_stream(const void *p)
+{
+    Vec16 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3])
+                 : "l"(p));
+    return r;
+}
+
+// Streaming 256-bit load (sm_100 and later).  The address must be 32-byte aligned.
+__device__ __forceinline__ Vec32 ldg256_stream(const void *p)
+{
+    Vec32 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]),
+                   "=r"(r.w[5]), "=r"(r.w[6]), "=r"(r.w[7])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void stg32_stream(void *p, uint32_t v)
+{
+    asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stg64_stream(void *p, uint32_t a, uint32_t b)
+{
+    asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void stg128_stream(void *p, const Vec16 &v)
+{
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]),
+                 "r"(v.w[2]), "r"(v.w[3])
+                 : "memory");
+}
+// 256-bit store (sm_100 and later); 32-byte aligned address.
+__device__ __forceinline__ void stg256_stream(void *p, const Vec32 &v)
+{
+    asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.w[0]),
+                 "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]),
+                 "r"(v.w[7])
+                 : "memory");
+}
+
+// ---- float type conversions -------------------------------------------------------------
+
+__device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi_to_f32(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// Two f32 -> packed bf16x2 / f16x2, round to nearest even; `lo` lands in bits 0..15.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Round an f32 to type FDT and widen it back.
+template <int FDT> __device__ __forceinline__ float round_to(float v)
+{
+    if constexpr (FDT == QK_F32) return v;
+    else if constexpr (FDT == QK_F16) return __half2float(__float2half_rn(v));
+    else return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float round_to_dyn(int dt, float v)
+{
+    if (dt == QK_F32) return v;
+    if (dt == QK_F16) return __half2float(__float2half_rn(v));
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// Element i of a buffer of float type `dt`, widened to f32.
+__device__ __forceinline__ float load_dyn(const void *p, int dt, int64_t i)
+{
+    if (dt == QK_F32) return reinterpret_cast<const float *>(p)[i];
+    if (dt == QK_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+}
+__device__ __forceinline__ void store_dyn(void *p, int dt, int64_t i, float v)
+{
+    if (dt == QK_F32) reinterpret_cast<float *>(p)[i] = v;
+    else if (dt == QK_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// Widen the 16 bytes of `v` (PER16 elements of type FDT) to f32.
+template <int FDT> __device__ __forceinline__ void widen16(const Vec16 &v, float *out)
+{
+    if constexpr (FDT == QK_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __uint_as_float(v.w[i]);
+    } else if constexpr (FDT == QK_BF16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = bf16_lo_to_f32(v.w[i]);
+            out[2 * i + 1] = bf16_hi_to_f32(v.w[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&v.w[i]));
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
+        }
+    }
+}
+
+// ---- scale arithmetic -----------------------------------------------------------------
+
+// scale = (2 * absmax) / (hi - lo), evaluated in f32 then narrowed to F
+// (crates/cubek-quant/tests/suite/symmetric.rs:35-38, :175-178).
+template <int FDT> __device__ __forceinline__ float scale_from_absmax(float absmax, float range)
+{
+    return round_to<FDT>(__fdiv_rn(2.0f * absmax, range));
+}
+
+// clamp(round(t)) with round-half-to-even; a NaN quotient (0/0) gives code 0.
+__device__ __forceinline__ float round_clamp(float t, float lo, float hi)
+{
+    float r = rintf(t);
+    r = fminf(fmaxf(r, lo), hi);
+    return (t != t) ? 0.0f : r;
+}
+
+// Reference arithmetic, one element, no shortcuts: RN_F(x / s), round, clamp.
+template <int FDT> __device__ __forceinline__ float quantize_exact(float x, float s, float lo, float hi)
+{
+    return round_clamp(round_to<FDT>(__fdiv_rn(x, s)), lo, hi);
+}
+
+// ---- fp4 / fp8 conversions (Blackwell cvt instructions) -----------------------------------
+
+// Two f32 -> one byte of e2m1 codes, round to nearest even, saturating; `lo` -> low nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}"
+        : "=h"(r)
+        : "f"(hi), "f"(lo));
+    return r;
+}
+// One byte of e2m1 codes -> f16x2 (low nibble -> low half).  Exact.
+__device__ __forceinline__ uint32_t cvt_f16x2_from_e2m1x2(uint32_t byte)
+{
+    uint32_t r;
+    uint16_t b = (uint16_t)byte;
+    asm("{\n\t.reg .b8 t;\n\tcvt.u8.u16 t, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, t;\n\t}" : "=r"(r) : "h"(b));
+    return r;
+}
+// Two f32 -> two fp8 codes in the low 16 bits; `lo` -> low byte.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t cvt_f16x2_from_e4m3x2(uint32_t two_bytes)
+{
+    uint32_t r;
+    uint16_t b = (uint16_t)two_bytes;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t cvt_f16x2_from_e5m2x2(uint32_t two_bytes)
+{
+    uint32_t r;
+    uint16_t b = (uint16_t)two_bytes;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(r) : "h"(b));
+    return r;
+}
+
+// ---- launch bookkeeping -----------------------------------------------------------------
+
+struct LaunchCfg {
+    int threads;      // threads per CTA
+    int ctas_per_sm;  // grid cap = SM count * ctas_per_sm
+    int sm_count;
+    int force_exact;  // 1: every unit takes the reference-arithmetic route
+};
+
+}  // namespace qk

@@ -1,0 +1,217 @@
+// Round trip through host buffers: slices of whole rows travel host -> device, are quantized
+// (fused absmax + scale + pack) and dequantized on the device, and codes, scales and restored
+// values travel back.  Three staging slots on three streams overlap the copies in both
+// directions with the kernels.  This is the call a host-resident caller of the reference's
+// test flow makes (create_tensor_from_slice -> quantize -> dequantize -> read_one_tensor,
+// crates/cubek-quant/tests/suite/symmetric.rs:32-127), as one entry point.
+#include <mutex>
+
+#include "common.cuh"
+#include "misc_kernels.cuh"
+
+namespace {
+
+constexpr int kSlots = 3;
+constexpr size_t kSliceTargetBytes = 32u << 20;  // input bytes per slice
+
+struct DeviceStreams {
+    cudaStream_t stream[kSlots] = {nullptr, nullptr, nullptr};
+    bool ready = false;
+};
+DeviceStreams g_streams[64];
+std::mutex g_streams_mutex;
+
+int dtype_size(int dt) { return dt == QK_F32 ? 4 : (dt == QK_F16 || dt == QK_BF16) ? 2 : 0; }
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Plan {
+    int ok = 0;
+    long long rows = 0, cols = 0;       // input viewed as rows x cols (cols = last dim)
+    long long slice_rows = 0;           // rows per slice
+    long long scales_per_row = 0;       // sliced block schemes: scales in one row
+    long long slice_scales = 1;         // scales held by one slice (whole tensor when unsliced)
+    bool sliced = false;
+    int nq = 0;
+    size_t in_row = 0, code_row = 0, scale_row = 0, out_row = 0;  // bytes per row
+    size_t slot_bytes = 0, in_off = 0, code_off = 0, scale_off = 0, out_off = 0, ws_off = 0;
+    bool per_tensor = false;
+};
+
+// Slices are whole rows; for block schemes the blocks must lie along the last dim and divide it,
+// so that no block straddles a slice.  Anything else runs as a single slice.
+Plan make_plan(const QkTensor *input, const QkScheme *scheme, int input_dtype)
+{
+    Plan p;
+    const int fsize = dtype_size(input_dtype);
+    p.nq = qk_num_quants(scheme);
+    if (!input || !input->shape || input->rank < 1 || input->rank > QK_MAX_RANK || fsize == 0 || p.nq == 0) return p;
+    p.cols = input->shape[input->rank - 1];
+    p.rows = 1;
+    for (int d = 0; d < input->rank - 1; ++d) p.rows *= input->shape[d];
+    if (p.cols <= 0 || p.rows <= 0 || p.cols % p.nq) return p;
+    p.per_tensor = scheme->level == QK_LEVEL_TENSOR;
+    bool sliceable = !p.per_tensor;
+    if (!p.per_tensor) {
+        const int br = scheme->block_rank;
+        if (br < 1 || br > input->rank) return p;
+        for (int i = 0; i < br - 1; ++i) sliceable = sliceable && scheme->block[i] == 1;
+        const long long B = scheme->block[br - 1];
+        if (B == 0) return p;
+        sliceable = sliceable && (p.cols % B == 0);
+        p.scales_per_row = (p.cols + B - 1) / B;
+        if (!sliceable) {
+            // N-d blocks: one slice, scales counted over the whole tensor.
+            long long ns = 1;
+            for (int d = 0; d < input->rank; ++d) {
+                const int bi = d - (input->rank - br);
+                const long long b = bi >= 0 ? scheme->block[bi] : 1;
+                ns *= (input->shape[d] + b - 1) / b;
+            }
+            p.slice_scales = ns;
+        }
+    }
+    p.in_row = (size_t)p.cols * fsize;
+    p.code_row = (size_t)(p.cols / p.nq) * (scheme->store == QK_STORE_U32 ? 4 : 1);
+    p.scale_row = (size_t)p.scales_per_row * dtype_size(scheme->param);
+    p.out_row = p.in_row;
+    if (sliceable) {
+        p.slice_rows = (long long)(kSliceTargetBytes / p.in_row);
+        if (p.slice_rows < 1) p.slice_rows = 1;
+        if (p.slice_rows > p.rows) p.slice_rows = p.rows;
+        p.slice_scales = p.scales_per_row * p.slice_rows;
+        p.sliced = p.slice_rows < p.rows;
+    } else {
+        p.slice_rows = p.rows;
+    }
+    p.in_off = 0;
+    p.code_off = align_up(p.in_off + p.in_row * p.slice_rows, 256);
+    p.scale_off = align_up(p.code_off + p.code_row * p.slice_rows, 256);
+    p.out_off = align_up(p.scale_off + (size_t)p.slice_scales * dtype_size(scheme->param), 256);
+    p.ws_off = align_up(p.out_off + p.out_row * p.slice_rows, 256);
+    // workspace: absmax cell (+ staged scales for general layouts)
+    p.slot_bytes = align_up(p.ws_off + 256 + (size_t)p.slice_scales * fsize, 256);
+    p.ok = 1;
+    return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *scheme, int input_dtype)
+{
+    if (!scheme) return 0;
+    Plan p = make_plan(input, scheme, input_dtype);
+    if (!p.ok) return 0;
+    const int slots = p.sliced ? kSlots : 1;
+    return p.slot_bytes * slots;
+}
+
+int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTensor *out_scale,
+                      const QkTensor *restored, const QkScheme *scheme, int input_dtype, void *staging,
+                      size_t staging_bytes, int device)
+{
+    if (!input || !codes || !out_scale || !restored || !scheme || !staging) return QK_ERR_NULL;
+    if (device < 0 || device >= 64) return QK_ERR_SHAPE;
+    Plan p = make_plan(input, scheme, input_dtype);
+    if (!p.ok) return QK_ERR_SHAPE;
+    const int slots = p.sliced ? kSlots : 1;
+    if (staging_bytes < p.slot_bytes * slots) return QK_ERR_WORKSPACE;
+    if (!input->ptr || !codes->ptr || !out_scale->ptr || !restored->ptr) return QK_ERR_NULL;
+
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return QK_ERR_CUDA + (int)e;
+    cudaStream_t *streams;
+    {
+        std::lock_guard<std::mutex> lock(g_streams_mutex);
+        DeviceStreams &ds = g_streams[device];
+        if (!ds.ready) {
+            for (int i = 0; i < kSlots; ++i) {
+                e = cudaStreamCreateWithFlags(&ds.stream[i], cudaStreamNonBlocking);
+                if (e != cudaSuccess) return QK_ERR_CUDA + (int)e;
+            }
+            ds.ready = true;
+        }
+        streams = ds.stream;
+    }
+
+    const int rank = input->rank;
+    const int fsize = dtype_size(input_dtype);
+    const int psize = dtype_size(scheme->param);
+    const int csize = scheme->store == QK_STORE_U32 ? 4 : 1;
+    int status = QK_OK;
+    long long slice = 0;
+    for (long long r0 = 0; r0 < p.rows && status == QK_OK; r0 += p.slice_rows, ++slice) {
+        const long long nr = (p.rows - r0 < p.slice_rows) ? p.rows - r0 : p.slice_rows;
+        const int slot = (int)(slice % slots);
+        cudaStream_t st = streams[slot];
+        char *base = static_cast<char *>(staging) + (size_t)slot * p.slot_bytes;
+
+        // The slot's previous work is ordered before this slice by stream order.
+        e = cudaMemcpyAsync(base + p.in_off, static_cast<const char *>(input->ptr) + (size_t)r0 * p.in_row,
+                            (size_t)nr * p.in_row, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) { status = QK_ERR_CUDA + (int)e; break; }
+
+        // Device views of this slice.  A sliced tensor is [nr, cols]; a single slice keeps the
+        // caller's shape so that N-d blocks still apply.
+        int64_t shp_in[QK_MAX_RANK], shp_code[QK_MAX_RANK], shp_scale[QK_MAX_RANK];
+        int64_t str_in[QK_MAX_RANK], str_code[QK_MAX_RANK], str_scale[QK_MAX_RANK];
+        int vr;
+        QkScheme sch = *scheme;
+        if (!p.sliced) {
+            vr = rank;
+            for (int d = 0; d < rank; ++d) {
+                shp_in[d] = input->shape[d];
+                shp_code[d] = codes->shape[d];
+            }
+            if (p.per_tensor) { shp_scale[0] = 1; }
+            else for (int d = 0; d < rank; ++d) shp_scale[d] = out_scale->shape[d];
+        } else {
+            vr = 2;
+            shp_in[0] = nr; shp_in[1] = p.cols;
+            shp_code[0] = nr; shp_code[1] = p.cols / p.nq;
+            shp_scale[0] = nr; shp_scale[1] = p.scales_per_row;
+            sch.block_rank = 1;
+            sch.block[0] = scheme->block[scheme->block_rank - 1];
+        }
+        const int sr = p.per_tensor ? 1 : vr;
+        auto fill_strides = [](int64_t *str, const int64_t *shp, int r) {
+            int64_t acc = 1;
+            for (int d = r - 1; d >= 0; --d) { str[d] = acc; acc *= shp[d]; }
+        };
+        fill_strides(str_in, shp_in, vr);
+        fill_strides(str_code, shp_code, vr);
+        fill_strides(str_scale, shp_scale, sr);
+        QkTensor t_in{base + p.in_off, vr, shp_in, str_in, fsize};
+        QkTensor t_code{base + p.code_off, vr, shp_code, str_code, csize};
+        QkTensor t_scale{base + p.scale_off, sr, shp_scale, str_scale, psize};
+        QkTensor t_out{base + p.out_off, vr, shp_in, str_in, fsize};
+
+        status = qk_quantize_dynamic(&t_in, &t_code, &t_scale, &sch, input_dtype, base + p.ws_off,
+                                     p.slot_bytes - p.ws_off, st);
+        if (status != QK_OK) break;
+        status = qk_dequantize(&t_code, &t_out, &t_scale, &sch, input_dtype, st);
+        if (status != QK_OK) break;
+
+        e = cudaMemcpyAsync(static_cast<char *>(codes->ptr) + (size_t)r0 * p.code_row, base + p.code_off,
+                            (size_t)nr * p.code_row, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) {
+            const size_t sbytes = p.sliced ? (size_t)nr * p.scale_row : (size_t)p.slice_scales * psize;
+            const size_t soff = p.sliced ? (size_t)r0 * p.scale_row : 0;
+            e = cudaMemcpyAsync(static_cast<char *>(out_scale->ptr) + soff, base + p.scale_off, sbytes,
+                                cudaMemcpyDeviceToHost, st);
+        }
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(static_cast<char *>(restored->ptr) + (size_t)r0 * p.out_row, base + p.out_off,
+                                (size_t)nr * p.out_row, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) status = QK_ERR_CUDA + (int)e;
+    }
+    for (int i = 0; i < slots; ++i) {
+        e = cudaStreamSynchronize(streams[i]);
+        if (e != cudaSuccess && status == QK_OK) status = QK_ERR_CUDA + (int)e;
+    }
+    return status;
+}
+
+}  // extern "C"

@@ -1,0 +1,278 @@
+// Per-tensor absmax (grid-wide reduction) and the layout-general fallback kernels.
+//
+// absmax: stands in for `cubek_reduce::reduce::<_, MaxAbs>` used by callers of the
+// reference (crates/cubek-reduce/src/instructions/maxabs.rs:31-87).  The reference's shared
+// strategy gives ONE cube to each output element (crates/cubek-reduce/src/config.rs:192-206),
+// i.e. a whole-tensor absmax runs on one SM; here every SM streams its
+// slice, reduces with warp shuffles and a shared-memory step, and merges with one atomicMax
+// on the bit pattern of the (non-negative) float, which orders like an unsigned integer.
+//
+// general kernels: any rank <= 8, N-d blocks, strided scales, sizes that do not fill whole
+// units.  They restate BlockScaledLayout::to_source_pos / is_block_start
+// (crates/cubek-quant/src/layout/scales.rs:144-195) per stored item, as the reference does.
+#include "misc_kernels.cuh"
+
+namespace qk {
+
+// ---------------------------------------------------------------------------------------
+// absmax
+// ---------------------------------------------------------------------------------------
+template <int FDT>
+__global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long n, unsigned int *cell)
+{
+    constexpr int PER = FInfo<FDT>::PER16;
+    constexpr int UNR = 4;
+    const char *in = static_cast<const char *>(in_);
+    const long long nchunks = n / PER;
+    float amax = 0.0f;
+
+    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
+    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
+         base += stride) {
+        Vec16 raw[UNR];
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            const long long idx = base + (long long)k * blockDim.x;
+            raw[k] = (idx < nchunks) ? ldg128_stream(in + idx * 16) : Vec16{{0u, 0u, 0u, 0u}};
+        }
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            float x[PER];
+            widen16<FDT>(raw[k], x);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) amax = fmaxf(amax, fabsf(x[i]));
+        }
+    }
+    // ragged tail (fewer than PER elements)
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (long long i = nchunks * PER; i < n; ++i) amax = fmaxf(amax, fabsf(load_dyn(in_, FDT, i)));
+
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    __shared__ float warp_max[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    if (warp == 0) {
+        float v = (lane < (int)(blockDim.x >> 5)) ? warp_max[lane] : 0.0f;
+#pragma unroll
+        for (int m = 4; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+        if (lane == 0) atomicMax(cell, __float_as_uint(v));
+    }
+}
+
+// Scalar route for inputs whose base is not 16-byte aligned.
+__global__ void __launch_bounds__(256) absmax_scalar_kernel(const void *in, int fdt, long long n, unsigned int *cell)
+{
+    float amax = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        amax = fmaxf(amax, fabsf(load_dyn(in, fdt, i)));
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if ((threadIdx.x & 31) == 0) atomicMax(cell, __float_as_uint(amax));
+}
+
+__global__ void finalize_scale_kernel(const unsigned int *cell, void *scale_out, int fdt, float range)
+{
+    const float amax = __uint_as_float(*cell);
+    const float s = __fdiv_rn(2.0f * amax, range);
+    store_dyn(scale_out, fdt, 0, s);
+}
+
+static int grid_for(long long work_items, int per_cta, const LaunchCfg &cfg)
+{
+    long long need = (work_items + per_cta - 1) / per_cta;
+    long long cap = (long long)cfg.sm_count * cfg.ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
+                          cudaStream_t stream)
+{
+    cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return e;
+    if (n == 0) return cudaSuccess;
+    const int threads = 256;
+    if ((reinterpret_cast<uintptr_t>(in) & 15u) != 0) {
+        absmax_scalar_kernel<<<grid_for(n, threads * 8, cfg), threads, 0, stream>>>(in, fdt, n, cell);
+        return cudaGetLastError();
+    }
+    const int per = (fdt == QK_F32) ? 4 : 8;
+    const int grid = grid_for(n / per + 1, threads * 4, cfg);
+    switch (fdt) {
+    case QK_F32: absmax_kernel<QK_F32><<<grid, threads, 0, stream>>>(in, n, cell); break;
+    case QK_F16: absmax_kernel<QK_F16><<<grid, threads, 0, stream>>>(in, n, cell); break;
+    default: absmax_kernel<QK_BF16><<<grid, threads, 0, stream>>>(in, n, cell); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,
+                                  cudaStream_t stream)
+{
+    finalize_scale_kernel<<<1, 1, 0, stream>>>(cell, scale_out, fdt, range);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// layout-general kernels
+// ---------------------------------------------------------------------------------------
+
+// Scale index of linear element `pos` and whether `pos` starts a block.
+__device__ __forceinline__ long long general_scale_pos(const GeneralLayout &L, long long pos, bool *is_start,
+                                                       long long *out_pos = nullptr)
+{
+    if (L.per_tensor) {
+        *is_start = (pos == 0);
+        if (out_pos) *out_pos = 0;
+        return 0;
+    }
+    long long offs = pos, sp = 0, sp_out = 0;
+    bool start = true;
+    for (int d = L.rank - 1; d >= 0; --d) {
+        const long long coord = offs % L.shape[d];
+        offs /= L.shape[d];
+        sp += (coord / L.block[d]) * L.scale_strides[d];
+        sp_out += (coord / L.block[d]) * L.out_scale_strides[d];
+        start = start && (coord % L.block[d] == 0);
+    }
+    *is_start = start;
+    if (out_pos) *out_pos = sp_out;
+    return sp;
+}
+
+// Native element encode of an integral, clamped value.
+__device__ __forceinline__ uint32_t encode_native(int kind, float c)
+{
+    if (kind == KIND_I8) return (uint32_t)(int)c & 0xFFu;
+    if (kind == KIND_E4M3) return cvt_e4m3x2(c, 0.0f) & 0xFFu;
+    return cvt_e5m2x2(c, 0.0f) & 0xFFu;
+}
+
+__global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuantArgs a)
+{
+    const int bits = kind_bits(a.kind);
+    const uint32_t mask = (1u << bits) - 1u;
+    for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < a.nitems;
+         item += (long long)gridDim.x * blockDim.x) {
+        const long long pos = item * a.nq;
+        bool is_start;
+        long long sp_out;
+        const long long sp = general_scale_pos(a.layout, pos, &is_start, &sp_out);
+        float scale_f;
+        if (a.absmax) scale_f = round_to_dyn(a.fdt, __fdiv_rn(2.0f * (*a.absmax), a.range));
+        else scale_f = load_dyn(a.scale_in, a.fdt, sp);
+        const float s_fs = round_to_dyn(a.param, scale_f);
+        if (is_start) store_dyn(a.out_scale, a.param, sp_out, s_fs);
+        const float s = round_to_dyn(a.fdt, s_fs);
+
+        if (a.kind <= KIND_PACK2) {
+            uint32_t word = 0;
+            for (int i = 0; i < a.nq; ++i) {
+                const float t = round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos + i), s));
+                const float c = round_clamp(t, a.lo, a.hi);
+                word |= ((uint32_t)(int)c & mask) << (i * bits);
+            }
+            static_cast<uint32_t *>(a.out)[item] = word;
+        } else if (a.kind == KIND_E2M1) {
+            const float c0 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos), s)), a.lo, a.hi);
+            const float c1 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos + 1), s)), a.lo, a.hi);
+            static_cast<uint8_t *>(a.out)[item] = (uint8_t)cvt_e2m1x2(c0, c1);
+        } else {
+            const float c = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos), s)), a.lo, a.hi);
+            static_cast<uint8_t *>(a.out)[item] = (uint8_t)encode_native(a.kind, c);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDequantArgs a)
+{
+    const int bits = kind_bits(a.kind);
+    const uint32_t mask = (1u << bits) - 1u;
+    const int sign_bit = 1 << (bits - 1), two_pow_n = 1 << bits;
+    for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < a.nitems;
+         item += (long long)gridDim.x * blockDim.x) {
+        const long long pos = item * a.nq;
+        bool is_start;
+        const long long sp = general_scale_pos(a.layout, pos, &is_start);
+        const float s = round_to_dyn(a.fdt, load_dyn(a.params, a.param, sp));
+        if (a.kind <= KIND_PACK2) {
+            const uint32_t word = static_cast<const uint32_t *>(a.values)[item];
+            for (int i = 0; i < a.nq; ++i) {
+                const int raw = (int)((word >> (i * bits)) & mask);
+                const int q = raw - (raw >= sign_bit ? two_pow_n : 0);
+                store_dyn(a.out, a.fdt, pos + i, s * (float)q);
+            }
+        } else if (a.kind == KIND_E2M1) {
+            uint32_t h2 = cvt_f16x2_from_e2m1x2(static_cast<const uint8_t *>(a.values)[item]);
+            float2 f = __half22float2(*reinterpret_cast<__half2 *>(&h2));
+            store_dyn(a.out, a.fdt, pos, s * f.x);
+            store_dyn(a.out, a.fdt, pos + 1, s * f.y);
+        } else {
+            const uint32_t b = static_cast<const uint8_t *>(a.values)[item];
+            float q;
+            if (a.kind == KIND_I8) q = (float)(int)(int8_t)b;
+            else {
+                uint32_t h2 = (a.kind == KIND_E4M3) ? cvt_f16x2_from_e4m3x2(b) : cvt_f16x2_from_e5m2x2(b);
+                q = __half22float2(*reinterpret_cast<__half2 *>(&h2)).x;
+            }
+            store_dyn(a.out, a.fdt, pos, s * q);
+        }
+    }
+}
+
+// One thread per block of the scales tensor: absmax over the (possibly clipped) N-d block.
+__global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScalesArgs a)
+{
+    const GeneralLayout &L = a.layout;
+    for (long long bi = (long long)blockIdx.x * blockDim.x + threadIdx.x; bi < a.nblocks;
+         bi += (long long)gridDim.x * blockDim.x) {
+        long long bc[QK_MAX_RANK], ext[QK_MAX_RANK];
+        long long rem = bi, cnt = 1, sp = 0;
+        for (int d = L.rank - 1; d >= 0; --d) {
+            const long long nb = (L.shape[d] + L.block[d] - 1) / L.block[d];
+            bc[d] = rem % nb;
+            rem /= nb;
+        }
+        for (int d = 0; d < L.rank; ++d) {
+            const long long start = bc[d] * L.block[d];
+            ext[d] = (L.shape[d] - start < L.block[d]) ? L.shape[d] - start : L.block[d];
+            cnt *= ext[d];
+            sp += bc[d] * L.scale_strides[d];
+        }
+        float amax = 0.0f;
+        for (long long k = 0; k < cnt; ++k) {
+            long long r = k, lin = 0, mul = 1;
+            for (int d = L.rank - 1; d >= 0; --d) {
+                const long long coord = bc[d] * L.block[d] + r % ext[d];
+                r /= ext[d];
+                lin += coord * mul;
+                mul *= L.shape[d];
+            }
+            amax = fmaxf(amax, fabsf(load_dyn(a.in, a.fdt, lin)));
+        }
+        store_dyn(a.scale_out, a.fdt, sp, __fdiv_rn(2.0f * amax, a.range));
+    }
+}
+
+cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (a.nitems == 0) return cudaSuccess;
+    general_quantize_kernel<<<grid_for(a.nitems, 256, cfg), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+cudaError_t launch_general_dequantize(const GeneralDequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (a.nitems == 0) return cudaSuccess;
+    general_dequantize_kernel<<<grid_for(a.nitems, 256, cfg), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+cudaError_t launch_general_scales(const GeneralScalesArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (a.nblocks == 0) return cudaSuccess;
+    general_scales_kernel<<<grid_for(a.nblocks, 256, cfg), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace qk

@@ -1,0 +1,61 @@
+// Declarations for the per-tensor absmax reduction and the layout-general fallback kernels.
+#pragma once
+
+#include "common.cuh"
+
+#define QK_MAX_RANK 8
+
+namespace qk {
+
+// Host-built description of the scales layout, mirroring BlockScaledLayout /
+// PerTensorLayout (crates/cubek-quant/src/layout/scales.rs:66-160).
+struct GeneralLayout {
+    int rank;
+    int per_tensor;
+    long long shape[QK_MAX_RANK];          // unpacked value shape
+    long long block[QK_MAX_RANK];          // block extents, left-padded with 1
+    long long scale_strides[QK_MAX_RANK];  // strides of the scales tensor (elements)
+    // strides of the second scales tensor of a quantize call (`out_scale`); the reference builds
+    // one view per scales handle (crates/cubek-quant/src/quantize.rs:313, :317)
+    long long out_scale_strides[QK_MAX_RANK];
+};
+
+struct GeneralQuantArgs {
+    GeneralLayout layout;
+    const void *in;
+    void *out;
+    const void *scale_in;
+    void *out_scale;
+    const float *absmax;
+    long long nitems;  // stored items (u32 words or native bytes)
+    int nq, kind, fdt, param;
+    float lo, hi, range;
+};
+
+struct GeneralDequantArgs {
+    GeneralLayout layout;
+    const void *values;
+    const void *params;
+    void *out;
+    long long nitems;
+    int nq, kind, fdt, param;
+};
+
+struct GeneralScalesArgs {
+    GeneralLayout layout;
+    const void *in;
+    void *scale_out;
+    long long nblocks;
+    int fdt;
+    float range;
+};
+
+cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
+                          cudaStream_t stream);
+cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,
+                                  cudaStream_t stream);
+cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_general_dequantize(const GeneralDequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_general_scales(const GeneralScalesArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
+
+}  // namespace qk

@@ -1,0 +1,14 @@
+// Quantize kernels instantiated for bf16 inputs.
+#include "quantize_inst.cuh"
+
+namespace qk {
+cudaError_t launch_quantize_bf16(int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return launch_quantize_t<QK_BF16>(kind, dyn, args, cfg, stream);
+}
+cudaError_t launch_block_scales_bf16(const void *in, void *scale_out, long long nchunks, int lg, float range,
+                                   const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return launch_block_scales_t<QK_BF16>(in, scale_out, nchunks, lg, range, cfg, stream);
+}
+}  // namespace qk

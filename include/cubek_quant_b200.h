@@ -1,0 +1,183 @@
+/*
+ * cubek_quant_b200 — C ABI of the B200 (sm_100a) quantize / dequantize library.
+ *
+ * Every entry point replaces one interface of the reference crate `cubek-quant`
+ * (paths below are relative to the reference checkout).  All functions are
+ * asynchronous on the caller's CUDA stream, allocate no device memory, never
+ * synchronise the device and return a status code instead of panicking.
+ *
+ * Pointers inside QkTensor are DEVICE pointers unless a function says otherwise.
+ */
+#ifndef CUBEK_QUANT_B200_H
+#define CUBEK_QUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- scheme: mirrors `cubecl_common::quant::scheme` as re-exported at
+ *      crates/cubek-quant/src/lib.rs:14 -------------------------------------------- */
+
+/* Float element types of inputs, outputs and params (`ElemType::Float(..)` passed as
+ * `input_elem` at crates/cubek-quant/src/quantize.rs:181; Flex32 is treated as F32). */
+typedef enum { QK_F32 = 0, QK_F16 = 1, QK_BF16 = 2 } QkDType;
+
+/* `QuantValue` (crates/cubek-quant/tests/suite/mod.rs:18-38, quantize.rs:192-198). */
+typedef enum {
+    QK_Q8F = 0, QK_Q8S = 1, QK_Q4F = 2, QK_Q4S = 3, QK_Q2F = 4, QK_Q2S = 5,
+    QK_E4M3 = 6, QK_E5M2 = 7, QK_E2M1 = 8
+} QkValue;
+
+/* `QuantStore` (quantize.rs:187, :199). */
+typedef enum { QK_STORE_NATIVE = 0, QK_STORE_U32 = 1 } QkStore;
+
+/* `QuantParam` (symmetric.rs:65); the value is a QkDType. */
+typedef enum { QK_PARAM_F32 = 0, QK_PARAM_F16 = 1, QK_PARAM_BF16 = 2 } QkParam;
+
+/* `QuantLevel` (symmetric.rs:61, :202). */
+typedef enum { QK_LEVEL_TENSOR = 0, QK_LEVEL_BLOCK = 1 } QkLevel;
+
+/* `QuantMode` (symmetric.rs:25). */
+typedef enum { QK_MODE_SYMMETRIC = 0 } QkMode;
+
+/* `QuantScheme { value, param, store, level, mode }`.  `block` holds `block_rank` u8
+ * extents (as `BlockSize` does); they are right-aligned to the tensor rank and
+ * left-padded with 1, like `BlockSize::to_dim_vec` (layout/scales.rs:239). */
+typedef struct {
+    int32_t value;       /* QkValue */
+    int32_t param;       /* QkParam */
+    int32_t store;       /* QkStore */
+    int32_t level;       /* QkLevel */
+    int32_t mode;        /* QkMode  */
+    int32_t block_rank;  /* 0 for QK_LEVEL_TENSOR */
+    uint8_t block[8];
+} QkScheme;
+
+/* The fields the reference reads from `TensorHandleRef` (`handle`, `shape`, `strides`,
+ * `elem_size`: layout/scales.rs:213-215, quantize.rs:234-239).  Strides in elements.
+ * `shape`/`strides` are host arrays of `rank` entries. */
+typedef struct {
+    void *ptr;
+    int32_t rank;
+    const int64_t *shape;
+    const int64_t *strides;
+    int32_t elem_size;
+} QkTensor;
+
+/* ---- status codes.  The "panic class" (1..4) stands for the reference's `panic!` /
+ *      `assert!` sites; the rest map to `Err(LaunchError)`. ------------------------- */
+enum {
+    QK_OK = 0,
+    QK_ERR_UNSUPPORTED_SCHEME = 1, /* quantize.rs:203-206, :218, :273, :324; dequantize.rs:205-208, :226, :278, :330 */
+    QK_ERR_BLOCK_SIZE = 2,         /* lib.rs:28-31 */
+    QK_ERR_SHAPE = 3,              /* last dim not a multiple of num_quants, or shapes that disagree */
+    QK_ERR_DTYPE = 4,              /* elem_size does not match the declared element type */
+    QK_ERR_LAYOUT = 5,             /* non-contiguous values / input / output */
+    QK_ERR_ALIGN = 6,              /* pointer not aligned to its element / word size */
+    QK_ERR_NULL = 7,
+    QK_ERR_WORKSPACE = 8,          /* workspace missing or too small */
+    QK_ERR_TOO_LARGE = 9,          /* more elements than the entry point supports */
+    QK_ERR_NCCL = 10,
+    QK_ERR_CUDA = 1000             /* QK_ERR_CUDA + cudaError_t */
+};
+
+/* Quantized values per stored item: 32/bits for QK_STORE_U32; 2 for native E2M1 (two fp4
+ * codes per byte), else 1.  `QuantScheme::num_quants` (quantize.rs:144, :290).  0 if invalid. */
+int qk_num_quants(const QkScheme *scheme);
+
+/* `QuantValue::range()` (quantize.rs:243, :296).  Returns QK_OK or QK_ERR_UNSUPPORTED_SCHEME. */
+int qk_value_range(int value, float *lo, float *hi);
+
+/*
+ * Replaces `cubek_quant::quantize::launch_ref` (quantize.rs:174-221), same argument order.
+ *   input     float tensor of type `input_dtype`, contiguous
+ *   output    quantized tensor: u32 words of shape [.., n/num_quants] (QK_STORE_U32), or
+ *             1-byte items (QK_STORE_NATIVE: i8, e4m3, e5m2; fp4 pairs of shape [.., n/2])
+ *   scale     scales typed `input_dtype`: shape [1] per tensor, else one per block
+ *             (its strides are honoured)
+ *   out_scale receives the scales cast to the param type; same shape/strides rules
+ */
+int qk_quantize(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
+                const QkTensor *out_scale, const QkScheme *scheme, int input_dtype,
+                void *stream);
+
+/*
+ * Replaces `cubek_quant::dequantize::launch_ref` (dequantize.rs:171-229), same argument order.
+ *   values  quantized tensor (as written by qk_quantize)
+ *   output  float tensor of type `output_dtype`, contiguous, shape = unpacked shape
+ *   params  scales typed as the scheme's param
+ */
+int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor *params,
+                  const QkScheme *scheme, int output_dtype, void *stream);
+
+/*
+ * The caller-side half of the reference flow: absmax per tensor / per block
+ * (`cubek_reduce::reduce::<_, MaxAbs>`, crates/cubek-reduce/src/lib.rs:93-131,
+ * instructions/maxabs.rs:31-87) followed by `scale = 2*absmax / (q_max - q_min)`
+ * (crates/cubek-quant/tests/suite/symmetric.rs:35-38, :175-178).  Writes `scale`
+ * typed `input_dtype`, ready to be handed to qk_quantize.
+ * Per tensor it needs `qk_workspace_bytes()` bytes of device workspace; per block none.
+ */
+int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkScheme *scheme,
+                      int input_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Fused form of qk_compute_scales + qk_quantize with identical results: per block one
+ * pass (absmax, scale, round, clamp, pack in registers); per tensor two passes (grid-wide
+ * absmax, then quantize).  `out_scale` is typed as the scheme's param.
+ */
+int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                        const QkScheme *scheme, int input_dtype,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Per-tensor quantize split for tensors sharded over several GPUs: phase 1 leaves the
+ * shard's absmax as one f32 in `absmax_out` (device); the caller max-reduces that scalar
+ * across ranks (qk_allreduce_max_f32 or any allreduce); phase 2 quantizes with the scale
+ * derived on the device from the reduced absmax.  No reference counterpart: the reference
+ * is single-device.
+ */
+int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, void *stream);
+int qk_quantize_from_absmax(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                            const float *absmax, const QkScheme *scheme, int input_dtype, void *stream);
+
+/* ncclAllReduce(buf, buf, count, ncclFloat32, ncclMax, comm, stream) on a library-resolved
+ * NCCL (libnccl.so.2 already loaded in the process, else dlopen).  `comm` is an ncclComm_t. */
+int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream);
+
+/* Device workspace needed by the per-tensor paths (a fixed, small size). */
+size_t qk_workspace_bytes(void);
+/* Workspace for qk_quantize_dynamic on this input: qk_workspace_bytes() plus, per block, room
+ * to stage F-typed scales when the layout is not the streaming one (N-d blocks, ragged sizes). */
+size_t qk_workspace_bytes_for(const QkTensor *input, const QkScheme *scheme, int input_dtype);
+
+/*
+ * Round trip through HOST buffers: copies `input` (host) to the device in slices, runs
+ * qk_quantize_dynamic then qk_dequantize per slice on internal streams, and copies codes,
+ * scales and the restored tensor back to host memory.  Slices are whole rows, so results
+ * equal the device entry points' for per-block schemes; per-tensor schemes run as one slice.
+ * `staging` is a caller-provided DEVICE buffer of at least qk_host_roundtrip_staging_bytes().
+ * Blocks until the results are in host memory.
+ */
+int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTensor *out_scale,
+                      const QkTensor *restored, const QkScheme *scheme, int input_dtype,
+                      void *staging, size_t staging_bytes, int device);
+size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *scheme, int input_dtype);
+
+const char *qk_strerror(int status);
+const char *qk_version(void);
+
+/* Number of kernels this library has launched in the calling process (for accounting). */
+uint64_t qk_launch_count(void);
+
+/* Kernel variant selection for measurements: 0 = default, see DESIGN notes in the source. */
+void qk_set_tuning(int key, int value);
+int qk_get_tuning(int key);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUBEK_QUANT_B200_H */
