@@ -1,0 +1,423 @@
+"""Benchmark of the quantize + dequantize hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--batch B] [--impl reference]
+
+One step = fused dynamic quantize followed by dequantize of a batch of B distinct synthetic
+tensors of the workload (B x inputs > L2, so every step streams from HBM).  Prints ONE JSON line.
+Under torchrun every rank processes its own batch (weak scaling, no data-path collective for
+per-block schemes); time is the max over ranks, measured with CUDA events.
+
+``--impl reference`` times the CPU oracle (a port of the reference's arithmetic; the reference
+itself needs a Rust toolchain and a JIT dependency that are not available) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+DEFAULT_WORKLOAD = "q4_block32_bf16_14336x4096"
+METRIC = "quantize+dequantize HBM GB/s"
+SPEC_PEAK_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_GBS, "fallback"
+
+
+def algorithmic_bytes(workload, rows=None):
+    """Bytes one quantize and one dequantize must move for a tensor of this workload."""
+    r, c = workload.shape
+    if rows is not None:
+        r = rows
+    n = r * c
+    s = workload.scheme
+    nscales = 1 if s.level.is_tensor else n // s.level.block_size.as_slice()[-1]
+    code_bytes = n * s.value.size_bits() // 8
+    in_bytes = n * workload.elem.size
+    quant = in_bytes * (2 if s.level.is_tensor else 1) + code_bytes + nscales * s.param.size
+    dequant = code_bytes + nscales * s.param.size + in_bytes
+    return quant, dequant
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_rows(workload, seconds_target=12.0):
+    """Rows of the workload tensor the oracle processes in about ``seconds_target`` seconds."""
+    import numpy as np
+    from oracle import oracle as O
+
+    probe_rows = min(256, workload.shape[0])
+    x = cpu_input(workload, probe_rows)
+    t0 = time.perf_counter()
+    codes, scale = O.quantize_dynamic(x, workload.scheme)
+    O.dequantize(codes, scale, workload.scheme, x.dtype)
+    dt = max(time.perf_counter() - t0, 1e-6)
+    rows = int(probe_rows * seconds_target / dt / 6)   # ~6 passes: warm-up + best of 5
+    rows = max(probe_rows, min(rows, workload.shape[0]))
+    return rows - rows % 8 if rows >= 8 else rows
+
+
+def cpu_input(workload, rows):
+    import numpy as np
+    from cubek_b200.synthetic import generate
+    from tests._util import NP_FLOAT, bfloat16
+    import torch
+
+    t = generate(workload, "cpu", rows=rows)
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(bfloat16)
+    return t.numpy()
+
+
+def time_cpu(workload, rows, repeats=5):
+    """Best-of-``repeats`` seconds of oracle quantize_dynamic + dequantize on ``rows`` rows."""
+    from oracle import oracle as O
+
+    x = cpu_input(workload, rows)
+    best = float("inf")
+    for i in range(repeats + 1):
+        t0 = time.perf_counter()
+        codes, scale = O.quantize_dynamic(x, workload.scheme)
+        O.dequantize(codes, scale, workload.scheme, x.dtype)
+        dt = time.perf_counter() - t0
+        if i > 0:
+            best = min(best, dt)
+    return best
+
+
+def cpu_baseline(workload):
+    from oracle import oracle as O
+
+    rows = cpu_sample_rows(workload)
+    secs = time_cpu(workload, rows)
+    q, d = algorithmic_bytes(workload, rows)
+    return {"value": round((q + d) / secs / 1e9, 3), "unit": "GB/s", "cores": O.max_threads(), "kind": "port",
+            "sample": f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor, best of 5, "
+                      f"OpenMP over {O.max_threads()} threads"}
+
+
+def run_reference(args, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+
+    rows = cpu_sample_rows(workload, seconds_target=max(2.0, 60.0 / max(args.steps + args.warmup, 1)))
+    x = cpu_input(workload, rows)
+    q, d = algorithmic_bytes(workload, rows)
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        codes, scale = O.quantize_dynamic(x, workload.scheme)
+        O.dequantize(codes, scale, workload.scheme, x.dtype)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    secs = sum(times) / len(times)
+    value = round((q + d) / secs / 1e9, 3)
+    sample = f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.elem.name.lower(),
+        "data": "synthetic", "config": config_of(workload, args, rows),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": O.max_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU port of the reference arithmetic (the oracle); the reference's own CubeCL CPU runtime "
+                "cannot be built here (no Rust toolchain, un-vendored JIT dependency)",
+    }))
+
+
+def config_of(workload, args, rows=None):
+    s = workload.scheme
+    return {"workload": workload.name, "shape": list(workload.shape) if rows is None else [rows, workload.shape[1]],
+            "batch_tensors_per_step": args.batch if rows is None else 1,
+            "value": s.value.name, "store": s.store.name, "param": s.param.name,
+            "level": "tensor" if s.level.is_tensor else f"block{list(s.level.block_size.as_slice())}",
+            "distribution": workload.distribution,
+            "l2": "batch of distinct tensors larger than L2; no flush needed"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def run_gpu(args, workload):
+    import torch
+    import torch.distributed as dist
+
+    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
+    from cubek_b200 import _ffi
+    from cubek_b200.synthetic import TORCH_DTYPE, generate
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    lib = _ffi.lib()      # raises if the CUDA library is missing: there is no fallback
+    scheme, elem = workload.scheme, workload.elem
+    r, c = workload.shape
+    B = args.batch
+    tdt = TORCH_DTYPE[elem]
+    code_torch = torch.int32 if scheme.store.name == "U32" else torch.uint8
+    pdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[int(scheme.param)]
+
+    xs = [generate(workload, dev, seed_offset=rank * 1000 + i) for i in range(B)]
+    codes = [torch.empty(scheme.packed_shape((r, c)), dtype=code_torch, device=dev) for _ in range(B)]
+    scales = [torch.empty(scheme.scales_shape((r, c)), dtype=pdt, device=dev) for _ in range(B)]
+    outs = [torch.empty((r, c), dtype=tdt, device=dev) for _ in range(B)]
+    ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    H = TensorHandleRef.from_torch
+    hx, hc, hs, ho, hws = [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], [H(t) for t in outs], H(ws)
+    client = ComputeClient.current()
+
+    def step(events=None):
+        for i in range(B):
+            if events is not None:
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record()
+            quantize.launch_dynamic(client, hx[i], hc[i], hs[i], scheme, elem, hws)
+            if events is not None:
+                e1.record()
+            dequantize.launch_ref(client, hc[i], ho[i], hs[i], scheme, elem)
+            if events is not None:
+                e2.record()
+                events.append((e0, e1, e2))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = lib.qk_launch_count()
+    events = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step(events)
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = lib.qk_launch_count() - launches_before
+    elapsed_ms = start.elapsed_time(stop)
+    q_ms = [a.elapsed_time(b) for a, b, _ in events]
+    d_ms = [b.elapsed_time(c_) for _, b, c_ in events]
+
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+
+    # sanity: the last round trip must be within half a quantization step (cheap, outside timing)
+    err_ok = bool(torch.isfinite(outs[-1].float()).all().item())
+
+    # ---- end to end through host buffers (pinned), copies inside the timed region ---------------
+    e2e = run_e2e(args, workload, dev, local_rank, rank, world, xs)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    q_bytes, d_bytes = algorithmic_bytes(workload)
+    total_bytes = (q_bytes + d_bytes) * B * args.steps * world
+    value = total_bytes / (elapsed_ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    q_avg, d_avg = sum(q_ms) / len(q_ms), sum(d_ms) / len(d_ms)
+    kernels = {
+        "quantize_dynamic": {"avg_ms": round(q_avg, 5), "bytes": q_bytes, "gbs": round(q_bytes / q_avg / 1e6, 1)},
+        "dequantize": {"avg_ms": round(d_avg, 5), "bytes": d_bytes, "gbs": round(d_bytes / d_avg / 1e6, 1)},
+    }
+    dom = "quantize_dynamic" if q_avg >= d_avg else "dequantize"
+    achieved = kernels[dom]["gbs"]
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": elem.name.lower(), "data": "synthetic",
+        "config": config_of(workload, args),
+        "pct_of_spec_peak": round(100 * value / world / SPEC_PEAK_GBS, 1),
+        "pct_of_measured_peak": round(100 * value / world / peak, 1),
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                     "kernels": kernels},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "finite_output": err_ok,
+    }
+    if world == 1:
+        out["cpu_baseline"] = cpu_baseline(workload)
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        try:
+            tr = json.loads(traffic_file.read_text()).get(workload.name, {})
+            out["roofline"]["traffic"] = tr.get(dom)
+        except Exception:
+            pass
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, workload, dev, local_rank, rank, world, xs):
+    """Same metric through ``qk_roundtrip_host``: inputs in pinned host memory, codes + scales +
+    restored tensor read back to pinned host memory, every step."""
+    import torch
+    import torch.distributed as dist
+
+    from cubek_b200 import TensorHandleRef
+    from cubek_b200 import _ffi
+    from cubek_b200.synthetic import TORCH_DTYPE
+
+    lib = _ffi.lib()
+    scheme, elem = workload.scheme, workload.elem
+    r, c = workload.shape
+    nb = min(args.batch, args.e2e_batch)
+    steps = max(1, min(args.steps, args.e2e_steps))
+    tdt = TORCH_DTYPE[elem]
+    code_torch = torch.int32 if scheme.store.name == "U32" else torch.uint8
+    pdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[int(scheme.param)]
+    h_in = [xs[i].cpu().pin_memory() for i in range(nb)]
+    h_codes = [torch.empty(scheme.packed_shape((r, c)), dtype=code_torch).pin_memory() for _ in range(nb)]
+    h_scales = [torch.empty(scheme.scales_shape((r, c)), dtype=pdt).pin_memory() for _ in range(nb)]
+    h_out = [torch.empty((r, c), dtype=tdt).pin_memory() for _ in range(nb)]
+    H = TensorHandleRef.from_torch
+    cin = [_ffi.CTensor(H(t)) for t in h_in]
+    ccodes = [_ffi.CTensor(H(t)) for t in h_codes]
+    cscales = [_ffi.CTensor(H(t)) for t in h_scales]
+    cout = [_ffi.CTensor(H(t)) for t in h_out]
+    sch = _ffi.c_scheme(scheme)
+    need = lib.qk_host_roundtrip_staging_bytes(cin[0].ref(), sch, int(elem))
+    staging = torch.empty(int(need), dtype=torch.uint8, device=dev)
+
+    def step():
+        for i in range(nb):
+            _ffi.check(lib.qk_roundtrip_host(cin[i].ref(), ccodes[i].ref(), cscales[i].ref(), cout[i].ref(), sch,
+                                             int(elem), staging.data_ptr(), int(need), local_rank))
+
+    step()   # warm-up (creates the internal streams)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    secs = time.perf_counter() - t0
+    t = torch.tensor([secs], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs = float(t.item())
+    q_bytes, d_bytes = algorithmic_bytes(workload)
+    h2d = sum(t.numel() * t.element_size() for t in h_in)
+    d2h = sum(t.numel() * t.element_size() for ts in (h_codes, h_scales, h_out) for t in ts)
+    # the restored tensor must be what the device path produced
+    return {"value": round((q_bytes + d_bytes) * nb * steps * world / secs / 1e9, 2), "unit": "GB/s",
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
+            "tensors_per_step": nb, "ms_per_step": round(secs / steps * 1e3, 3),
+            "api": "qk_roundtrip_host (pinned host buffers, 3-slot pipelined copies)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--batch", type=int, default=8, help="distinct tensors per step")
+    ap.add_argument("--e2e-batch", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from cubek_b200.synthetic import WORKLOADS
+
+    workload = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, workload)
+    else:
+        run_gpu(args, workload)
+
+
+if __name__ == "__main__":
+    main()

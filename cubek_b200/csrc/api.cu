@@ -15,44 +15,38 @@
 
 namespace qk {
 
-cudaError_t launch_quantize_f32(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_quantize_f16(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_quantize_bf16(int, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_f32(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_f16(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_f32(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_f16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_bf16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f32(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
 
-cudaError_t launch_quantize(int fdt, int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg,
-                            cudaStream_t stream)
+cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+                            const LaunchCfg &cfg, cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_quantize_f32(kind, dyn, args, cfg, stream);
-    case QK_F16: return launch_quantize_f16(kind, dyn, args, cfg, stream);
-    case QK_BF16: return launch_quantize_bf16(kind, dyn, args, cfg, stream);
+    case QK_F32: return launch_quantize_f32(kind, unit_bytes, dyn, clamp, args, cfg, stream);
+    case QK_F16: return launch_quantize_f16(kind, unit_bytes, dyn, clamp, args, cfg, stream);
+    case QK_BF16: return launch_quantize_bf16(kind, unit_bytes, dyn, clamp, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
-                                const LaunchCfg &cfg, cudaStream_t stream)
+                                float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_block_scales_f32(in, scale_out, nchunks, lg, range, cfg, stream);
-    case QK_F16: return launch_block_scales_f16(in, scale_out, nchunks, lg, range, cfg, stream);
-    case QK_BF16: return launch_block_scales_bf16(in, scale_out, nchunks, lg, range, cfg, stream);
+    case QK_F32: return launch_block_scales_f32(in, scale_out, nchunks, lg, range, inv_range, cfg, stream);
+    case QK_F16: return launch_block_scales_f16(in, scale_out, nchunks, lg, range, inv_range, cfg, stream);
+    case QK_BF16: return launch_block_scales_bf16(in, scale_out, nchunks, lg, range, inv_range, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
-int unit_elems(int fdt, int kind)
-{
-    const int per16 = (fdt == QK_F32) ? 4 : 8;
-    return cmax(per16, kind_elems_per_u32(kind));
-}
-
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_COUNT = 4 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {8}, {0}, {0}};
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}};  // ctas_per_sm 0 = one full wave
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -242,43 +236,60 @@ static int log2_exact(long long v)
 static bool aligned(const void *p, unsigned a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // The streaming kernels need whole units, power-of-two blocks made of whole units along the
-// last dim, contiguous scales and vector-aligned bases.  Returns log2(units per block), -1 for
-// per tensor, or -2 when the call has to take the layout-general kernels.
+// last dim, contiguous scales and vector-aligned bases.  Picks the unit (64 bytes when blocks
+// and the tensor allow, else the smallest unit of the kind); returns log2(units per block), -1
+// for per tensor, or -2 when the call has to take the layout-general kernels.
 static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, const QkTensor *out,
-                            const QkTensor *scale, const QkTensor *out_scale)
+                            const QkTensor *scale, const QkTensor *out_scale, int *unit_bytes)
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
-    const int U = unit_elems(fdt, g.kind);
-    if (g.n % U != 0) return -2;
+    const int esz = dtype_size(fdt);
     if (!aligned(in->ptr, 16)) return -2;
-    const int out_words = U / kind_elems_per_u32(g.kind);
-    if (!aligned(out->ptr, 4 * out_words)) return -2;
-    if (g.per_tensor) return -1;
-    if (!g.last_dim_blocks) return -2;
-    if (g.B % U != 0) return -2;
-    const int lg = log2_exact(g.B / U);
-    if (lg < 0 || lg > 5) return -2;
-    if (scale && !is_contiguous(scale)) return -2;
-    if (out_scale && !is_contiguous(out_scale)) return -2;
-    return lg;
+    if (!g.per_tensor) {
+        if (!g.last_dim_blocks) return -2;
+        if (scale && !is_contiguous(scale)) return -2;
+        if (out_scale && !is_contiguous(out_scale)) return -2;
+    }
+    const int candidates[2] = {64, min_unit_bytes(fdt, g.kind)};
+    for (int ci = 0; ci < 2; ++ci) {
+        const int ub = candidates[ci];
+        const int U = ub / esz;
+        if (g.n % U != 0) continue;
+        const int out_words = U / kind_elems_per_u32(g.kind);
+        const int out_align = out_words >= 4 ? 16 : 4 * out_words;
+        if (!aligned(out->ptr, out_align)) continue;
+        *unit_bytes = ub;
+        if (g.per_tensor) return -1;
+        if (g.B % U != 0) continue;
+        const int lg = log2_exact(g.B / U);
+        if (lg < 0 || lg > 5) continue;
+        return lg;
+    }
+    return -2;
 }
 
 static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values, const QkTensor *out,
-                              const QkTensor *params)
+                              const QkTensor *params, int *out_bytes)
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
-    const int E = dequant_unit_elems(fdt, g.kind);
-    if (g.n % E != 0) return -2;
-    const int in_words = E / kind_elems_per_u32(g.kind);
-    if (!aligned(values->ptr, 4 * in_words)) return -2;
+    const int esz = dtype_size(fdt);
     if (!aligned(out->ptr, 16)) return -2;
-    if (g.per_tensor) return -1;
-    if (!g.last_dim_blocks) return -2;
-    if (g.B % E != 0) return -2;
-    const int lg = log2_exact(g.B / E);
-    if (lg < 0) return -2;
-    if (!is_contiguous(params)) return -2;
-    return lg;
+    if (!g.per_tensor && (!g.last_dim_blocks || !is_contiguous(params))) return -2;
+    const int candidates[2] = {64, min_dequant_bytes(fdt, g.kind)};
+    for (int ci = 0; ci < 2; ++ci) {
+        const int ob = candidates[ci];
+        const int E = ob / esz;
+        if (g.n % E != 0) continue;
+        const int in_words = E / kind_elems_per_u32(g.kind);
+        if (!aligned(values->ptr, in_words >= 4 ? 16 : 4 * in_words)) continue;
+        *out_bytes = ob;
+        if (g.per_tensor) return -1;
+        if (g.B % E != 0) continue;
+        const int lg = log2_exact(g.B / E);
+        if (lg < 0) continue;
+        return lg;
+    }
+    return -2;
 }
 
 static int quantize_common(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
@@ -358,18 +369,19 @@ int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor
     if (g.n == 0) return QK_OK;
 
     const LaunchCfg cfg = current_cfg();
-    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params);
+    int out_bytes = 0;
+    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params, &out_bytes);
     if (lg >= -1) {
         DequantArgs a;
         a.values = values->ptr;
         a.params = params->ptr;
         a.out = output->ptr;
-        a.nunits = g.n / dequant_unit_elems(output_dtype, g.kind);
+        a.nunits = g.n / (out_bytes / fsize);
         a.lg_units_per_block = lg;
         a.param = scheme->param;
         a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
         count_launch();
-        return cuda_status(launch_dequantize(output_dtype, g.kind, a, cfg, stream));
+        return cuda_status(launch_dequantize(output_dtype, g.kind, out_bytes, a, cfg, stream));
     }
     GeneralDequantArgs a;
     fill_layout(a.layout, g, params, nullptr);
@@ -419,7 +431,7 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
     const int lg = (g.last_dim_blocks && g.B % per16 == 0) ? log2_exact(g.B / per16) : -1;
     if (!g_tune[TUNE_FORCE_GENERAL].load() && lg >= 0 && lg <= 5 && aligned(input->ptr, 16) && is_contiguous(scale)) {
         count_launch();
-        return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / per16, lg, range, cfg, stream));
+        return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / per16, lg, range, 1.0f / range, cfg, stream));
     }
     GeneralScalesArgs a;
     fill_layout(a.layout, g, scale, nullptr);
@@ -568,7 +580,8 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     float lo, hi;
     qk_value_range(scheme->value, &lo, &hi);
     const LaunchCfg cfg = current_cfg();
-    const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale);
+    int unit_bytes = 0;
+    const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale, &unit_bytes);
     if (lg >= -1) {
         QuantArgs a;
         a.in = input->ptr;
@@ -576,16 +589,19 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         a.scale_in = scale ? scale->ptr : nullptr;
         a.out_scale = out_scale->ptr;
         a.absmax = absmax;
-        a.nunits = g.n / unit_elems(input_dtype, g.kind);
+        a.nunits = g.n / (unit_bytes / fsize);
         a.lg_units_per_block = lg;
         a.param = scheme->param;
         a.lo = lo;
         a.hi = hi;
         a.range = hi - lo;
+        a.inv_range = 1.0f / (hi - lo);
         a.force_exact = cfg.force_exact;
-        a.aligned32 = aligned(input->ptr, 32) ? 1 : 0;
+        a.aligned32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
+        const bool symmetric = (lo == -hi);
+        const bool clamp = need_clamp(input_dtype, g.kind, dynamic, symmetric, scheme->param);
         count_launch();
-        return cuda_status(launch_quantize(input_dtype, g.kind, dynamic, a, cfg, stream));
+        return cuda_status(launch_quantize(input_dtype, g.kind, unit_bytes, dynamic, clamp, a, cfg, stream));
     }
 
     // Layout-general route.

@@ -1,49 +1,66 @@
-// Dequantize kernels instantiated for every (float type, stored-code kind).
+// Dequantize kernels instantiated for every (float type, stored-code kind, unit size).
 #include "dequantize_kernels.cuh"
 
 namespace qk {
 
-template <int FDT, int KIND>
+template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int threads)
+{
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+    return n;
+}
+
+template <int FDT, int KIND, int OB>
 static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
     const int threads = cfg.threads;
+    static const int occ256 = resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB>, 256);
+    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm
+                                             : (threads == 256 ? occ256 : resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB>, threads));
     long long need = (args.nunits + (long long)threads * 4 - 1) / ((long long)threads * 4);
-    const long long cap = (long long)cfg.sm_count * cfg.ctas_per_sm;
+    const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    dequantize_kernel<FDT, KIND><<<(int)need, threads, 0, stream>>>(args);
+    dequantize_kernel<FDT, KIND, OB><<<(int)need, threads, 0, stream>>>(args);
     return cudaGetLastError();
 }
 
+template <int FDT, int KIND>
+static cudaError_t launch_unit(int out_bytes, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    constexpr int MINB = min_dequant_bytes(FDT, KIND);
+    if (out_bytes == 64) return launch_one<FDT, KIND, 64>(args, cfg, stream);
+    if constexpr (MINB < 64) {
+        if (out_bytes == MINB) return launch_one<FDT, KIND, MINB>(args, cfg, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
 template <int FDT>
-static cudaError_t launch_kind(int kind, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+static cudaError_t launch_kind(int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+                               cudaStream_t stream)
 {
     switch (kind) {
-    case KIND_PACK8: return launch_one<FDT, KIND_PACK8>(args, cfg, stream);
-    case KIND_PACK4: return launch_one<FDT, KIND_PACK4>(args, cfg, stream);
-    case KIND_PACK2: return launch_one<FDT, KIND_PACK2>(args, cfg, stream);
-    case KIND_I8: return launch_one<FDT, KIND_I8>(args, cfg, stream);
-    case KIND_E2M1: return launch_one<FDT, KIND_E2M1>(args, cfg, stream);
-    case KIND_E4M3: return launch_one<FDT, KIND_E4M3>(args, cfg, stream);
-    case KIND_E5M2: return launch_one<FDT, KIND_E5M2>(args, cfg, stream);
+    case KIND_PACK8: return launch_unit<FDT, KIND_PACK8>(out_bytes, args, cfg, stream);
+    case KIND_PACK4: return launch_unit<FDT, KIND_PACK4>(out_bytes, args, cfg, stream);
+    case KIND_PACK2: return launch_unit<FDT, KIND_PACK2>(out_bytes, args, cfg, stream);
+    case KIND_I8: return launch_unit<FDT, KIND_I8>(out_bytes, args, cfg, stream);
+    case KIND_E2M1: return launch_unit<FDT, KIND_E2M1>(out_bytes, args, cfg, stream);
+    case KIND_E4M3: return launch_unit<FDT, KIND_E4M3>(out_bytes, args, cfg, stream);
+    case KIND_E5M2: return launch_unit<FDT, KIND_E5M2>(out_bytes, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
-cudaError_t launch_dequantize(int fdt, int kind, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+                              cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_kind<QK_F32>(kind, args, cfg, stream);
-    case QK_F16: return launch_kind<QK_F16>(kind, args, cfg, stream);
-    case QK_BF16: return launch_kind<QK_BF16>(kind, args, cfg, stream);
+    case QK_F32: return launch_kind<QK_F32>(kind, out_bytes, args, cfg, stream);
+    case QK_F16: return launch_kind<QK_F16>(kind, out_bytes, args, cfg, stream);
+    case QK_BF16: return launch_kind<QK_BF16>(kind, out_bytes, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
-}
-
-int dequant_unit_elems(int fdt, int kind)
-{
-    const int size = (fdt == QK_F32) ? 4 : 2;
-    return cmax(32 / size, kind_elems_per_u32(kind));
 }
 
 }  // namespace qk

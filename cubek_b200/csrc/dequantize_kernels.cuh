@@ -4,32 +4,48 @@
 // reference (crates/cubek-quant/src/dequantize.rs:121-167; unpack_q :86-118; the product
 // `cast<F>(scale) * value` :22-25).  There is no addition in the element arithmetic, so a
 // fused multiply-add cannot change a result: outputs are bit-exact.
+//
+// Output dominates the traffic (2-4 bytes written per 0.25-1 byte read), so a thread produces
+// 32 or 64 contiguous bytes with 256-bit stores.  For f16 / bf16 outputs the codes are turned
+// into packed F x2 values directly: a biased field b dropped into the mantissa of 2^k gives
+// F(2^k + b) exactly; subtracting the bias and multiplying by the scale are packed operations
+// whose single rounding is the reference's rounding (the product of two F values is exact in
+// the multiplier and rounded once).
 #pragma once
 
 #include "common.cuh"
+#include "quantize_kernels.cuh"  // packed helpers
 
 namespace qk {
 
 struct DequantArgs {
-    const void *values;   // u32 words or native bytes
-    const void *params;   // param-typed scales, contiguous, one per block (or one)
-    void *out;            // F-typed output
-    long long nunits;     // dequant units in the tensor
+    const void *values;      // u32 words or native bytes
+    const void *params;      // param-typed scales, contiguous, one per block (or one)
+    void *out;               // F-typed output
+    long long nunits;        // dequant units in the tensor
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
-    int param;            // QkParam
-    int aligned32;        // output base 32-byte aligned (256-bit stores allowed)
+    int param;               // QkParam
+    int aligned32;           // output base 32-byte aligned (256-bit stores allowed)
 };
 
-// One dequant unit is 32 bytes of output (64 for f32 from 2-bit codes).
-template <int FDT, int KIND> struct DUnit {
+// One dequant unit: OB bytes of output produced by one thread.
+template <int FDT, int KIND, int OB> struct DUnitT {
+    static constexpr int ESZ = FInfo<FDT>::SIZE;
     static constexpr int EPW = kind_elems_per_u32(KIND);
-    static constexpr int ELEMS = cmax(32 / FInfo<FDT>::SIZE, EPW);
-    static constexpr int IN_WORDS = ELEMS / EPW;                   // 1, 2 or 4
-    static constexpr int OUT_BYTES = ELEMS * FInfo<FDT>::SIZE;     // 32 or 64
+    static constexpr int E = OB / ESZ;          // elements
+    static constexpr int IW = E / EPW;          // input words: 1, 2, 4 or 8
+    static constexpr int OREG = OB / 4;         // output registers
+    static_assert(E % EPW == 0 && IW >= 1, "a unit must consume whole stored words");
 };
+
+// Smallest dequant unit: 32 bytes of output, or one stored word if that is more.
+__host__ __device__ constexpr int min_dequant_bytes(int fdt, int kind)
+{
+    return cmax(32, kind_elems_per_u32(kind) * ((fdt == QK_F32) ? 4 : 2));
+}
 
 // Decode the EPW codes of one stored word into f32 (exact).
-template <int KIND> __device__ __forceinline__ void decode_word(uint32_t w, float *q)
+template <int KIND> __device__ __forceinline__ void decode_word_f32(uint32_t w, float *q)
 {
     if constexpr (KIND == KIND_PACK8 || KIND == KIND_I8) {
         // bias to unsigned, drop the byte into the mantissa of 2^23, subtract 2^23 + 128.
@@ -40,14 +56,21 @@ template <int KIND> __device__ __forceinline__ void decode_word(uint32_t w, floa
         q[3] = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7653)) - 8388736.0f;
     } else if constexpr (KIND == KIND_PACK4) {
         const uint32_t b = w ^ 0x88888888u;
+        const uint32_t ev = b & 0x0F0F0F0Fu, od = (b >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            q[i] = __uint_as_float(((b >> (4 * i)) & 0xFu) | 0x4B000000u) - 8388616.0f;
+        for (int i = 0; i < 4; ++i) {
+            q[2 * i] = __uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7650 + i)) - 8388616.0f;
+            q[2 * i + 1] = __uint_as_float(__byte_perm(od, 0x4B000000u, 0x7650 + i)) - 8388616.0f;
+        }
     } else if constexpr (KIND == KIND_PACK2) {
         const uint32_t b = w ^ 0xAAAAAAAAu;
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-            q[i] = __uint_as_float(((b >> (2 * i)) & 0x3u) | 0x4B000000u) - 8388610.0f;
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t f = (b >> (2 * j)) & 0x03030303u;   // elements j, j+4, j+8, j+12
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                q[j + 4 * i] = __uint_as_float(__byte_perm(f, 0x4B000000u, 0x7650 + i)) - 8388610.0f;
+        }
     } else if constexpr (KIND == KIND_E2M1) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -68,13 +91,71 @@ template <int KIND> __device__ __forceinline__ void decode_word(uint32_t w, floa
     }
 }
 
+// One stored word -> EPW/2 registers of packed F x2 outputs (element order), scale applied.
+// `s` is the scale as f32 (already narrowed to F), `s2` the same value as packed F x2.
 template <int FDT, int KIND>
+__device__ __forceinline__ void dequant_word(uint32_t w, float s, uint32_t s2, uint32_t *o)
+{
+    constexpr int EPW = kind_elems_per_u32(KIND);
+    if constexpr (FDT == QK_F32) {
+        float q[EPW];
+        decode_word_f32<KIND>(w, q);
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) o[i] = __float_as_uint(s * q[i]);
+    } else if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2 ||
+                         ((KIND == KIND_PACK8 || KIND == KIND_I8) && FDT == QK_F16)) {
+        // F(2^k + b) for a biased field b: 0x4300 | b = 128 + b (bf16, b < 128),
+        // 0x6400 | b = 1024 + b (f16, b < 1024).
+        constexpr uint32_t BASE = (FDT == QK_BF16) ? 0x43004300u : 0x64006400u;
+        constexpr float BASE_F = (FDT == QK_BF16) ? 128.0f : 1024.0f;
+        constexpr int BITS = kind_bits(KIND);
+        const uint32_t bias2 = h2_const<FDT>(BASE_F + (float)(1 << (BITS - 1)));
+        if constexpr (BITS == 8) {
+            const uint32_t b = w ^ 0x80808080u;
+            // bytes (0,1) -> halves of o[0]; bytes (2,3) -> o[1]
+            const uint32_t p0 = __byte_perm(b, BASE, 0x7150);           // [b0, BASE.b1, b1, BASE.b3]
+            const uint32_t p1 = __byte_perm(b, BASE, 0x7352);           // [b2, BASE.b1, b3, BASE.b3]
+            o[0] = h2_mul<FDT>(h2_sub<FDT>(p0, bias2), s2);
+            o[1] = h2_mul<FDT>(h2_sub<FDT>(p1, bias2), s2);
+        } else if constexpr (BITS == 4) {
+            const uint32_t b = w ^ 0x88888888u;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // byte k holds elements 2k (low nibble) and 2k+1 (high nibble)
+                const uint32_t byte = __byte_perm(b, 0u, 0x4440 + k);
+                const uint32_t p = ((byte * 0x1001u) & 0x000F000Fu) | BASE;
+                o[k] = h2_mul<FDT>(h2_sub<FDT>(p, bias2), s2);
+            }
+        } else {
+            const uint32_t b = w ^ 0xAAAAAAAAu;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                // nibble k holds elements 2k (low 2 bits) and 2k+1 (high 2 bits)
+                const uint32_t nib = (b >> (4 * k)) & 0xFu;
+                const uint32_t p = ((nib * 0x4001u) & 0x00030003u) | BASE;
+                o[k] = h2_mul<FDT>(h2_sub<FDT>(p, bias2), s2);
+            }
+        }
+    } else if constexpr (KIND == KIND_E2M1 && FDT == QK_F16) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = h2_mul<FDT>(cvt_f16x2_from_e2m1x2(__byte_perm(w, 0u, 0x4440 + k)), s2);
+    } else {
+        // bf16 8-bit codes (9-bit biased values do not fit a bf16 mantissa), bf16 fp4 and fp8:
+        // decode to f32, multiply (exact product), narrow once.
+        float q[EPW];
+        decode_word_f32<KIND>(w, q);
+#pragma unroll
+        for (int i = 0; i < EPW; i += 2) o[i / 2] = h2_pack<FDT>(s * q[i], s * q[i + 1]);
+    }
+}
+
+template <int FDT, int KIND, int OB>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
 {
-    using DU = DUnit<FDT, KIND>;
-    constexpr int E = DU::ELEMS;
-    constexpr int IW = DU::IN_WORDS;
+    using DU = DUnitT<FDT, KIND, OB>;
+    constexpr int IW = DU::IW;
     constexpr int EPW = DU::EPW;
+    constexpr int OREG_PER_WORD = EPW * DU::ESZ / 4;
     constexpr int UNR = 4;
 
     const uint32_t *vals = static_cast<const uint32_t *>(a.values);
@@ -89,48 +170,51 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
          base += stride) {
         uint32_t w[UNR][IW];
         float s[UNR];
+        const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            const bool valid = idx < a.nunits;
-            if constexpr (IW == 1) {
-                w[k][0] = valid ? __ldg(vals + idx) : 0u;
-            } else if constexpr (IW == 2) {
-                uint2 t = valid ? __ldg(reinterpret_cast<const uint2 *>(vals) + idx) : make_uint2(0u, 0u);
-                w[k][0] = t.x;
-                w[k][1] = t.y;
+            const bool valid = full || idx < a.nunits;
+            if (valid) {
+                if constexpr (IW == 1) {
+                    w[k][0] = __ldg(vals + idx);
+                } else if constexpr (IW == 2) {
+                    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(vals) + idx);
+                    w[k][0] = t.x;
+                    w[k][1] = t.y;
+                } else {
+#pragma unroll
+                    for (int v = 0; v < IW / 4; ++v) {
+                        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(vals) + idx * (IW / 4) + v);
+                        w[k][4 * v] = t.x;
+                        w[k][4 * v + 1] = t.y;
+                        w[k][4 * v + 2] = t.z;
+                        w[k][4 * v + 3] = t.w;
+                    }
+                }
+                // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
+                if (lg < 0) s[k] = tensor_scale;
+                else if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(a.params) + (idx >> lg)));
+                else s[k] = round_to<FDT>(load_dyn(a.params, a.param, idx >> lg));
             } else {
-                uint4 t = valid ? __ldg(reinterpret_cast<const uint4 *>(vals) + idx) : make_uint4(0u, 0u, 0u, 0u);
-                w[k][0] = t.x;
-                w[k][1] = t.y;
-                w[k][2] = t.z;
-                w[k][3] = t.w;
+#pragma unroll
+                for (int j = 0; j < IW; ++j) w[k][j] = 0u;
+                s[k] = 0.0f;
             }
-            // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
-            s[k] = (lg < 0) ? tensor_scale : (valid ? round_to<FDT>(load_dyn(a.params, a.param, idx >> lg)) : 0.0f);
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            if (idx >= a.nunits) continue;
-            float q[E];
+            if (!(full || idx < a.nunits)) continue;
+            uint32_t o[DU::OREG];
+            uint32_t s2 = 0;
+            if constexpr (FDT != QK_F32) s2 = h2_pack<FDT>(s[k], s[k]);
 #pragma unroll
-            for (int j = 0; j < IW; ++j) decode_word<KIND>(w[k][j], q + j * EPW);
-            uint32_t o[DU::OUT_BYTES / 4];
-            if constexpr (FDT == QK_F32) {
-#pragma unroll
-                for (int i = 0; i < E; ++i) o[i] = __float_as_uint(s[k] * q[i]);
-            } else if constexpr (FDT == QK_BF16) {
-#pragma unroll
-                for (int i = 0; i < E; i += 2) o[i / 2] = pack_bf16x2(s[k] * q[i], s[k] * q[i + 1]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < E; i += 2) o[i / 2] = pack_f16x2(s[k] * q[i], s[k] * q[i + 1]);
-            }
-            char *dst = out + idx * DU::OUT_BYTES;
+            for (int j = 0; j < IW; ++j) dequant_word<FDT, KIND>(w[k][j], s[k], s2, o + j * OREG_PER_WORD);
+            char *dst = out + idx * OB;
             if (aligned32) {
 #pragma unroll
-                for (int v = 0; v < DU::OUT_BYTES / 32; ++v) {
+                for (int v = 0; v < OB / 32; ++v) {
                     Vec32 t;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) t.w[i] = o[8 * v + i];
@@ -138,7 +222,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                 }
             } else {
 #pragma unroll
-                for (int v = 0; v < DU::OUT_BYTES / 16; ++v) {
+                for (int v = 0; v < OB / 16; ++v) {
                     Vec16 t;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) t.w[i] = o[4 * v + i];
@@ -149,8 +233,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     }
 }
 
-cudaError_t launch_dequantize(int fdt, int kind, const DequantArgs &args, const LaunchCfg &cfg,
+cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
                               cudaStream_t stream);
-int dequant_unit_elems(int fdt, int kind);
 
 }  // namespace qk

@@ -82,7 +82,7 @@ __global__ void finalize_scale_kernel(const unsigned int *cell, void *scale_out,
 static int grid_for(long long work_items, int per_cta, const LaunchCfg &cfg)
 {
     long long need = (work_items + per_cta - 1) / per_cta;
-    long long cap = (long long)cfg.sm_count * cfg.ctas_per_sm;
+    long long cap = (long long)cfg.sm_count * (cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 8);
     if (need < 1) need = 1;
     return (int)(need < cap ? need : cap);
 }

@@ -2,13 +2,14 @@
 #include "quantize_inst.cuh"
 
 namespace qk {
-cudaError_t launch_quantize_f32(int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+cudaError_t launch_quantize_f32(int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+                               const LaunchCfg &cfg, cudaStream_t stream)
 {
-    return launch_quantize_t<QK_F32>(kind, dyn, args, cfg, stream);
+    return launch_quantize_t<QK_F32>(kind, unit_bytes, dyn, clamp, args, cfg, stream);
 }
 cudaError_t launch_block_scales_f32(const void *in, void *scale_out, long long nchunks, int lg, float range,
-                                   const LaunchCfg &cfg, cudaStream_t stream)
+                                   float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
 {
-    return launch_block_scales_t<QK_F32>(in, scale_out, nchunks, lg, range, cfg, stream);
+    return launch_block_scales_t<QK_F32>(in, scale_out, nchunks, lg, range, inv_range, cfg, stream);
 }
 }  // namespace qk

@@ -6,51 +6,78 @@
 
 namespace qk {
 
-template <int FDT, int KIND, bool DYN>
+// One wave exactly: the grid is the number of CTAs the device holds at once (or fewer when the
+// tensor is small), so that no CTA waits for a slot and all finish together.
+template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int threads)
+{
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+    return n;
+}
+
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
 static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
-    constexpr int UNR = 64 / Unit<FDT, KIND>::IN_BYTES;
+    constexpr int UNR = (UB >= 64) ? 2 : 4;
     const int threads = cfg.threads;
+    static const int occ256 = resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, 256);
+    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm
+                                             : (threads == 256 ? occ256 : resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, threads));
     long long need = (args.nunits + (long long)threads * UNR - 1) / ((long long)threads * UNR);
-    const long long cap = (long long)cfg.sm_count * cfg.ctas_per_sm;
+    const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    quantize_kernel<FDT, KIND, DYN><<<(int)need, threads, 0, stream>>>(args);
+    quantize_kernel<FDT, KIND, UB, DYN, CLAMP><<<(int)need, threads, 0, stream>>>(args);
     return cudaGetLastError();
 }
 
-template <int FDT, bool DYN>
-static cudaError_t launch_kind(int kind, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+template <int FDT, int KIND, int UB>
+static cudaError_t launch_mode(bool dyn, bool clamp, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (!dyn) return launch_one<FDT, KIND, UB, false, true>(args, cfg, stream);
+    if (clamp) return launch_one<FDT, KIND, UB, true, true>(args, cfg, stream);
+    return launch_one<FDT, KIND, UB, true, false>(args, cfg, stream);
+}
+
+template <int FDT, int KIND>
+static cudaError_t launch_unit(int unit_bytes, bool dyn, bool clamp, const QuantArgs &args, const LaunchCfg &cfg,
+                               cudaStream_t stream)
+{
+    constexpr int MINB = min_unit_bytes(FDT, KIND);
+    if (unit_bytes == 64) return launch_mode<FDT, KIND, 64>(dyn, clamp, args, cfg, stream);
+    if constexpr (MINB < 64) {
+        if (unit_bytes == MINB) return launch_mode<FDT, KIND, MINB>(dyn, clamp, args, cfg, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int FDT>
+static cudaError_t launch_quantize_t(int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+                                     const LaunchCfg &cfg, cudaStream_t stream)
 {
     switch (kind) {
-    case KIND_PACK8: return launch_one<FDT, KIND_PACK8, DYN>(args, cfg, stream);
-    case KIND_PACK4: return launch_one<FDT, KIND_PACK4, DYN>(args, cfg, stream);
-    case KIND_PACK2: return launch_one<FDT, KIND_PACK2, DYN>(args, cfg, stream);
-    case KIND_I8: return launch_one<FDT, KIND_I8, DYN>(args, cfg, stream);
-    case KIND_E2M1: return launch_one<FDT, KIND_E2M1, DYN>(args, cfg, stream);
-    case KIND_E4M3: return launch_one<FDT, KIND_E4M3, DYN>(args, cfg, stream);
-    case KIND_E5M2: return launch_one<FDT, KIND_E5M2, DYN>(args, cfg, stream);
+    case KIND_PACK8: return launch_unit<FDT, KIND_PACK8>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_PACK4: return launch_unit<FDT, KIND_PACK4>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_PACK2: return launch_unit<FDT, KIND_PACK2>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_I8: return launch_unit<FDT, KIND_I8>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_E2M1: return launch_unit<FDT, KIND_E2M1>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_E4M3: return launch_unit<FDT, KIND_E4M3>(unit_bytes, dyn, clamp, args, cfg, stream);
+    case KIND_E5M2: return launch_unit<FDT, KIND_E5M2>(unit_bytes, dyn, clamp, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
 template <int FDT>
-static cudaError_t launch_quantize_t(int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg,
-                                     cudaStream_t stream)
-{
-    return dyn ? launch_kind<FDT, true>(kind, args, cfg, stream) : launch_kind<FDT, false>(kind, args, cfg, stream);
-}
-
-template <int FDT>
 static cudaError_t launch_block_scales_t(const void *in, void *scale_out, long long nchunks, int lg, float range,
-                                         const LaunchCfg &cfg, cudaStream_t stream)
+                                         float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
 {
-    const int threads = cfg.threads;
+    const int threads = 256;
+    static const int occ = resident_ctas_per_sm(block_scales_kernel<FDT>, 256);
     long long need = (nchunks + (long long)threads * 4 - 1) / ((long long)threads * 4);
-    const long long cap = (long long)cfg.sm_count * cfg.ctas_per_sm;
+    const long long cap = (long long)cfg.sm_count * occ;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    block_scales_kernel<FDT><<<(int)need, threads, 0, stream>>>(in, scale_out, nchunks, lg, range);
+    block_scales_kernel<FDT><<<(int)need, threads, 0, stream>>>(in, scale_out, nchunks, lg, range, inv_range);
     return cudaGetLastError();
 }
 

@@ -4,8 +4,21 @@
 // reference (crates/cubek-quant/src/quantize.rs:100-171).  The reference gives each thread
 // one u32 and resolves the scale index with a div/mod chain per thread; here a thread owns
 // a "unit" of consecutive elements (16..64 bytes of input, whole output words), blocks are
-// power-of-two runs of units, and in the fused form the absmax of a block is reduced with
-// warp shuffles so that the data is read exactly once.
+// power-of-two runs of units, and in the fused form the absmax of a block is reduced in
+// registers (plus warp shuffles when a block spans several lanes) so that the data is read
+// exactly once.
+//
+// The path is HBM bound only if the arithmetic stays cheap: at 6.5 TB/s a bf16 -> q4 kernel
+// consumes ~9 elements per clock per SM, which leaves ~7 ALU-pipe lane-instructions per
+// element.  The element arithmetic below is therefore written per float type:
+//   * f32: exact division as x*r corrected by two FMAs (r = RN(1/s)), rounding by adding
+//     1.5*2^23, packing with shifts-as-multiplies;
+//   * f16 / bf16: the product x*r in f32 narrowed by one cvt.rn.{f16,bf16}x2.f32 gives the
+//     correctly rounded quotient in F (see fast path notes); clamp, round-to-integer and the
+//     code bias are then done two elements at a time in packed {f16,bf16}x2 arithmetic.
+// A slow route with the reference arithmetic spelled out (true division, rintf) handles
+// scales outside the window where those shortcuts are proven, and is what the tests compare
+// the fast route against.
 #pragma once
 
 #include "common.cuh"
@@ -16,176 +29,141 @@ struct QuantArgs {
     const void *in;          // F-typed input, contiguous
     void *out;               // u32 words or native bytes
     const void *scale_in;    // F-typed scales (given-scale form); contiguous, one per block
-    void *out_scale;         // param-typed scales out (may alias nothing else)
+    void *out_scale;         // param-typed scales out
     const float *absmax;     // per tensor: absmax scalar on the device (overrides scale_in)
     long long nunits;        // units in the tensor
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     int param;               // QkParam of out_scale
     float lo, hi, range;     // clamp bounds, hi - lo
+    float inv_range;         // RN(1 / range), computed on the host
     int force_exact;         // 1: reference arithmetic for every unit
-    int aligned32;           // input base is 32-byte aligned (256-bit loads allowed)
+    int aligned32;           // input and output bases are 32-byte aligned (256-bit accesses allowed)
 };
 
-// -------------------------------------------------------------------------------------
-// Loading one unit (16 / 32 / 64 contiguous bytes) with 128- or 256-bit streaming loads.
-// -------------------------------------------------------------------------------------
-template <int IN_BYTES> struct RawUnit { Vec16 v[IN_BYTES / 16]; };
+// A unit: UB bytes of input handled by one thread.
+template <int FDT, int KIND, int UB> struct UnitT {
+    static constexpr int ESZ = FInfo<FDT>::SIZE;
+    static constexpr int U = UB / ESZ;                      // elements
+    static constexpr int EPW = kind_elems_per_u32(KIND);    // elements per output word
+    static constexpr int OW = U / EPW;                      // output words (1, 2, 4 or 8)
+    static constexpr int RAW = UB / 4;                      // 32-bit registers of input
+    static_assert(U % EPW == 0 && OW >= 1, "a unit must fill whole output words");
+};
 
-template <int IN_BYTES>
-__device__ __forceinline__ void load_unit(RawUnit<IN_BYTES> &u, const char *p, bool valid, bool aligned32)
+// Smallest unit for (float type, kind): one 128-bit access and one output word.
+__host__ __device__ constexpr int min_unit_bytes(int fdt, int kind)
 {
-    if (!valid) {
-#pragma unroll
-        for (int i = 0; i < IN_BYTES / 16; ++i) u.v[i] = Vec16{{0u, 0u, 0u, 0u}};
-        return;
-    }
-    if constexpr (IN_BYTES == 16) {
-        u.v[0] = ldg128_stream(p);
-    } else {
-        if (aligned32) {
-#pragma unroll
-            for (int i = 0; i < IN_BYTES / 32; ++i) {
-                Vec32 t = ldg256_stream(p + 32 * i);
-                u.v[2 * i] = Vec16{{t.w[0], t.w[1], t.w[2], t.w[3]}};
-                u.v[2 * i + 1] = Vec16{{t.w[4], t.w[5], t.w[6], t.w[7]}};
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < IN_BYTES / 16; ++i) u.v[i] = ldg128_stream(p + 16 * i);
-        }
-    }
+    return cmax(16, kind_elems_per_u32(kind) * ((fdt == QK_F32) ? 4 : 2));
 }
 
-// -------------------------------------------------------------------------------------
-// Element arithmetic on one unit.
-// -------------------------------------------------------------------------------------
-
-// 1.5 * 2^23: adding it to |v| < 2^22 rounds v to an integer (half to even) and leaves
-// that integer, in two's complement, in the low mantissa bits.
+// 1.5 * 2^23: adding it to |v| < 2^22 rounds v to an integer (half to even) and leaves that
+// integer, in two's complement, in the low mantissa bits.
 #define QK_MAGIC 12582912.0f
 #define QK_MAGIC_BITS 0x4B400000u
 
-// Fast quotient RN_F(x / s) for a scale in the safe exponent window, given r = RN(1/s).
-//   f32: q0 = x*r; q1 = fma(fma(-s, q0, x), r, q0) is the correctly rounded quotient when r
-//        is the correctly rounded reciprocal and nothing under/overflows.  With a caller
-//        supplied scale the first guess is clamped so that a huge quotient ends as +-inf or
-//        a huge finite value of the right sign (never NaN); it is clamped afterwards anyway.
-//   f16/bf16: x and s carry 11 / 8 significant bits, so x/s is never closer than 2^-23 /
-//        2^-17 (relative) to a rounding boundary of F, and the f32 product x*r (error
-//        < 2^-22.9) rounds to the same F value as the exact quotient for every |x/s| in
-//        [1/8, 1024] (checked exhaustively on the host); outside it the code is 0 or clamped.
-template <int FDT, bool BOUNDED>
-__device__ __forceinline__ float fast_quotient(float x, float s, float r, float lo, float hi)
+// ---- packed half helpers ----------------------------------------------------------------
+template <int FDT> __device__ __forceinline__ uint32_t h2_absmax(uint32_t a, uint32_t b)
 {
-    float q0 = x * r;
+    uint32_t r;  // magnitude = max(|a|,|b|) per half; the sign bit is the xor of the signs
+    if constexpr (FDT == QK_BF16) asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("max.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <int FDT> __device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    if constexpr (FDT == QK_BF16) asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <int FDT> __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    if constexpr (FDT == QK_BF16) asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <int FDT> __device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    if constexpr (FDT == QK_BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <int FDT> __device__ __forceinline__ uint32_t h2_min(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    if constexpr (FDT == QK_BF16) asm("min.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("min.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <int FDT> __device__ __forceinline__ uint32_t h2_max(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    if constexpr (FDT == QK_BF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// Two f32 -> packed F x2 (lo in bits 0..15), round to nearest even.
+template <int FDT> __device__ __forceinline__ uint32_t h2_pack(float lo, float hi)
+{
+    if constexpr (FDT == QK_BF16) return pack_bf16x2(lo, hi);
+    else return pack_f16x2(lo, hi);
+}
+// A small integer-valued constant as packed F x2 (both halves).
+template <int FDT> __device__ __forceinline__ uint32_t h2_const(float v) { return h2_pack<FDT>(v, v); }
+
+template <int FDT> __device__ __forceinline__ float h_lo_to_f32(uint32_t p)
+{
+    if constexpr (FDT == QK_BF16) return bf16_lo_to_f32(p);
+    else return __half2float(__ushort_as_half((unsigned short)(p & 0xffffu)));
+}
+template <int FDT> __device__ __forceinline__ float h_hi_to_f32(uint32_t p)
+{
+    if constexpr (FDT == QK_BF16) return bf16_hi_to_f32(p);
+    else return __half2float(__ushort_as_half((unsigned short)(p >> 16)));
+}
+
+// Element i of the raw registers, widened to f32.
+template <int FDT> __device__ __forceinline__ float raw_elem(const uint32_t *raw, int i)
+{
+    if constexpr (FDT == QK_F32) return __uint_as_float(raw[i]);
+    else return (i & 1) ? h_hi_to_f32<FDT>(raw[i >> 1]) : h_lo_to_f32<FDT>(raw[i >> 1]);
+}
+
+// absmax of the unit as f32 (exact: it is one of the inputs).  NaNs are ignored.
+template <int FDT, int RAW> __device__ __forceinline__ float unit_absmax(const uint32_t *raw)
+{
     if constexpr (FDT == QK_F32) {
-        if constexpr (!BOUNDED) q0 = fminf(fmaxf(q0, lo - 2.0f), hi + 2.0f);
-        float e = __fmaf_rn(-s, q0, x);
-        return __fmaf_rn(e, r, q0);
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < RAW; ++i) m = fmaxf(m, fabsf(__uint_as_float(raw[i])));
+        return m;
     } else {
-        return q0;  // narrowed to F by the caller
+        uint32_t m = raw[0];
+#pragma unroll
+        for (int i = 1; i < RAW; ++i) m = h2_absmax<FDT>(m, raw[i]);
+        m = h2_absmax<FDT>(m, m >> 16) & 0x7fffu;  // low half: max(|lo|, |hi|)
+        return h_lo_to_f32<FDT>(m);
     }
 }
 
-template <int FDT, int KIND, bool BOUNDED>
-__device__ __forceinline__ void quantize_unit(const float *x, float s, float lo, float hi, bool fast,
-                                              uint32_t *outw)
+// ---- scale arithmetic (once per unit) -------------------------------------------------------
+
+// (2*absmax) / range, correctly rounded.  Inside [2^-100, 2^100] the quotient is obtained as
+// q0 = a*inv, q = fma(fma(-range, q0, a), inv, q0) with inv = RN(1/range): exhaustively equal to
+// IEEE division for every f32 `a` in that window and every range of a supported value type.
+__device__ __forceinline__ float div_by_range(float a, float range, float inv_range)
 {
-    constexpr int U = Unit<FDT, KIND>::ELEMS;
-    constexpr int OW = Unit<FDT, KIND>::OUT_WORDS;
-    constexpr int EPW = kind_elems_per_u32(KIND);
-    float c[U];  // clamped, integral values
-
-    if (fast) {
-        const float r = __frcp_rn(s);
-        float t[U];
-#pragma unroll
-        for (int i = 0; i < U; ++i) t[i] = fast_quotient<FDT, BOUNDED>(x[i], s, r, lo, hi);
-        if constexpr (FDT == QK_BF16) {
-#pragma unroll
-            for (int i = 0; i < U; i += 2) {
-                uint32_t p = pack_bf16x2(t[i], t[i + 1]);
-                t[i] = bf16_lo_to_f32(p);
-                t[i + 1] = bf16_hi_to_f32(p);
-            }
-        } else if constexpr (FDT == QK_F16) {
-#pragma unroll
-            for (int i = 0; i < U; i += 2) {
-                uint32_t p = pack_f16x2(t[i], t[i + 1]);
-                float2 f = __half22float2(*reinterpret_cast<__half2 *>(&p));
-                t[i] = f.x;
-                t[i + 1] = f.y;
-            }
-        }
-        // clamp first (the bounds are integers, so clamp and round commute), then round.
-#pragma unroll
-        for (int i = 0; i < U; ++i) c[i] = fminf(fmaxf(t[i], lo), hi);
-    } else {
-#pragma unroll
-        for (int i = 0; i < U; ++i) c[i] = quantize_exact<FDT>(x[i], s, lo, hi);
+    if (a >= 7.888609052e-31f && a <= 1.267650600e+30f) {
+        const float q0 = a * inv_range;
+        return __fmaf_rn(__fmaf_rn(-range, q0, a), inv_range, q0);
     }
-
-    if constexpr (KIND == KIND_PACK8 || KIND == KIND_I8) {
-#pragma unroll
-        for (int w = 0; w < OW; ++w) {
-            uint32_t b[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) b[i] = __float_as_uint(c[4 * w + i] + QK_MAGIC);
-            uint32_t l = __byte_perm(b[0], b[1], 0x0040);
-            uint32_t h = __byte_perm(b[2], b[3], 0x0040);
-            outw[w] = __byte_perm(l, h, 0x5410);
-        }
-    } else if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2) {
-        // Bias every code to be non-negative (q + 2^(bits-1)), add the shifted float bit
-        // patterns, remove the constant part, then flip the top bit of every field to get
-        // back to two's complement.
-        constexpr int BITS = kind_bits(KIND);
-        constexpr uint32_t BIAS = 1u << (BITS - 1);
-        constexpr uint32_t FLIP = (BITS == 4) ? 0x88888888u : 0xAAAAAAAAu;
-        uint32_t kconst = 0;
-#pragma unroll
-        for (int i = 0; i < EPW; ++i) kconst += (QK_MAGIC_BITS << (i * BITS));
-#pragma unroll
-        for (int w = 0; w < OW; ++w) {
-            uint32_t acc = 0;
-#pragma unroll
-            for (int i = 0; i < EPW; ++i) {
-                uint32_t b = __float_as_uint(c[EPW * w + i] + (QK_MAGIC + (float)BIAS));
-                acc += b << (i * BITS);
-            }
-            outw[w] = (acc - kconst) ^ FLIP;
-        }
-    } else if constexpr (KIND == KIND_E2M1) {
-#pragma unroll
-        for (int w = 0; w < OW; ++w) {
-            uint32_t by[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float a = (c[8 * w + 2 * i] + QK_MAGIC) - QK_MAGIC;
-                float b = (c[8 * w + 2 * i + 1] + QK_MAGIC) - QK_MAGIC;
-                by[i] = cvt_e2m1x2(a, b);
-            }
-            uint32_t l = __byte_perm(by[0], by[1], 0x0040);
-            uint32_t h = __byte_perm(by[2], by[3], 0x0040);
-            outw[w] = __byte_perm(l, h, 0x5410);
-        }
-    } else {  // KIND_E4M3 / KIND_E5M2
-#pragma unroll
-        for (int w = 0; w < OW; ++w) {
-            uint32_t hw[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                float a = rintf(c[4 * w + 2 * i]);
-                float b = rintf(c[4 * w + 2 * i + 1]);
-                hw[i] = (KIND == KIND_E4M3) ? cvt_e4m3x2(a, b) : cvt_e5m2x2(a, b);
-            }
-            outw[w] = __byte_perm(hw[0], hw[1], 0x5410);
-        }
-    }
+    return __fdiv_rn(a, range);
 }
 
-// Scales outside this window (zero, subnormal-ish, huge, negative, NaN) take the reference
-// arithmetic: the shortcuts above assume 1/s and x*(1/s) stay inside the normal range.
+// Scales outside this window (zero, tiny, huge, negative, NaN) take the reference arithmetic:
+// the shortcuts assume 1/s and x*(1/s) stay inside the normal range.
 __device__ __forceinline__ bool scale_is_safe(float s)
 {
     return s >= 7.888609052e-31f /* 2^-100 */ && s <= 1.267650600e+30f /* 2^100 */;
@@ -197,18 +175,259 @@ template <int FDT, int KIND> __host__ __device__ constexpr bool kind_allows_fast
     return !(KIND == KIND_E5M2 && FDT != QK_F32);
 }
 
+// ---- packing of integral f32 values -----------------------------------------------------------
+// `c` holds integral (or to-be-rounded, already clamped) f32 values in element order.
+template <int KIND, int U> __device__ __forceinline__ void pack_from_f32(const float *c, uint32_t *outw)
+{
+    constexpr int EPW = kind_elems_per_u32(KIND);
+    constexpr int OW = U / EPW;
+    if constexpr (KIND == KIND_PACK8 || KIND == KIND_I8) {
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) b[i] = __float_as_uint(c[4 * w + i] + QK_MAGIC);
+            const uint32_t l = __byte_perm(b[0], b[1], 0x0040);
+            const uint32_t h = __byte_perm(b[2], b[3], 0x0040);
+            outw[w] = __byte_perm(l, h, 0x5410);
+        }
+    } else if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2) {
+        // Bias every code to be non-negative (q + 2^(bits-1)), sum the shifted float bit
+        // patterns (shifts as multiplies, which run on the FMA pipe), remove the constant part,
+        // then flip the top bit of every field to return to two's complement.
+        constexpr int BITS = kind_bits(KIND);
+        constexpr uint32_t BIAS = 1u << (BITS - 1);
+        constexpr uint32_t FLIP = (BITS == 4) ? 0x88888888u : 0xAAAAAAAAu;
+        uint32_t kconst = 0;
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) kconst += (QK_MAGIC_BITS << (i * BITS));
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < EPW; ++i)
+                acc += __float_as_uint(c[EPW * w + i] + (QK_MAGIC + (float)BIAS)) * (1u << (i * BITS));
+            outw[w] = (acc - kconst) ^ FLIP;
+        }
+    } else if constexpr (KIND == KIND_E2M1) {
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t by[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // round to integer; keep the sign of a zero result (-0.3 -> -0, code 0b1000)
+                const float a = copysignf((c[8 * w + 2 * i] + QK_MAGIC) - QK_MAGIC, c[8 * w + 2 * i]);
+                const float b = copysignf((c[8 * w + 2 * i + 1] + QK_MAGIC) - QK_MAGIC, c[8 * w + 2 * i + 1]);
+                by[i] = cvt_e2m1x2(a, b);
+            }
+            const uint32_t l = __byte_perm(by[0], by[1], 0x0040);
+            const uint32_t h = __byte_perm(by[2], by[3], 0x0040);
+            outw[w] = __byte_perm(l, h, 0x5410);
+        }
+    } else {  // KIND_E4M3 / KIND_E5M2
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t hw[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float a = rintf(c[4 * w + 2 * i]);
+                const float b = rintf(c[4 * w + 2 * i + 1]);
+                hw[i] = (KIND == KIND_E4M3) ? cvt_e4m3x2(a, b) : cvt_e5m2x2(a, b);
+            }
+            outw[w] = __byte_perm(hw[0], hw[1], 0x5410);
+        }
+    }
+}
+
+// ---- reference arithmetic route ---------------------------------------------------------------
+template <int FDT, int KIND, int UB>
+__device__ void quantize_unit_exact(const uint32_t *raw, float s, float lo, float hi, uint32_t *outw)
+{
+    using UT = UnitT<FDT, KIND, UB>;
+    float c[UT::U];
+#pragma unroll
+    for (int i = 0; i < UT::U; ++i) c[i] = quantize_exact<FDT>(raw_elem<FDT>(raw, i), s, lo, hi);
+    pack_from_f32<KIND, UT::U>(c, outw);
+}
+
+// ---- fast route ---------------------------------------------------------------------------------
+// Valid for scale_is_safe(s) and finite inputs.  CLAMP = false is used by the fused form when
+// |x/s| cannot reach hi + 0.5 (see need_clamp()).
+//   f32 quotient: q0 = x*r, q = fma(fma(-s, q0, x), r, q0) with r = RN(1/s) is the correctly
+//     rounded quotient.  With a caller-supplied scale (BOUNDED = false) the first guess is
+//     clamped so that a huge quotient ends as +-inf or a huge value of the right sign (never NaN).
+//   f16 / bf16 quotient: x and s carry 11 / 8 significant bits, so x/s is never closer than
+//     2^-23 / 2^-17 (relative) to a rounding boundary of F; the f32 product x*r rounds to the
+//     same F value as the exact quotient for every |x/s| in [1/8, 1024] (checked exhaustively on
+//     the host for all pairs); outside that range the code is 0 or the clamp bound either way.
+template <int FDT, int KIND, int UB, bool CLAMP, bool BOUNDED>
+__device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s, float lo, float hi, uint32_t *outw)
+{
+    using UT = UnitT<FDT, KIND, UB>;
+    constexpr int U = UT::U;
+    constexpr int EPW = UT::EPW;
+    constexpr int OW = UT::OW;
+    const float r = __frcp_rn(s);
+
+    if constexpr (FDT == QK_F32) {
+        float c[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const float x = __uint_as_float(raw[i]);
+            float q0 = x * r;
+            if constexpr (!BOUNDED) q0 = fminf(fmaxf(q0, lo - 2.0f), hi + 2.0f);
+            const float t = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+            c[i] = CLAMP ? fminf(fmaxf(t, lo), hi) : t;
+        }
+        pack_from_f32<KIND, U>(c, outw);
+    } else if constexpr (KIND == KIND_E4M3 || KIND == KIND_E5M2) {
+        float c[U];
+#pragma unroll
+        for (int i = 0; i < U; i += 2) {
+            const uint32_t p = h2_pack<FDT>(raw_elem<FDT>(raw, i) * r, raw_elem<FDT>(raw, i + 1) * r);
+            c[i] = fminf(fmaxf(h_lo_to_f32<FDT>(p), lo), hi);
+            c[i + 1] = fminf(fmaxf(h_hi_to_f32<FDT>(p), lo), hi);
+        }
+        pack_from_f32<KIND, U>(c, outw);
+    } else {
+        // Packed route.  Quotients are narrowed to F two at a time; which two elements share a
+        // register is chosen per kind so that the output word can be assembled with left shifts
+        // only: element j and element j + EPW/2 of a word for the integer packs, neighbours
+        // (2j, 2j+1) for fp4 bytes and for bf16 8-bit codes.
+        const uint32_t lo2 = h2_const<FDT>(lo), hi2 = h2_const<FDT>(hi);
+        constexpr bool SPLIT_PAIRS = (KIND == KIND_PACK4 || KIND == KIND_PACK2 ||
+                                      ((KIND == KIND_PACK8 || KIND == KIND_I8) && FDT == QK_F16));
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t p[EPW / 2];
+#pragma unroll
+            for (int j = 0; j < EPW / 2; ++j) {
+                const int e0 = w * EPW + (SPLIT_PAIRS ? j : 2 * j);
+                const int e1 = w * EPW + (SPLIT_PAIRS ? j + EPW / 2 : 2 * j + 1);
+                uint32_t q = h2_pack<FDT>(raw_elem<FDT>(raw, e0) * r, raw_elem<FDT>(raw, e1) * r);
+                if constexpr (CLAMP) q = h2_min<FDT>(h2_max<FDT>(q, lo2), hi2);
+                p[j] = q;
+            }
+            if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2) {
+                // F(192 + b) = 0x4340 + b (bf16), F(1536 + b) = 0x6600 + b (f16) for small b >= 0.
+                constexpr int BITS = kind_bits(KIND);
+                constexpr float BIAS = (float)(1 << (BITS - 1));
+                constexpr uint32_t HBITS = (FDT == QK_BF16) ? 0x43404340u : 0x66006600u;
+                constexpr uint32_t FLIP = (BITS == 4) ? 0x88888888u : 0xAAAAAAAAu;
+                const uint32_t magic = h2_const<FDT>(((FDT == QK_BF16) ? 192.0f : 1536.0f) + BIAS);
+                uint32_t kconst = 0, acc = 0;
+#pragma unroll
+                for (int j = 0; j < EPW / 2; ++j) {
+                    kconst += HBITS << (j * BITS);
+                    acc += h2_add<FDT>(p[j], magic) * (1u << (j * BITS));
+                }
+                outw[w] = (acc - kconst) ^ FLIP;
+            } else if constexpr (KIND == KIND_PACK8 || KIND == KIND_I8) {
+                if constexpr (FDT == QK_F16) {
+                    // low byte of each half = q + 128; p[0] = (e0, e2), p[1] = (e1, e3)
+                    const uint32_t magic = h2_const<FDT>(1536.0f + 128.0f);
+                    const uint32_t a = h2_add<FDT>(p[0], magic), b = h2_add<FDT>(p[1], magic);
+                    outw[w] = __byte_perm(a, b, 0x6240) ^ 0x80808080u;
+                } else {
+                    // bf16 cannot hold 9-bit integers: finish in f32.
+                    uint32_t b[4];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        b[2 * j] = __float_as_uint(bf16_lo_to_f32(p[j]) + QK_MAGIC);
+                        b[2 * j + 1] = __float_as_uint(bf16_hi_to_f32(p[j]) + QK_MAGIC);
+                    }
+                    const uint32_t l = __byte_perm(b[0], b[1], 0x0040);
+                    const uint32_t h = __byte_perm(b[2], b[3], 0x0040);
+                    outw[w] = __byte_perm(l, h, 0x5410);
+                }
+            } else {  // KIND_E2M1: p[j] = (e_2j, e_2j+1) -> byte j
+                const uint32_t magic = h2_const<FDT>((FDT == QK_BF16) ? 192.0f : 1536.0f);
+                uint32_t by[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t q = h2_sub<FDT>(h2_add<FDT>(p[j], magic), magic);   // round to integer
+                    q = (q & 0x7fff7fffu) | (p[j] & 0x80008000u);                // keep the sign of zero
+                    by[j] = cvt_e2m1x2(h_lo_to_f32<FDT>(q), h_hi_to_f32<FDT>(q));
+                }
+                const uint32_t l = __byte_perm(by[0], by[1], 0x0040);
+                const uint32_t h = __byte_perm(by[2], by[3], 0x0040);
+                outw[w] = __byte_perm(l, h, 0x5410);
+            }
+        }
+    }
+}
+
+// Whether the fused form must clamp: with scale = 2*absmax/(hi-lo) taken from the same data,
+// |x/s| <= (hi-lo)/2 * (1 + e) where e covers the narrowing of the scale to F and to the param
+// type.  For symmetric ranges and f32 params that never reaches hi + 0.5, except for 8-bit codes
+// of bf16 inputs (127 * (1 + 2^-9) narrows to 127.5, which rounds to 128).  Everything else
+// (the "F" ranges, whose positive bound is one short; half-precision params; given scales) clamps.
+__host__ __device__ constexpr bool need_clamp(int fdt, int kind, bool dyn, bool symmetric, int param)
+{
+    if (!dyn || !symmetric || param != QK_F32) return true;
+    if (kind == KIND_E4M3 || kind == KIND_E5M2) return true;
+    if (fdt == QK_BF16 && (kind == KIND_PACK8 || kind == KIND_I8)) return true;
+    return false;
+}
+
+// -------------------------------------------------------------------------------------
+// Loading / storing one unit.
+// -------------------------------------------------------------------------------------
+template <int UB> __device__ __forceinline__ void load_unit(uint32_t *raw, const char *p, bool aligned32)
+{
+    if constexpr (UB == 16) {
+        const Vec16 v = ldg128_stream(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) raw[i] = v.w[i];
+    } else {
+        if (aligned32) {
+#pragma unroll
+            for (int k = 0; k < UB / 32; ++k) {
+                const Vec32 v = ldg256_stream(p + 32 * k);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) raw[8 * k + i] = v.w[i];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < UB / 16; ++k) {
+                const Vec16 v = ldg128_stream(p + 16 * k);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) raw[4 * k + i] = v.w[i];
+            }
+        }
+    }
+}
+
+template <int OW> __device__ __forceinline__ void store_words(uint32_t *dst, const uint32_t *w, bool aligned32)
+{
+    if constexpr (OW == 1) {
+        stg32_stream(dst, w[0]);
+    } else if constexpr (OW == 2) {
+        stg64_stream(dst, w[0], w[1]);
+    } else if constexpr (OW == 4) {
+        stg128_stream(dst, Vec16{{w[0], w[1], w[2], w[3]}});
+    } else {
+        static_assert(OW == 8, "1, 2, 4 or 8 output words");
+        if (aligned32) {
+            stg256_stream(dst, Vec32{{w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]}});
+        } else {
+            stg128_stream(dst, Vec16{{w[0], w[1], w[2], w[3]}});
+            stg128_stream(dst + 4, Vec16{{w[4], w[5], w[6], w[7]}});
+        }
+    }
+}
+
 // -------------------------------------------------------------------------------------
 // The kernel.  DYN = true: scale from the block's own absmax (one pass, fused).
 // DYN = false: scale given (tensor of F, one per block) or derived from a device absmax.
 // -------------------------------------------------------------------------------------
-template <int FDT, int KIND, bool DYN>
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
 __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
 {
-    using UT = Unit<FDT, KIND>;
-    constexpr int U = UT::ELEMS;
-    constexpr int IN_BYTES = UT::IN_BYTES;
-    constexpr int OW = UT::OUT_WORDS;
-    constexpr int UNR = 64 / IN_BYTES;  // units in flight per thread (64 bytes of loads)
+    using UT = UnitT<FDT, KIND, UB>;
+    constexpr int RAW = UT::RAW;
+    constexpr int OW = UT::OW;
+    constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread
     using F = typename ElemOf<FDT>::type;
 
     const char *in = static_cast<const char *>(a.in);
@@ -216,11 +435,11 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
     const bool aligned32 = a.aligned32 != 0;
     const int lg = a.lg_units_per_block;
 
-    // Per tensor with a device absmax: derive the scale once per thread.
+    // Per tensor: one scale for the whole launch, derived once per thread.
     float tensor_scale = 0.0f;
     if constexpr (!DYN) {
         if (lg < 0) {
-            tensor_scale = a.absmax ? scale_from_absmax<FDT>(*a.absmax, a.range)
+            tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * (*a.absmax), a.range, a.inv_range))
                                     : static_cast<float>(static_cast<const F *>(a.scale_in)[0]);
         }
     }
@@ -228,38 +447,39 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < a.nunits;
          base += stride) {
-        RawUnit<IN_BYTES> raw[UNR];
+        uint32_t raw[UNR][RAW];
+        const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            load_unit<IN_BYTES>(raw[k], in + idx * IN_BYTES, idx < a.nunits, aligned32);
+            if (full || idx < a.nunits) {
+                load_unit<UB>(raw[k], in + idx * UB, aligned32);
+            } else {
+#pragma unroll
+                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+            }
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            const bool valid = idx < a.nunits;
-            float x[U];
-#pragma unroll
-            for (int v = 0; v < UT::IN_VEC16; ++v) widen16<FDT>(raw[k].v[v], x + v * FInfo<FDT>::PER16);
+            const bool valid = full || idx < a.nunits;
 
             float scale_f;
             if constexpr (DYN) {
-                float amax = 0.0f;
-#pragma unroll
-                for (int i = 0; i < U; ++i) amax = fmaxf(amax, fabsf(x[i]));
+                float amax = unit_absmax<FDT, RAW>(raw[k]);
                 // Blocks are aligned runs of 2^lg lanes; every lane of the warp takes part.
 #pragma unroll
                 for (int m = 1; m < 32; m <<= 1)
                     if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-                scale_f = scale_from_absmax<FDT>(amax, a.range);
+                scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
             } else {
                 scale_f = (lg < 0) ? tensor_scale
                                    : (valid ? static_cast<float>(static_cast<const F *>(a.scale_in)[idx >> lg]) : 1.0f);
             }
             // write_scale: the scale is cast to the param type, stored, and that value (cast
             // back to F) is the divisor (crates/cubek-quant/src/quantize.rs:83-98).
-            const float s_fs = round_to_dyn(a.param, scale_f);
-            const float s = round_to<FDT>(s_fs);
+            const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
+            const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
             if (valid) {
                 if (lg < 0) {
                     if (idx == 0) store_dyn(a.out_scale, a.param, 0, s_fs);
@@ -267,64 +487,60 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
                     store_dyn(a.out_scale, a.param, idx >> lg, s_fs);
                 }
             }
-            const bool fast = kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s);
             uint32_t w[OW];
-            quantize_unit<FDT, KIND, DYN>(x, s, a.lo, a.hi, fast, w);
-            if (valid) {
-                if constexpr (OW == 1) stg32_stream(out + idx, w[0]);
-                else stg64_stream(out + idx * 2, w[0], w[1]);
-            }
+            if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s))
+                quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], s, a.lo, a.hi, w);
+            else
+                quantize_unit_exact<FDT, KIND, UB>(raw[k], s, a.lo, a.hi, w);
+            if (valid) store_words<OW>(out + idx * OW, w, aligned32);
         }
     }
 }
 
 // -------------------------------------------------------------------------------------
 // Scales only (per block), for the two-call form: absmax over each block then the scale
-// formula, written as F.  Same unit/shuffle geometry as the fused kernel (KIND fixed to
-// the 16-byte unit).
+// formula, written as F.  16-byte chunks, blocks are aligned runs of 2^lg lanes.
 // -------------------------------------------------------------------------------------
 template <int FDT>
 __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void *scale_out, long long nchunks,
-                                                           int lg_chunks_per_block, float range)
+                                                           int lg_chunks_per_block, float range, float inv_range)
 {
     using F = typename ElemOf<FDT>::type;
-    constexpr int PER = FInfo<FDT>::PER16;
     constexpr int UNR = 4;
     const char *in = static_cast<const char *>(in_);
     const int lg = lg_chunks_per_block;
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
          base += stride) {
-        Vec16 raw[UNR];
+        uint32_t raw[UNR][4];
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            raw[k] = (idx < nchunks) ? ldg128_stream(in + idx * 16) : Vec16{{0u, 0u, 0u, 0u}};
+            if (idx < nchunks) {
+                load_unit<16>(raw[k], in + idx * 16, false);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) raw[k][i] = 0u;
+            }
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            float x[PER];
-            widen16<FDT>(raw[k], x);
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < PER; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            float amax = unit_absmax<FDT, 4>(raw[k]);
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1)
                 if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
             if (idx < nchunks && (idx & ((1ll << lg) - 1)) == 0)
-                static_cast<F *>(scale_out)[idx >> lg] = static_cast<F>(scale_from_absmax<FDT>(amax, range));
+                static_cast<F *>(scale_out)[idx >> lg] =
+                    static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
         }
     }
 }
 
 // Host-side launchers, one translation unit per float type.
-cudaError_t launch_quantize(int fdt, int kind, bool dyn, const QuantArgs &args, const LaunchCfg &cfg,
-                            cudaStream_t stream);
-cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg,
-                                float range, const LaunchCfg &cfg, cudaStream_t stream);
-
-// Elements per unit for (float type, kind), for the host-side geometry checks.
-int unit_elems(int fdt, int kind);
+cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+                            const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
+                                float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
 
 }  // namespace qk

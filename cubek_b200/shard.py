@@ -1,0 +1,97 @@
+"""Sharding of one tensor (or a set of tensors) over the GPUs of a node.
+
+The reference is single-device; this is the one data-parallel scheme the path needs.  A 2-D
+tensor is split into contiguous row ranges, one per rank.  Blocks lie along the last dim, so a
+block never straddles two shards and per-block quantization needs no communication at all.
+Per-tensor quantization needs one exchange: the shard-local absmax scalars are max-reduced
+(``all_reduce(MAX)`` over NCCL; exact and order independent because absmax >= 0), after which
+every rank derives the same scale bits and quantizes its own rows.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
+
+from . import quantize as _quantize
+from .scheme import ElemType, QuantScheme
+from .tensor import ComputeClient, TensorHandleRef
+
+
+@dataclass(frozen=True)
+class RowShard:
+    rank: int
+    row_start: int
+    rows: int
+
+
+def row_granularity(cols: int, elem: ElemType, scheme: QuantScheme) -> int:
+    """Smallest number of rows whose bytes are a multiple of 256 (keeps every shard base aligned
+    for 256-bit accesses on input, codes and scales) and whose elements fill whole stored items."""
+    nq = scheme.num_quants()
+    code_bytes_per_row_x8 = cols * scheme.size_bits_stored() // nq  # bits per row of codes
+    g = 1
+    for bytes_per_row in (cols * elem.size, max(code_bytes_per_row_x8 // 8, 1)):
+        need = 256 // math.gcd(256, bytes_per_row)
+        g = g * need // math.gcd(g, need)
+    return g
+
+
+def plan_rows(rows: int, cols: int, world: int, elem: ElemType, scheme: QuantScheme) -> List[RowShard]:
+    """Contiguous, non-overlapping row ranges covering ``rows``; every range but the last is a
+    multiple of ``row_granularity`` and ranges differ by at most one granule."""
+    if world < 1:
+        raise ValueError("world must be >= 1")
+    if cols % scheme.num_quants():
+        raise ValueError("last dim must be a multiple of num_quants")
+    if not scheme.level.is_tensor:
+        blk = scheme.level.block_size.to_dim_vec(2)
+        if blk[0] != 1 or cols % blk[1]:
+            raise ValueError("row sharding needs blocks along the last dim that divide it")
+    g = row_granularity(cols, elem, scheme)
+    granules = -(-rows // g)
+    base, extra = divmod(granules, world)
+    shards, start = [], 0
+    for r in range(world):
+        n = (base + (1 if r < extra else 0)) * g
+        n = max(0, min(n, rows - start))
+        shards.append(RowShard(r, start, n))
+        start += n
+    assert start == rows
+    return shards
+
+
+def assign_round_robin(sizes: Sequence[int], world: int) -> List[List[int]]:
+    """Whole-tensor placement for weight sets: greedy longest-first onto the least loaded rank.
+    Returns, per rank, the indices of the tensors it owns."""
+    load = [0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for i in sorted(range(len(sizes)), key=lambda i: -sizes[i]):
+        r = min(range(world), key=lambda r: (load[r], r))
+        owned[r].append(i)
+        load[r] += sizes[i]
+    for o in owned:
+        o.sort()
+    return owned
+
+
+def allreduce_absmax(absmax, group=None) -> None:
+    """In-place MAX all-reduce of a tensor of absmax scalars (one per row-sharded tensor)."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=group)
+
+
+def quantize_per_tensor_sharded(client: ComputeClient, shard: TensorHandleRef, output: TensorHandleRef,
+                                out_scale: TensorHandleRef, absmax, scheme: QuantScheme, elem: ElemType,
+                                group=None) -> None:
+    """Per-tensor quantization of this rank's rows of a row-sharded tensor.
+
+    ``absmax`` is a 1-element float32 torch tensor on the shard's device.  The three steps run on
+    the current stream with no host synchronisation: local absmax, all-reduce(MAX), quantize with
+    the scale derived on the device from the reduced value.
+    """
+    _quantize.absmax(client, shard, elem, absmax.data_ptr())
+    allreduce_absmax(absmax, group)
+    _quantize.launch_from_absmax(client, shard, output, out_scale, absmax.data_ptr(), scheme, elem)

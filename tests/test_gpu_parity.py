@@ -1,0 +1,198 @@
+"""CUDA kernels against the oracle, bit for bit, through the C ABI: every value x store x float
+type x level, on random and adversarial inputs; the streaming kernels, their reference-arithmetic
+route and the layout-general kernels must all give the same bits."""
+import itertools
+
+import numpy as np
+import pytest
+
+from cubek_b200 import ElemType, QuantLevel, QuantParam, QuantScheme, QuantStore, QuantValue
+from cubek_b200 import _ffi
+from oracle import oracle as O
+from tests._cases import FLOATS, adversarial_tensor, all_value_stores, random_tensor, scheme_grid, scheme_id
+from tests._util import (assert_bits_equal, gpu_compute_scales, gpu_dequantize, gpu_quantize, gpu_quantize_dynamic)
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = (64, 256)
+
+
+def full_check(x, scheme, F):
+    scale = O.compute_scales(x, scheme)
+    codes, out_scale = O.quantize(x, scale, scheme)
+    restored = O.dequantize(codes, out_scale, scheme, F)
+    assert_bits_equal(gpu_compute_scales(x, scheme), scale, "scale")
+    g_codes, g_out_scale = gpu_quantize(x, scale, scheme)
+    assert_bits_equal(g_codes, codes, "codes")
+    assert_bits_equal(g_out_scale, out_scale, "out_scale")
+    d_codes, d_out_scale = gpu_quantize_dynamic(x, scheme)
+    assert_bits_equal(d_codes, codes, "codes (fused)")
+    assert_bits_equal(d_out_scale, out_scale, "out_scale (fused)")
+    assert_bits_equal(gpu_dequantize(codes, out_scale, scheme, F), restored, "restored")
+
+
+@pytest.fixture
+def tuning():
+    yield lambda key, value: _ffi.lib().qk_set_tuning(key, value)
+    for key in (_ffi.TUNE_FORCE_EXACT, _ffi.TUNE_FORCE_GENERAL):
+        _ffi.lib().qk_set_tuning(key, 0)
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("scheme", list(scheme_grid(SHAPE)), ids=scheme_id)
+def test_streaming_kernels(fname, scheme):
+    F = FLOATS[fname]
+    full_check(random_tensor(SHAPE, F, 1), scheme, F)
+    full_check(adversarial_tensor(SHAPE, F, scheme, 2), scheme, F)
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("scheme", list(scheme_grid(SHAPE)), ids=scheme_id)
+def test_reference_arithmetic_route(fname, scheme, tuning):
+    tuning(_ffi.TUNE_FORCE_EXACT, 1)
+    F = FLOATS[fname]
+    full_check(adversarial_tensor(SHAPE, F, scheme, 3), scheme, F)
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("scheme", list(scheme_grid(SHAPE)), ids=scheme_id)
+def test_layout_general_kernels(fname, scheme, tuning):
+    tuning(_ffi.TUNE_FORCE_GENERAL, 1)
+    F = FLOATS[fname]
+    full_check(adversarial_tensor(SHAPE, F, scheme, 4), scheme, F)
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("param", [QuantParam.F16, QuantParam.BF16])
+@pytest.mark.parametrize("value,store", [(QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4F, QuantStore.U32),
+                                         (QuantValue.E2M1, QuantStore.Native), (QuantValue.Q8F, QuantStore.Native)])
+def test_half_precision_params(fname, param, value, store):
+    F = FLOATS[fname]
+    for level in (QuantLevel.Tensor, QuantLevel.block([32])):
+        scheme = QuantScheme(value=value, store=store, param=param, level=level)
+        full_check(random_tensor(SHAPE, F, 5), scheme, F)
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("shape,block", [((6, 10, 48), [2, 16]), ((5, 96), [24]), ((7, 3, 40), [3, 1, 8]),
+                                         ((33, 24), [8]), ((4, 4, 4, 16), [2, 2, 16])])
+def test_nd_blocks_and_ragged_shapes(fname, shape, block):
+    """Blocks over several dims (clipped at the edges), block sizes that are not powers of two
+    and sizes that do not fill whole units all go through the layout-general kernels."""
+    F = FLOATS[fname]
+    for value, store in ((QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4S, QuantStore.U32),
+                         (QuantValue.Q8S, QuantStore.Native), (QuantValue.E2M1, QuantStore.Native)):
+        scheme = QuantScheme(value=value, store=store, level=QuantLevel.block(block))
+        if block[-1] % scheme.num_quants() or shape[-1] % scheme.num_quants():
+            continue
+        full_check(random_tensor(shape, F, 6), scheme, F)
+
+
+def test_strided_scales_are_honoured():
+    """scale / out_scale / params may be views with their own strides (the reference builds its
+    scales layout from the handle's strides, layout/scales.rs:233-234)."""
+    import torch
+    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
+    from tests._util import to_device, to_numpy
+
+    F = np.float32
+    scheme = QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([32]))
+    x = random_tensor(SHAPE, F, 7)
+    scale = O.compute_scales(x, scheme)
+    codes, out_scale = O.quantize(x, scale, scheme)
+    dx = to_device(x)
+    wide = torch.zeros((SHAPE[0], 2 * scale.shape[1]), device="cuda")
+    dscale = wide[:, ::2]
+    dscale.copy_(torch.from_numpy(scale))
+    wide_out = torch.full((SHAPE[0], 3 * scale.shape[1]), -1.0, device="cuda")
+    dos = wide_out[:, 1::3]
+    dq = torch.zeros(codes.shape, dtype=torch.int32, device="cuda")
+    client = ComputeClient.current()
+    quantize.launch_ref(client, TensorHandleRef.from_torch(dx), TensorHandleRef.from_torch(dq),
+                        TensorHandleRef.from_torch(dscale), TensorHandleRef.from_torch(dos), scheme, ElemType.F32)
+    do = torch.zeros(SHAPE, device="cuda")
+    dequantize.launch_ref(client, TensorHandleRef.from_torch(dq), TensorHandleRef.from_torch(do),
+                          TensorHandleRef.from_torch(dos), scheme, ElemType.F32)
+    torch.cuda.synchronize()
+    assert_bits_equal(to_numpy(dq, np.uint32), codes, "codes")
+    assert_bits_equal(dos.contiguous().cpu().numpy(), out_scale, "out_scale")
+    assert float(wide_out[:, 0::3].max()) == -1.0 and float(wide_out[:, 2::3].max()) == -1.0
+    assert_bits_equal(do.cpu().numpy(), O.dequantize(codes, out_scale, scheme, F), "restored")
+
+
+def test_e2m1_nibble_order_and_code_table():
+    """All 16 fp4 codes through the native dequantize, and the integers -6..6 through the native
+    quantize: even element in the low nibble, 5 -> 4."""
+    scheme = QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native)
+    one = np.array([1.0], dtype=np.float32)
+    codes = np.array([[lo | (hi << 4) for lo, hi in zip(range(0, 16, 2), range(1, 16, 2))]], dtype=np.uint8)
+    got = gpu_dequantize(codes, one, scheme, np.float32)
+    want = np.array([[0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6]], dtype=np.float32)
+    assert np.array_equal(got, want)
+    assert_bits_equal(got, O.dequantize(codes, one, scheme, np.float32), "e2m1 table")
+    x = np.array([[-6, -5, -4, -3, -2, -1, 0, 1, 2, 3, 4, 5, 6, 7, 0.4, 2.5]], dtype=np.float32)
+    q, _ = gpu_quantize(x, one, scheme)
+    oq, _ = O.quantize(x, one, scheme)
+    assert_bits_equal(q, oq, "e2m1 codes")
+    back = gpu_dequantize(q, one, scheme, np.float32)
+    assert back.reshape(-1).tolist() == [-6, -4, -4, -3, -2, -1, 0, 1, 2, 3, 4, 4, 6, 6, 0, 2]
+
+
+@pytest.mark.parametrize("fname", ["f16", "bf16"])
+@pytest.mark.parametrize("value,store", [(QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4S, QuantStore.U32),
+                                         (QuantValue.Q2F, QuantStore.U32), (QuantValue.E2M1, QuantStore.Native),
+                                         (QuantValue.E4M3, QuantStore.Native)])
+def test_every_finite_half_value_as_input(fname, value, store):
+    """All 2^16 bit patterns of the input type (non-finite ones replaced by 0) against several
+    scales: exercises every rounding boundary of the narrowed quotient."""
+    F = FLOATS[fname]
+    bits = np.arange(65536, dtype=np.uint16)
+    x = bits.view(F).copy()
+    x[~np.isfinite(x.astype(np.float32))] = 0
+    x = x.reshape(256, 256)
+    scheme = QuantScheme(value=value, store=store)
+    for s in (1.0, 0.37109375, 3.0, 0.0078125, 119.5):
+        scale = np.array([s], dtype=F)
+        codes, out_scale = O.quantize(x, scale, scheme)
+        g_codes, g_out_scale = gpu_quantize(x, scale, scheme)
+        assert_bits_equal(g_codes, codes, f"codes at scale {s}")
+        assert_bits_equal(g_out_scale, out_scale, "out_scale")
+    codes, out_scale = O.quantize_dynamic(x, scheme)
+    assert_bits_equal(gpu_dequantize(codes, out_scale, scheme, F), O.dequantize(codes, out_scale, scheme, F), "restored")
+
+
+@pytest.mark.parametrize("fname,kind,value,store,level", [
+    ("f32", "normal", QuantValue.Q8S, QuantStore.U32, QuantLevel.Tensor),
+    ("bf16", "outliers", QuantValue.Q4S, QuantStore.U32, QuantLevel.block([32])),
+    ("f16", "rowscaled", QuantValue.E2M1, QuantStore.Native, QuantLevel.block([16])),
+    ("f16", "rowscaled", QuantValue.E2M1, QuantStore.Native, QuantLevel.block([32])),
+    ("f32", "uniform", QuantValue.Q2S, QuantStore.U32, QuantLevel.block([64])),
+    ("bf16", "normal", QuantValue.Q8S, QuantStore.U32, QuantLevel.block([128])),
+    ("bf16", "normal", QuantValue.Q8S, QuantStore.U32, QuantLevel.Tensor),
+])
+def test_benchmark_configurations_medium(fname, kind, value, store, level):
+    """The benchmark schemes and distributions on 1024 x 4096 tensors: large enough that every
+    CTA loops and the grid cap is reached, small enough for the oracle."""
+    F = FLOATS[fname]
+    scheme = QuantScheme(value=value, store=store, level=level)
+    full_check(random_tensor((1024, 4096), F, 8, kind), scheme, F)
+
+
+def test_scale_extremes_take_the_reference_route():
+    """Scales outside the shortcut window (zero, subnormal, huge, negative) and quotients that
+    overflow must match the oracle too."""
+    scheme = QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([32]))
+    x = random_tensor((8, 256), np.float32, 9)
+    x[0] *= 1e30
+    x[1] *= 1e-30
+    x[2] *= 1e-42
+    scale = O.compute_scales(x, scheme)
+    scale[3] = 1e-38
+    scale[4] = -0.01
+    scale[5] = 3e38
+    scale[6] = 1e-45
+    codes, out_scale = O.quantize(x, scale, scheme)
+    g_codes, g_out_scale = gpu_quantize(x, scale, scheme)
+    assert_bits_equal(g_codes, codes, "codes")
+    d_codes, _ = gpu_quantize_dynamic(x, scheme)
+    assert_bits_equal(d_codes, O.quantize_dynamic(x, scheme)[0], "codes (fused)")
