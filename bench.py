@@ -58,58 +58,58 @@ def algorithmic_bytes(workload, rows=None):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons (read-only NVML queries) while the timed region
+    runs.  The timed region lasts milliseconds, so a thread polls NVML every ~2 ms instead of
+    going through nvidia-smi's 100 ms loop."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+        self.samples, self.reason_bits, self.max_mhz = [], 0, None
+        self._stop = threading.Event()
         self.thread = None
+        self.nvml = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu_index
+            if visible:
+                try:
+                    index = int(visible.split(",")[self.gpu_index])
+                except ValueError:
+                    pass
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread = threading.Thread(target=self._poll, daemon=True)
         self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _poll(self):
+        nv = self.nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def stop(self):
-        if not self.proc:
+        if not self.nvml:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -246,19 +246,18 @@ def run_gpu(args, workload):
     H = TensorHandleRef.from_torch
     hx, hc, hs, ho, hws = [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], [H(t) for t in outs], H(ws)
     client = ComputeClient.current()
+    # argument marshalling is done once; a step is 2*B calls straight into the C ABI
+    quant_calls = [quantize.PreparedDynamic(client, hx[i], hc[i], hs[i], scheme, elem, hws) for i in range(B)]
+    dequant_calls = [dequantize.Prepared(client, hc[i], ho[i], hs[i], scheme, elem) for i in range(B)]
 
-    def step(events=None):
+    def step():
         for i in range(B):
-            if events is not None:
-                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-                e0.record()
-            quantize.launch_dynamic(client, hx[i], hc[i], hs[i], scheme, elem, hws)
-            if events is not None:
-                e1.record()
-            dequantize.launch_ref(client, hc[i], ho[i], hs[i], scheme, elem)
-            if events is not None:
-                e2.record()
-                events.append((e0, e1, e2))
+            quant_calls[i]()
+            dequant_calls[i]()
+
+    def only(calls):
+        for c in calls:
+            c()
 
     def barrier():
         if world > 1:
@@ -272,18 +271,32 @@ def run_gpu(args, workload):
     if rank == 0:
         sampler.start()
     launches_before = lib.qk_launch_count()
-    events = []
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        step(events)
+        step()
     stop.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     launches = lib.qk_launch_count() - launches_before
     elapsed_ms = start.elapsed_time(stop)
-    q_ms = [a.elapsed_time(b) for a, b, _ in events]
-    d_ms = [b.elapsed_time(c_) for _, b, c_ in events]
+
+    # Per-kernel durations for the roofline: the same launches, one kind at a time, again
+    # bracketed by events on the launch stream (events between every pair of kernels would
+    # serialise launch and execution and time the gap, not the kernel).
+    def time_kind(calls):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        only(calls)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(args.steps):
+            only(calls)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (args.steps * len(calls))
+
+    q_avg = time_kind(quant_calls)
+    d_avg = time_kind(dequant_calls)
+    clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -305,7 +318,6 @@ def run_gpu(args, workload):
     total_bytes = (q_bytes + d_bytes) * B * args.steps * world
     value = total_bytes / (elapsed_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
-    q_avg, d_avg = sum(q_ms) / len(q_ms), sum(d_ms) / len(d_ms)
     kernels = {
         "quantize_dynamic": {"avg_ms": round(q_avg, 5), "bytes": q_bytes, "gbs": round(q_bytes / q_avg / 1e6, 1)},
         "dequantize": {"avg_ms": round(d_avg, 5), "bytes": d_bytes, "gbs": round(d_bytes / d_avg / 1e6, 1)},
@@ -400,7 +412,7 @@ def run_e2e(args, workload, dev, local_rank, rank, world, xs):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--batch", type=int, default=8, help="distinct tensors per step")

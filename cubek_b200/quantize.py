@@ -60,3 +60,26 @@ def launch_from_absmax(client: ComputeClient, input: TensorHandleRef, output: Te
     ti, to, tos = _ffi.c_tensors(input, output, out_scale)
     _ffi.check(_ffi.lib().qk_quantize_from_absmax(ti.ref(), to.ref(), tos.ref(), absmax_ptr,
                                                   _ffi.c_scheme(scheme), int(input_elem), client.stream))
+
+
+class PreparedDynamic:
+    """``launch_dynamic`` with the argument marshalling done once.
+
+    Building the C structs costs more host time than a small tensor takes on the device; callers
+    that quantize the same buffers repeatedly (or loop over many tensors) prepare the call once
+    and invoke it with no Python-side allocation."""
+
+    def __init__(self, client: ComputeClient, input: TensorHandleRef, output: TensorHandleRef,
+                 out_scale: TensorHandleRef, scheme: QuantScheme, input_elem: ElemType,
+                 workspace: TensorHandleRef | None = None):
+        self._keep = _ffi.c_tensors(input, output, out_scale)
+        self._scheme = _ffi.c_scheme(scheme)
+        ws_ptr, ws_bytes = (workspace.handle, workspace.shape[0] * workspace.elem_size) if workspace else (None, 0)
+        self._args = (self._keep[0].ref(), self._keep[1].ref(), self._keep[2].ref(), self._scheme, int(input_elem),
+                      ws_ptr, ws_bytes, client.stream)
+        self._fn = _ffi.lib().qk_quantize_dynamic
+
+    def __call__(self) -> None:
+        status = self._fn(*self._args)
+        if status:
+            _ffi.check(status)
