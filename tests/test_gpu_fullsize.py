@@ -1,0 +1,113 @@
+"""The benchmark configurations at their full sizes.  The oracle is too slow for whole tensors of
+this size, so parity is established through (1) bit-exact comparison with the oracle on a random
+sample of whole rows, (2) size-independent properties: the fused one-pass result equals the
+two-call result, the round-trip error is within half a quantization step of every element, and
+re-quantizing the restored tensor with the same scales reproduces the codes (idempotence)."""
+import numpy as np
+import pytest
+import torch
+
+from cubek_b200 import ComputeClient, ElemType, QuantParam, TensorHandleRef, dequantize, quantize
+from cubek_b200.synthetic import TORCH_DTYPE, WORKLOADS, generate
+from oracle import oracle as O
+from tests._util import NP_FLOAT, assert_bits_equal, to_numpy
+
+pytestmark = pytest.mark.gpu
+H = TensorHandleRef.from_torch
+
+FULL = ["q8_tensor_f32_4096x4096", "q4_block32_bf16_14336x4096", "e2m1_block16_f16_8192x4096",
+        "e2m1_block32_f16_8192x4096", "q2_block64_f32_65536x4096", "q8_block128_bf16_14336x4096",
+        "q8_tensor_bf16_14336x4096"]
+
+
+def run_full(w, x):
+    s, elem = w.scheme, w.elem
+    client = ComputeClient.current()
+    code_t = torch.int32 if s.store.name == "U32" else torch.uint8
+    codes = torch.empty(s.packed_shape(x.shape), dtype=code_t, device="cuda")
+    out_scale = torch.empty(s.scales_shape(x.shape), dtype=torch.float32, device="cuda")
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    quantize.launch_dynamic(client, H(x), H(codes), H(out_scale), s, elem, H(ws))
+    restored = torch.empty_like(x)
+    dequantize.launch_ref(client, H(codes), H(restored), H(out_scale), s, elem)
+    torch.cuda.synchronize()
+    return codes, out_scale, restored
+
+
+@pytest.mark.parametrize("name", FULL)
+def test_full_size_configuration(name):
+    w = WORKLOADS[name]
+    s, elem = w.scheme, w.elem
+    F = NP_FLOAT[elem]
+    x = generate(w, "cuda")
+    rows, cols = x.shape
+    client = ComputeClient.current()
+    codes, out_scale, restored = run_full(w, x)
+
+    # (a) the two-call form gives the same bits as the fused one
+    scale = torch.empty(s.scales_shape(x.shape), dtype=TORCH_DTYPE[elem], device="cuda")
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    quantize.compute_scales(client, H(x), H(scale), s, elem, H(ws))
+    codes2 = torch.empty_like(codes)
+    out_scale2 = torch.empty_like(out_scale)
+    quantize.launch_ref(client, H(x), H(codes2), H(scale), H(out_scale2), s, elem)
+    torch.cuda.synchronize()
+    assert torch.equal(codes, codes2) and torch.equal(out_scale.view(torch.int32), out_scale2.view(torch.int32))
+
+    # (b) round trip within half a step (plus the narrowing of the product for 16-bit types)
+    if s.level.is_tensor:
+        step = out_scale.reshape(1, 1).expand(rows, cols)
+    else:
+        step = out_scale.repeat_interleave(s.level.block_size.as_slice()[-1], dim=1)
+    err = (restored.float() - x.float()).abs()
+    if s.value.name == "E2M1":
+        bound = step * 1.5                     # round to an integer (0.5), then 5 -> 4 on the fp4 grid (1.0)
+    else:
+        bound = step * 0.5
+    # The quotient and the product are rounded to F: relative 2^-24 (the reference tests allow
+    # 1e-4), 2^-11 for f16, 2^-8 for bf16, once on the way in (can move the code by one) and once out.
+    rel = {ElemType.F32: 1e-4, ElemType.F16: 2.0 ** -9, ElemType.BF16: 2.0 ** -6}[elem]
+    assert bool((err <= bound * (1 + 1e-4) + x.float().abs() * rel + 1e-30).all())
+
+    # (c) idempotence: quantizing the restored tensor with the same scales gives the same codes
+    if s.value.name != "E2M1":
+        codes3 = torch.empty_like(codes)
+        out_scale3 = torch.empty_like(out_scale)
+        quantize.launch_ref(client, H(restored), H(codes3), H(out_scale.to(TORCH_DTYPE[elem])), H(out_scale3), s, elem)
+        torch.cuda.synchronize()
+        if elem == ElemType.F32:
+            assert torch.equal(codes, codes3)
+
+    # (d) bit-exact against the oracle on 48 whole rows (per block) / on the whole tensor's scale
+    g = torch.Generator().manual_seed(7)
+    pick = torch.sort(torch.randperm(rows, generator=g)[:48]).values
+    if s.level.is_tensor:
+        # the oracle needs the global scale: take it from the device result after checking it
+        xs = to_numpy(x[pick.cuda()].contiguous(), F)
+        amax = float(x.float().abs().max())
+        lo, hi = s.value.range()
+        want_scale = np.array([np.float32(2) * np.float32(amax) / np.float32(hi - lo)], dtype=np.float32).astype(F)
+        o_codes, o_scale = O.quantize(xs, want_scale, s)
+        assert_bits_equal(to_numpy(out_scale, np.float32), o_scale, "scale")
+    else:
+        xs = to_numpy(x[pick.cuda()].contiguous(), F)
+        o_codes, o_scale = O.quantize_dynamic(xs, s)
+        assert_bits_equal(to_numpy(out_scale[pick.cuda()].contiguous(), np.float32), o_scale, "scales")
+    assert_bits_equal(to_numpy(codes[pick.cuda()].contiguous(), o_codes.dtype), o_codes, "codes")
+    o_restored = O.dequantize(o_codes, o_scale, s, F)
+    assert_bits_equal(to_numpy(restored[pick.cuda()].contiguous(), F), o_restored, "restored")
+
+
+def test_embedding_sized_tensor_q8_block128():
+    """The largest single tensor of the Llama-3-8B-shaped set (128256 x 4096 bf16, 1 GB)."""
+    from dataclasses import replace
+
+    w = replace(WORKLOADS["q8_block128_bf16_14336x4096"], shape=(128256, 4096))
+    x = generate(w, "cuda")
+    codes, out_scale, restored = run_full(w, x)
+    F = NP_FLOAT[w.elem]
+    pick = torch.tensor([0, 1, 777, 64000, 128255], device="cuda")
+    xs = to_numpy(x[pick].contiguous(), F)
+    o_codes, o_scale = O.quantize_dynamic(xs, w.scheme)
+    assert_bits_equal(to_numpy(codes[pick].contiguous(), np.uint32), o_codes, "codes")
+    assert_bits_equal(to_numpy(restored[pick].contiguous(), F), O.dequantize(o_codes, o_scale, w.scheme, F), "restored")

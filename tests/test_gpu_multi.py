@@ -1,0 +1,75 @@
+"""Multi-GPU data path on real devices (needs >= 2 GPUs): one process per GPU over NCCL.
+Row shards quantized independently concatenate to the single-GPU result bit for bit, and the
+per-tensor path (absmax -> all-reduce(MAX) -> quantize) gives every rank the single-GPU scale."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    from cubek_b200 import (ComputeClient, ElemType, QuantLevel, QuantScheme, QuantStore, QuantValue, TensorHandleRef,
+                            quantize)
+    from cubek_b200.shard import plan_rows, quantize_per_tensor_sharded
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        H = TensorHandleRef.from_torch
+        rows, cols = 4096, 4096
+        g = torch.Generator(device="cuda").manual_seed(99)           # same tensor on every rank
+        full = torch.randn((rows, cols), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        full[rows - 1, cols - 1] = 9.5                                # global absmax in the last shard
+        client = ComputeClient.current()
+        ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+        results = {}
+        for name, scheme in (("tensor", QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32)),
+                             ("block", QuantScheme(value=QuantValue.Q4S, store=QuantStore.U32,
+                                                   level=QuantLevel.block([32])))):
+            # single-device result
+            codes_full = torch.empty(scheme.packed_shape((rows, cols)), dtype=torch.int32, device="cuda")
+            scale_full = torch.empty(scheme.scales_shape((rows, cols)), dtype=torch.float32, device="cuda")
+            quantize.launch_dynamic(client, H(full), H(codes_full), H(scale_full), scheme, ElemType.BF16, H(ws))
+            # this rank's shard
+            sh = plan_rows(rows, cols, world, ElemType.BF16, scheme)[rank]
+            mine = full[sh.row_start: sh.row_start + sh.rows]
+            codes = torch.empty(scheme.packed_shape((sh.rows, cols)), dtype=torch.int32, device="cuda")
+            scale = torch.empty(scheme.scales_shape((sh.rows, cols)), dtype=torch.float32, device="cuda")
+            if scheme.level.is_tensor:
+                absmax = torch.zeros(1, dtype=torch.float32, device="cuda")
+                quantize_per_tensor_sharded(client, H(mine), H(codes), H(scale), absmax, scheme, ElemType.BF16)
+                torch.cuda.synchronize()
+                assert torch.equal(scale.view(torch.int32), scale_full.view(torch.int32)), "scale differs"
+            else:
+                quantize.launch_dynamic(client, H(mine), H(codes), H(scale), scheme, ElemType.BF16, H(ws))
+                torch.cuda.synchronize()
+                assert torch.equal(scale, scale_full[sh.row_start: sh.row_start + sh.rows])
+            assert torch.equal(codes, codes_full[sh.row_start: sh.row_start + sh.rows]), f"{name} codes differ"
+            results[name] = True
+        open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_row_shards_match_single_gpu(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 8)
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
