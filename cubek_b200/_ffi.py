@@ -70,6 +70,8 @@ _SIGNATURES = {
                                                                C.c_size_t, C.c_void_p]),
     "qk_quantize_dynamic": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                                  C.c_size_t, C.c_void_p]),
+    "qk_quantize_dynamic_noalloc": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p]),
+    "qk_noalloc_scratch_bytes": (C.c_size_t, []),
     "qk_absmax_f32": (C.c_int, [C.POINTER(QkTensor), C.c_int, C.c_void_p, C.c_void_p]),
     "qk_quantize_from_absmax": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.c_void_p, C.POINTER(QkScheme), C.c_int,
                                                                      C.c_void_p]),

@@ -148,6 +148,38 @@ int qk_quantize_from_absmax(const QkTensor *input, const QkTensor *output, const
  * NCCL (libnccl.so.2 already loaded in the process, else dlopen).  `comm` is an ncclComm_t. */
 int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream);
 
+/*
+ * qk_quantize_dynamic for callers that cannot allocate.  (No counterpart in the reference, whose
+ * callers always own a memory pool.)
+ *
+ * Who this is for: code that is handed finished input and output buffers but has no allocator of
+ * its own and may not touch the CUDA one - a plug-in running inside a host application that has
+ * already carved up the whole device between its components, a callback on a latency-critical
+ * thread where the device-wide synchronisation hidden in cudaMalloc / cudaFree is not acceptable,
+ * or a process whose memory budget is fixed and audited at start-up.  Such a caller has nowhere
+ * to get the workspace that qk_quantize_dynamic asks for.
+ *
+ * Here the scratch lives in a fixed array inside the library image: qk_noalloc_scratch_bytes()
+ * bytes (64 KiB) per GPU that loads the library, held until the process exits.  The call performs
+ * no cudaMalloc, cudaFree or other allocating call; input, output and out_scale are still the
+ * caller's buffers.  Results are bit-identical to qk_quantize_dynamic.
+ *
+ *  - Limit: per-tensor schemes and the streaming per-block layouts work at any tensor size (they
+ *    need at most one cell of scratch).  Layouts that take the general kernels (N-d blocks, block
+ *    sizes that are not a power of two, ragged sizes) stage one input-typed scale per block in the
+ *    array; if those do not fit (256 bytes + scales > 64 KiB) the call returns QK_ERR_TOO_LARGE
+ *    and launches nothing.
+ *  - First call on a device: looks up the array's device address (once per device, with that
+ *    device current).  Make that first call during set-up, before any CUDA stream capture begins.
+ *  - Sharing: every call on a GPU uses the same array, on whatever stream it is given.  Two calls
+ *    whose kernels can overlap on the GPU (different streams, no dependency between them) race on
+ *    it; order them with events or keep them on one stream.  The array keeps the previous call's
+ *    contents; the part that must start at zero is cleared by each call.
+ */
+int qk_quantize_dynamic_noalloc(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                                const QkScheme *scheme, int input_dtype, void *stream);
+size_t qk_noalloc_scratch_bytes(void);
+
 /* Device workspace needed by the per-tensor paths (a fixed, small size). */
 size_t qk_workspace_bytes(void);
 /* Workspace for qk_quantize_dynamic on this input: qk_workspace_bytes() plus, per block, room
