@@ -238,6 +238,8 @@ def run_gpu(args, workload):
         dist.init_process_group("nccl", device_id=dev)
 
     lib = _ffi.lib()      # raises if the CUDA library is missing: there is no fallback
+    if args.no_pdl:
+        lib.qk_set_tuning(_ffi.TUNE_PDL, 0)
     scheme, elem = workload.scheme, workload.elem
     r, c = workload.shape
     B = args.batch
@@ -420,6 +422,7 @@ def main():
     ap.add_argument("--e2e-batch", type=int, default=2)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

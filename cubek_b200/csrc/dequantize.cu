@@ -21,8 +21,7 @@ static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cud
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    dequantize_kernel<FDT, KIND, OB><<<(int)need, threads, 0, stream>>>(args);
-    return cudaGetLastError();
+    return launch_kernel(dequantize_kernel<FDT, KIND, OB>, (int)need, threads, stream, cfg.pdl != 0, args);
 }
 
 template <int FDT, int KIND>

@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     char *out = static_cast<char *>(a.out);
     const int lg = a.lg_units_per_block;
     const bool aligned32 = a.aligned32 != 0;
+    pdl_entry();
     float tensor_scale = 0.0f;
     if (lg < 0) tensor_scale = round_to<FDT>(load_dyn(a.params, a.param, 0));
 

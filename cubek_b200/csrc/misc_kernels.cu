@@ -25,6 +25,7 @@ __global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long 
     const char *in = static_cast<const char *>(in_);
     const long long nchunks = n / PER;
     float amax = 0.0f;
+    pdl_entry();
 
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
@@ -100,12 +101,12 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
     }
     const int per = (fdt == QK_F32) ? 4 : 8;
     const int grid = grid_for(n / per + 1, threads * 4, cfg);
+    const bool pdl = cfg.pdl != 0;
     switch (fdt) {
-    case QK_F32: absmax_kernel<QK_F32><<<grid, threads, 0, stream>>>(in, n, cell); break;
-    case QK_F16: absmax_kernel<QK_F16><<<grid, threads, 0, stream>>>(in, n, cell); break;
-    default: absmax_kernel<QK_BF16><<<grid, threads, 0, stream>>>(in, n, cell); break;
+    case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell);
+    case QK_F16: return launch_kernel(absmax_kernel<QK_F16>, grid, threads, stream, pdl, in, n, cell);
+    default: return launch_kernel(absmax_kernel<QK_BF16>, grid, threads, stream, pdl, in, n, cell);
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,

@@ -27,8 +27,7 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    quantize_kernel<FDT, KIND, UB, DYN, CLAMP><<<(int)need, threads, 0, stream>>>(args);
-    return cudaGetLastError();
+    return launch_kernel(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, (int)need, threads, stream, cfg.pdl != 0, args);
 }
 
 template <int FDT, int KIND, int UB>
@@ -77,8 +76,8 @@ static cudaError_t launch_block_scales_t(const void *in, void *scale_out, long l
     const long long cap = (long long)cfg.sm_count * occ;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    block_scales_kernel<FDT><<<(int)need, threads, 0, stream>>>(in, scale_out, nchunks, lg, range, inv_range);
-    return cudaGetLastError();
+    return launch_kernel(block_scales_kernel<FDT>, (int)need, threads, stream, cfg.pdl != 0, in, scale_out, nchunks, lg,
+                         range, inv_range);
 }
 
 }  // namespace qk

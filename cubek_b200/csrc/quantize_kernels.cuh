@@ -434,6 +434,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
     uint32_t *out = static_cast<uint32_t *>(a.out);
     const bool aligned32 = a.aligned32 != 0;
     const int lg = a.lg_units_per_block;
+    pdl_entry();
 
     // Per tensor: one scale for the whole launch, derived once per thread.
     float tensor_scale = 0.0f;
@@ -509,6 +510,7 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
     constexpr int UNR = 4;
     const char *in = static_cast<const char *>(in_);
     const int lg = lg_chunks_per_block;
+    pdl_entry();
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
          base += stride) {
