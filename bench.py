@@ -215,6 +215,7 @@ def config_of(workload, args, rows=None):
             "value": s.value.name, "store": s.store.name, "param": s.param.name,
             "level": "tensor" if s.level.is_tensor else f"block{list(s.level.block_size.as_slice())}",
             "distribution": workload.distribution,
+            "api": "qk_quantize_dynamic_batch + qk_dequantize_batch (one launch per batch each)",
             "l2": "batch of distinct tensors larger than L2; no flush needed"}
 
 
@@ -255,23 +256,38 @@ def run_gpu(args, workload):
     H = TensorHandleRef.from_torch
     hx, hc, hs, ho, hws = [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], [H(t) for t in outs], H(ws)
     client = ComputeClient.current()
-    # argument marshalling is done once; a step is 2*B calls straight into the C ABI
+    # Argument marshalling is done once.  A step is two calls into the C ABI: the fused quantize
+    # of the whole batch and the dequantize of the whole batch (one launch each for up to 64
+    # tensors).  The same work as one call per tensor is timed afterwards for comparison.
+    quant_batch = quantize.PreparedDynamicBatch(client, hx, hc, hs, scheme, elem, hws)
+    dequant_batch = dequantize.PreparedBatch(client, hc, ho, hs, scheme, elem)
     quant_calls = [quantize.PreparedDynamic(client, hx[i], hc[i], hs[i], scheme, elem, hws) for i in range(B)]
     dequant_calls = [dequantize.Prepared(client, hc[i], ho[i], hs[i], scheme, elem) for i in range(B)]
 
     def step():
+        quant_batch()
+        dequant_batch()
+
+    def step_single():
         for i in range(B):
             quant_calls[i]()
             dequant_calls[i]()
-
-    def only(calls):
-        for c in calls:
-            c()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def timed(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
 
     for _ in range(args.warmup):
         step()
@@ -290,21 +306,13 @@ def run_gpu(args, workload):
     elapsed_ms = start.elapsed_time(stop)
 
     # Per-kernel durations for the roofline: the same launches, one kind at a time, again
-    # bracketed by events on the launch stream (events between every pair of kernels would
+    # bracketed by events on the launch stream (an event between every pair of kernels would
     # serialise launch and execution and time the gap, not the kernel).
-    def time_kind(calls):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        only(calls)
-        torch.cuda.synchronize()
-        a.record()
-        for _ in range(args.steps):
-            only(calls)
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / (args.steps * len(calls))
-
-    q_avg = time_kind(quant_calls)
-    d_avg = time_kind(dequant_calls)
+    q_avg = timed(quant_batch, args.steps)
+    d_avg = timed(dequant_batch, args.steps)
+    single_ms = timed(step_single, max(args.steps // 2, 1))
+    single_q = timed(lambda: [c() for c in quant_calls], max(args.steps // 2, 1)) / B
+    single_d = timed(lambda: [c() for c in dequant_calls], max(args.steps // 2, 1)) / B
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
@@ -328,11 +336,14 @@ def run_gpu(args, workload):
     value = total_bytes / (elapsed_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
     kernels = {
-        "quantize_dynamic": {"avg_ms": round(q_avg, 5), "bytes": q_bytes, "gbs": round(q_bytes / q_avg / 1e6, 1)},
-        "dequantize": {"avg_ms": round(d_avg, 5), "bytes": d_bytes, "gbs": round(d_bytes / d_avg / 1e6, 1)},
+        "quantize_dynamic": {"avg_ms": round(q_avg, 5), "bytes": q_bytes * B, "gbs": round(q_bytes * B / q_avg / 1e6, 1),
+                             "tensors_per_launch": B},
+        "dequantize": {"avg_ms": round(d_avg, 5), "bytes": d_bytes * B, "gbs": round(d_bytes * B / d_avg / 1e6, 1),
+                       "tensors_per_launch": B},
     }
     dom = "quantize_dynamic" if q_avg >= d_avg else "dequantize"
     achieved = kernels[dom]["gbs"]
+    traffic = NCU_TRAFFIC_BYTES.get(workload.name, {}).get(dom)
     out = {
         "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
@@ -341,13 +352,17 @@ def run_gpu(args, workload):
         "pct_of_spec_peak": round(100 * value / world / SPEC_PEAK_GBS, 1),
         "pct_of_measured_peak": round(100 * value / world / peak, 1),
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
-                     "kernels": kernels},
+                     "frac": round(achieved / peak, 4), "traffic": traffic * B if traffic else None,
+                     "peak_source": f"{peak_kind} copy bandwidth", "kernels": kernels},
+        "single_tensor_calls": {
+            "value": round((q_bytes + d_bytes) * B / single_ms / 1e6, 1), "unit": "GB/s (this rank)",
+            "ms_per_step": round(single_ms, 4),
+            "quantize_dynamic": {"avg_ms": round(single_q, 5), "gbs": round(q_bytes / single_q / 1e6, 1)},
+            "dequantize": {"avg_ms": round(single_d, 5), "gbs": round(d_bytes / single_d / 1e6, 1)}},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "finite_output": err_ok,
     }
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(workload)
-    out["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(workload.name, {}).get(dom)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -70,6 +70,9 @@ _SIGNATURES = {
                                                                C.c_size_t, C.c_void_p]),
     "qk_quantize_dynamic": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                                  C.c_size_t, C.c_void_p]),
+    "qk_quantize_dynamic_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
+                                                    C.c_size_t, C.c_void_p]),
+    "qk_dequantize_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p]),
     "qk_quantize_dynamic_noalloc": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p]),
     "qk_noalloc_scratch_bytes": (C.c_size_t, []),
     "qk_absmax_f32": (C.c_int, [C.POINTER(QkTensor), C.c_int, C.c_void_p, C.c_void_p]),
@@ -148,3 +151,12 @@ class CTensor:
 
 def c_tensors(*tensors: TensorHandleRef) -> Sequence[CTensor]:
     return [CTensor(t) for t in tensors]
+
+
+class CTensorArray:
+    """A contiguous C array of QkTensor (for the batch entry points), keeping its parts alive."""
+
+    def __init__(self, tensors: Sequence[TensorHandleRef]):
+        self._items = [CTensor(t) for t in tensors]
+        self.array = (QkTensor * max(len(self._items), 1))(*[t.c for t in self._items])
+        self.count = len(self._items)

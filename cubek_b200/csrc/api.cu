@@ -293,9 +293,46 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
     return -2;
 }
 
+// Streaming launches are collected here: consecutive tensors that share the kernel
+// specialisation and geometry go out as one launch (up to QK_MAX_BATCH tensors).
+struct QuantBatch {
+    QuantArgs a;
+    int fdt = -1, kind = -1, unit_bytes = 0;
+    bool dyn = false, clamp = false;
+    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; }
+};
+struct DequantBatch {
+    DequantArgs a;
+    int fdt = -1, kind = -1, out_bytes = 0;
+    DequantBatch() { a.ntensors = 0; a.nunits = 0; }
+};
+
+static int flush_quant(QuantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (b.a.ntensors == 0) return QK_OK;
+    count_launch();
+    const cudaError_t e = launch_quantize(b.fdt, b.kind, b.unit_bytes, b.dyn, b.clamp, b.a, cfg, stream);
+    b.a.ntensors = 0;
+    b.a.nunits = 0;
+    b.a.absmax = nullptr;
+    return cuda_status(e);
+}
+
+static int flush_dequant(DequantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (b.a.ntensors == 0) return QK_OK;
+    count_launch();
+    const cudaError_t e = launch_dequantize(b.fdt, b.kind, b.out_bytes, b.a, cfg, stream);
+    b.a.ntensors = 0;
+    b.a.nunits = 0;
+    return cuda_status(e);
+}
+
 static int quantize_common(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
                            const QkTensor *out_scale, const float *absmax, bool dynamic, void *gen_scales,
-                           const QkScheme *scheme, int input_dtype, cudaStream_t stream);
+                           const QkScheme *scheme, int input_dtype, cudaStream_t stream, QuantBatch *batch = nullptr);
+static int dequantize_common(const QkTensor *values, const QkTensor *output, const QkTensor *params,
+                             const QkScheme *scheme, int output_dtype, cudaStream_t stream, DequantBatch *batch = nullptr);
 
 }  // namespace qk
 
@@ -352,50 +389,83 @@ int qk_quantize(const QkTensor *input, const QkTensor *output, const QkTensor *s
 }
 
 int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor *params, const QkScheme *scheme,
-                  int output_dtype, void *stream_)
+                  int output_dtype, void *stream)
+{
+    return dequantize_common(values, output, params, scheme, output_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int qk_dequantize_batch(int count, const QkTensor *values, const QkTensor *outputs, const QkTensor *params,
+                        const QkScheme *scheme, int output_dtype, void *stream_)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (!values || !output || !params || !scheme) return QK_ERR_NULL;
+    if (count < 0) return QK_ERR_SHAPE;
+    if (count == 0) return QK_OK;
+    if (!values || !outputs || !params || !scheme) return QK_ERR_NULL;
+    DequantBatch batch;
+    for (int i = 0; i < count; ++i) {
+        const int rc = dequantize_common(&values[i], &outputs[i], &params[i], scheme, output_dtype, stream, &batch);
+        if (rc != QK_OK) {
+            flush_dequant(batch, current_cfg(), stream);
+            return rc;
+        }
+    }
+    return flush_dequant(batch, current_cfg(), stream);
+}
+
+int qk_quantize_dynamic_batch(int count, const QkTensor *inputs, const QkTensor *outputs, const QkTensor *out_scales,
+                              const QkScheme *scheme, int input_dtype, void *workspace, size_t workspace_bytes,
+                              void *stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (count < 0) return QK_ERR_SHAPE;
+    if (count == 0) return QK_OK;
+    if (!inputs || !outputs || !out_scales || !scheme) return QK_ERR_NULL;
     int rc = check_scheme(scheme);
     if (rc) return rc;
-    const int fsize = dtype_size(output_dtype);
-    if (fsize == 0) return QK_ERR_DTYPE;
-    if ((rc = check_tensor(output, fsize))) return rc;
-    if ((rc = check_tensor(values, scheme->store == QK_STORE_U32 ? 4 : 1))) return rc;
-    if ((rc = check_tensor(params, dtype_size(scheme->param)))) return rc;
-    Geometry g;
-    if ((rc = build_geometry(g, scheme, output, values))) return rc;
-    if ((rc = check_scales_shape(g, params))) return rc;
-    if (!is_contiguous(values) || !is_contiguous(output)) return QK_ERR_LAYOUT;
-    if (g.n == 0) return QK_OK;
-
     const LaunchCfg cfg = current_cfg();
-    int out_bytes = 0;
-    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params, &out_bytes);
-    if (lg >= -1) {
-        DequantArgs a;
-        a.values = values->ptr;
-        a.params = params->ptr;
-        a.out = output->ptr;
-        a.nunits = g.n / (out_bytes / fsize);
-        a.lg_units_per_block = lg;
-        a.param = scheme->param;
-        a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
+    QuantBatch batch;
+    if (scheme->level == QK_LEVEL_TENSOR) {
+        // One absmax cell per tensor at the front of the workspace, cleared once; every tensor's
+        // absmax is reduced into its cell, then the quantize launches read them by tensor index.
+        if (!workspace || workspace_bytes < sizeof(unsigned int) * (size_t)count) return QK_ERR_WORKSPACE;
+        if (!aligned(workspace, 4)) return QK_ERR_ALIGN;
+        const int fsize = dtype_size(input_dtype);
+        if (fsize == 0) return QK_ERR_DTYPE;
+        unsigned int *cells = static_cast<unsigned int *>(workspace);
+        cudaError_t e = cudaMemsetAsync(cells, 0, sizeof(unsigned int) * (size_t)count, stream);
+        if (e != cudaSuccess) return cuda_status(e);
         count_launch();
-        return cuda_status(launch_dequantize(output_dtype, g.kind, out_bytes, a, cfg, stream));
+        for (int i = 0; i < count; ++i) {
+            if ((rc = check_tensor(&inputs[i], fsize))) return rc;
+            if (!is_contiguous(&inputs[i])) return QK_ERR_LAYOUT;
+            const long long n = numel(&inputs[i]);
+            if (n > 0) count_launch();
+            e = launch_absmax(input_dtype, inputs[i].ptr, n, cells + i, cfg, stream, false);
+            if (e != cudaSuccess) return cuda_status(e);
+        }
+        for (int i = 0; i < count; ++i) {
+            rc = quantize_common(&inputs[i], &outputs[i], nullptr, &out_scales[i],
+                                 reinterpret_cast<const float *>(cells + i), false, nullptr, scheme, input_dtype, stream,
+                                 &batch);
+            if (rc != QK_OK) {
+                flush_quant(batch, cfg, stream);
+                return rc;
+            }
+        }
+        return flush_quant(batch, cfg, stream);
     }
-    GeneralDequantArgs a;
-    fill_layout(a.layout, g, params, nullptr);
-    a.values = values->ptr;
-    a.params = params->ptr;
-    a.out = output->ptr;
-    a.nitems = g.n / g.nq;
-    a.nq = g.nq;
-    a.kind = g.kind;
-    a.fdt = output_dtype;
-    a.param = scheme->param;
-    count_launch();
-    return cuda_status(launch_general_dequantize(a, cfg, stream));
+    for (int i = 0; i < count; ++i) {
+        void *gen_scales = nullptr;
+        if (workspace && workspace_bytes >= qk_workspace_bytes_for(&inputs[i], scheme, input_dtype))
+            gen_scales = static_cast<char *>(workspace) + 256;
+        rc = quantize_common(&inputs[i], &outputs[i], nullptr, &out_scales[i], nullptr, true, gen_scales, scheme,
+                             input_dtype, stream, &batch);
+        if (rc != QK_OK) {
+            flush_quant(batch, cfg, stream);
+            return rc;
+        }
+    }
+    return flush_quant(batch, cfg, stream);
 }
 
 int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkScheme *scheme, int input_dtype,
@@ -558,7 +628,7 @@ namespace qk {
 // Shared body of qk_quantize / qk_quantize_dynamic / qk_quantize_from_absmax.
 static int quantize_common(const QkTensor *input, const QkTensor *output, const QkTensor *scale,
                            const QkTensor *out_scale, const float *absmax, bool dynamic, void *gen_scales,
-                           const QkScheme *scheme, int input_dtype, cudaStream_t stream)
+                           const QkScheme *scheme, int input_dtype, cudaStream_t stream, QuantBatch *batch)
 {
     if (!input || !output || !out_scale || !scheme) return QK_ERR_NULL;
     int rc = check_scheme(scheme);
@@ -584,26 +654,49 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     int unit_bytes = 0;
     const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale, &unit_bytes);
     if (lg >= -1) {
-        QuantArgs a;
-        a.in = input->ptr;
-        a.out = output->ptr;
-        a.scale_in = scale ? scale->ptr : nullptr;
-        a.out_scale = out_scale->ptr;
-        a.absmax = absmax;
-        a.nunits = g.n / (unit_bytes / fsize);
-        a.lg_units_per_block = lg;
-        a.param = scheme->param;
-        a.lo = lo;
-        a.hi = hi;
-        a.range = hi - lo;
-        a.inv_range = 1.0f / (hi - lo);
-        a.force_exact = cfg.force_exact;
-        a.aligned32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
+        QuantBatch local;
+        QuantBatch &b = batch ? *batch : local;
         const bool symmetric = (lo == -hi);
         const bool clamp = need_clamp(input_dtype, g.kind, dynamic, symmetric, scheme->param);
-        count_launch();
-        return cuda_status(launch_quantize(input_dtype, g.kind, unit_bytes, dynamic, clamp, a, cfg, stream));
+        const long long nunits = g.n / (unit_bytes / fsize);
+        const int a32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
+        // A tensor joins the pending launch only if it needs the very same kernel and constants;
+        // per-tensor absmax cells must be consecutive (the kernel indexes them by tensor).
+        const bool joins = b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == input_dtype &&
+                           b.kind == g.kind && b.unit_bytes == unit_bytes && b.dyn == dynamic && b.clamp == clamp &&
+                           b.a.lg_units_per_block == lg && b.a.param == scheme->param && b.a.lo == lo && b.a.hi == hi &&
+                           b.a.force_exact == cfg.force_exact &&
+                           ((absmax == nullptr && b.a.absmax == nullptr) ||
+                            (absmax != nullptr && b.a.absmax != nullptr && absmax == b.a.absmax + b.a.ntensors));
+        if (!joins) {
+            if ((rc = flush_quant(b, cfg, stream))) return rc;
+            b.fdt = input_dtype;
+            b.kind = g.kind;
+            b.unit_bytes = unit_bytes;
+            b.dyn = dynamic;
+            b.clamp = clamp;
+            b.a.absmax = absmax;
+            b.a.lg_units_per_block = lg;
+            b.a.param = scheme->param;
+            b.a.lo = lo;
+            b.a.hi = hi;
+            b.a.range = hi - lo;
+            b.a.inv_range = 1.0f / (hi - lo);
+            b.a.force_exact = cfg.force_exact;
+            b.a.aligned32 = 1;
+        }
+        QuantTensor &t = b.a.t[b.a.ntensors];
+        t.in = input->ptr;
+        t.out = output->ptr;
+        t.scale_in = scale ? scale->ptr : nullptr;
+        t.out_scale = out_scale->ptr;
+        b.a.nunits += nunits;
+        t.unit_end = b.a.nunits;
+        b.a.aligned32 &= a32;
+        b.a.ntensors += 1;
+        return batch ? QK_OK : flush_quant(b, cfg, stream);
     }
+    if (batch && (rc = flush_quant(*batch, cfg, stream))) return rc;
 
     // Layout-general route.
     GeneralQuantArgs a;
@@ -654,6 +747,67 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     a.range = hi - lo;
     count_launch();
     return cuda_status(launch_general_quantize(a, cfg, stream));
+}
+
+// Shared body of qk_dequantize / qk_dequantize_batch.
+static int dequantize_common(const QkTensor *values, const QkTensor *output, const QkTensor *params,
+                             const QkScheme *scheme, int output_dtype, cudaStream_t stream, DequantBatch *batch)
+{
+    if (!values || !output || !params || !scheme) return QK_ERR_NULL;
+    int rc = check_scheme(scheme);
+    if (rc) return rc;
+    const int fsize = dtype_size(output_dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    if ((rc = check_tensor(output, fsize))) return rc;
+    if ((rc = check_tensor(values, scheme->store == QK_STORE_U32 ? 4 : 1))) return rc;
+    if ((rc = check_tensor(params, dtype_size(scheme->param)))) return rc;
+    Geometry g;
+    if ((rc = build_geometry(g, scheme, output, values))) return rc;
+    if ((rc = check_scales_shape(g, params))) return rc;
+    if (!is_contiguous(values) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (g.n == 0) return QK_OK;
+
+    const LaunchCfg cfg = current_cfg();
+    int out_bytes = 0;
+    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params, &out_bytes);
+    if (lg >= -1) {
+        DequantBatch local;
+        DequantBatch &b = batch ? *batch : local;
+        const bool joins = b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == output_dtype &&
+                           b.kind == g.kind && b.out_bytes == out_bytes && b.a.lg_units_per_block == lg &&
+                           b.a.param == scheme->param;
+        if (!joins) {
+            if ((rc = flush_dequant(b, cfg, stream))) return rc;
+            b.fdt = output_dtype;
+            b.kind = g.kind;
+            b.out_bytes = out_bytes;
+            b.a.lg_units_per_block = lg;
+            b.a.param = scheme->param;
+            b.a.aligned32 = 1;
+        }
+        DequantTensor &t = b.a.t[b.a.ntensors];
+        t.values = values->ptr;
+        t.params = params->ptr;
+        t.out = output->ptr;
+        b.a.nunits += g.n / (out_bytes / fsize);
+        t.unit_end = b.a.nunits;
+        b.a.aligned32 &= aligned(output->ptr, 32) ? 1 : 0;
+        b.a.ntensors += 1;
+        return batch ? QK_OK : flush_dequant(b, cfg, stream);
+    }
+    if (batch && (rc = flush_dequant(*batch, cfg, stream))) return rc;
+    GeneralDequantArgs a;
+    fill_layout(a.layout, g, params, nullptr);
+    a.values = values->ptr;
+    a.params = params->ptr;
+    a.out = output->ptr;
+    a.nitems = g.n / g.nq;
+    a.nq = g.nq;
+    a.kind = g.kind;
+    a.fdt = output_dtype;
+    a.param = scheme->param;
+    count_launch();
+    return cuda_status(launch_general_dequantize(a, cfg, stream));
 }
 
 }  // namespace qk

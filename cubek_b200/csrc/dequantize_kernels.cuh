@@ -18,14 +18,21 @@
 
 namespace qk {
 
+struct DequantTensor {
+    const void *values;  // u32 words or native bytes
+    const void *params;  // param-typed scales, contiguous, one per block (or one)
+    void *out;           // F-typed output
+    long long unit_end;  // units in this and all earlier tensors of the batch
+};
+
+// One tensor, or a batch of tensors sharing scheme, float type and unit geometry.
 struct DequantArgs {
-    const void *values;      // u32 words or native bytes
-    const void *params;      // param-typed scales, contiguous, one per block (or one)
-    void *out;               // F-typed output
-    long long nunits;        // dequant units in the tensor
+    DequantTensor t[QK_MAX_BATCH];
+    int ntensors;
+    long long nunits;        // dequant units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     int param;               // QkParam
-    int aligned32;           // output base 32-byte aligned (256-bit stores allowed)
+    int aligned32;           // every output base 32-byte aligned (256-bit stores allowed)
 };
 
 // One dequant unit: OB bytes of output produced by one thread.
@@ -158,35 +165,38 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     constexpr int OREG_PER_WORD = EPW * DU::ESZ / 4;
     constexpr int UNR = 4;
 
-    const uint32_t *vals = static_cast<const uint32_t *>(a.values);
-    char *out = static_cast<char *>(a.out);
     const int lg = a.lg_units_per_block;
     const bool aligned32 = a.aligned32 != 0;
     pdl_entry();
-    float tensor_scale = 0.0f;
-    if (lg < 0) tensor_scale = round_to<FDT>(load_dyn(a.params, a.param, 0));
+    int ti = 0;  // tensor of the batch this thread is in (only ever moves forward)
 
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < a.nunits;
          base += stride) {
         uint32_t w[UNR][IW];
         float s[UNR];
+        char *dst[UNR];
         const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             const bool valid = full || idx < a.nunits;
             if (valid) {
+                while (ti + 1 < a.ntensors && idx >= a.t[ti].unit_end) ++ti;
+                const DequantTensor &T = a.t[ti];
+                const long long li = idx - (ti ? a.t[ti - 1].unit_end : 0);
+                const uint32_t *vals = static_cast<const uint32_t *>(T.values);
+                dst[k] = static_cast<char *>(T.out) + li * OB;
                 if constexpr (IW == 1) {
-                    w[k][0] = __ldg(vals + idx);
+                    w[k][0] = __ldg(vals + li);
                 } else if constexpr (IW == 2) {
-                    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(vals) + idx);
+                    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(vals) + li);
                     w[k][0] = t.x;
                     w[k][1] = t.y;
                 } else {
 #pragma unroll
                     for (int v = 0; v < IW / 4; ++v) {
-                        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(vals) + idx * (IW / 4) + v);
+                        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(vals) + li * (IW / 4) + v);
                         w[k][4 * v] = t.x;
                         w[k][4 * v + 1] = t.y;
                         w[k][4 * v + 2] = t.z;
@@ -194,13 +204,14 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                     }
                 }
                 // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
-                if (lg < 0) s[k] = tensor_scale;
-                else if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(a.params) + (idx >> lg)));
-                else s[k] = round_to<FDT>(load_dyn(a.params, a.param, idx >> lg));
+                const long long si = (lg < 0) ? 0 : (li >> lg);
+                if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(T.params) + si));
+                else s[k] = round_to<FDT>(load_dyn(T.params, a.param, si));
             } else {
 #pragma unroll
                 for (int j = 0; j < IW; ++j) w[k][j] = 0u;
                 s[k] = 0.0f;
+                dst[k] = nullptr;
             }
         }
 #pragma unroll
@@ -212,14 +223,13 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
             if constexpr (FDT != QK_F32) s2 = h2_pack<FDT>(s[k], s[k]);
 #pragma unroll
             for (int j = 0; j < IW; ++j) dequant_word<FDT, KIND>(w[k][j], s[k], s2, o + j * OREG_PER_WORD);
-            char *dst = out + idx * OB;
             if (aligned32) {
 #pragma unroll
                 for (int v = 0; v < OB / 32; ++v) {
                     Vec32 t;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) t.w[i] = o[8 * v + i];
-                    stg256_stream(dst + 32 * v, t);
+                    stg256_stream(dst[k] + 32 * v, t);
                 }
             } else {
 #pragma unroll
@@ -227,7 +237,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                     Vec16 t;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) t.w[i] = o[4 * v + i];
-                    stg128_stream(dst + 16 * v, t);
+                    stg128_stream(dst[k] + 16 * v, t);
                 }
             }
         }

@@ -89,10 +89,12 @@ static int grid_for(long long work_items, int per_cta, const LaunchCfg &cfg)
 }
 
 cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
-                          cudaStream_t stream)
+                          cudaStream_t stream, bool zero_first)
 {
-    cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
-    if (e != cudaSuccess) return e;
+    if (zero_first) {
+        cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
+        if (e != cudaSuccess) return e;
+    }
     if (n == 0) return cudaSuccess;
     const int threads = 256;
     if ((reinterpret_cast<uintptr_t>(in) & 15u) != 0) {

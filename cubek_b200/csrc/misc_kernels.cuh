@@ -50,8 +50,10 @@ struct GeneralScalesArgs {
     float range;
 };
 
+// absmax of `n` elements max-reduced into `*cell` (bit pattern of a non-negative f32).  The cell
+// must hold zero (or an earlier partial result) beforehand; `zero_first` clears it on the stream.
 cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
-                          cudaStream_t stream);
+                          cudaStream_t stream, bool zero_first = true);
 cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,
                                   cudaStream_t stream);
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);

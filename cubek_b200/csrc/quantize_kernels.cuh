@@ -25,19 +25,30 @@
 
 namespace qk {
 
+// A launch covers one tensor or a batch of tensors that share the scheme, float type and unit
+// geometry.  Units are numbered across the batch; `unit_end` is the running total.
+constexpr int QK_MAX_BATCH = 64;
+
+struct QuantTensor {
+    const void *in;        // F-typed input, contiguous
+    void *out;             // u32 words or native bytes
+    const void *scale_in;  // F-typed scales (given-scale form); contiguous, one per block
+    void *out_scale;       // param-typed scales out
+    long long unit_end;    // units in this and all earlier tensors of the batch
+};
+
 struct QuantArgs {
-    const void *in;          // F-typed input, contiguous
-    void *out;               // u32 words or native bytes
-    const void *scale_in;    // F-typed scales (given-scale form); contiguous, one per block
-    void *out_scale;         // param-typed scales out
-    const float *absmax;     // per tensor: absmax scalar on the device (overrides scale_in)
-    long long nunits;        // units in the tensor
+    QuantTensor t[QK_MAX_BATCH];
+    int ntensors;
+    const float *absmax;     // per tensor: absmax scalars on the device, one per tensor of the batch
+                             // (overrides scale_in)
+    long long nunits;        // units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     int param;               // QkParam of out_scale
     float lo, hi, range;     // clamp bounds, hi - lo
     float inv_range;         // RN(1 / range), computed on the host
     int force_exact;         // 1: reference arithmetic for every unit
-    int aligned32;           // input and output bases are 32-byte aligned (256-bit accesses allowed)
+    int aligned32;           // every input and output base is 32-byte aligned (256-bit accesses allowed)
 };
 
 // A unit: UB bytes of input handled by one thread.
@@ -430,32 +441,32 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
     constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread
     using F = typename ElemOf<FDT>::type;
 
-    const char *in = static_cast<const char *>(a.in);
-    uint32_t *out = static_cast<uint32_t *>(a.out);
     const bool aligned32 = a.aligned32 != 0;
     const int lg = a.lg_units_per_block;
     pdl_entry();
 
-    // Per tensor: one scale for the whole launch, derived once per thread.
-    float tensor_scale = 0.0f;
-    if constexpr (!DYN) {
-        if (lg < 0) {
-            tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * (*a.absmax), a.range, a.inv_range))
-                                    : static_cast<float>(static_cast<const F *>(a.scale_in)[0]);
-        }
-    }
+    int ti = 0;                 // tensor of the batch this thread is in (only ever moves forward)
+    int scale_ti = -1;          // tensor `tensor_scale` belongs to
+    float tensor_scale = 0.0f;  // per tensor: one scale for the whole tensor
 
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < a.nunits;
          base += stride) {
         uint32_t raw[UNR][RAW];
+        int tk[UNR];
+        long long lidx[UNR];
         const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             if (full || idx < a.nunits) {
-                load_unit<UB>(raw[k], in + idx * UB, aligned32);
+                while (ti + 1 < a.ntensors && idx >= a.t[ti].unit_end) ++ti;
+                tk[k] = ti;
+                lidx[k] = idx - (ti ? a.t[ti - 1].unit_end : 0);
+                load_unit<UB>(raw[k], static_cast<const char *>(a.t[ti].in) + lidx[k] * UB, aligned32);
             } else {
+                tk[k] = ti;
+                lidx[k] = 0;
 #pragma unroll
                 for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
             }
@@ -464,6 +475,8 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             const bool valid = full || idx < a.nunits;
+            const QuantTensor &T = a.t[tk[k]];
+            const long long li = lidx[k];
 
             float scale_f;
             if constexpr (DYN) {
@@ -473,9 +486,15 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
                 for (int m = 1; m < 32; m <<= 1)
                     if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
                 scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
+            } else if (lg < 0) {
+                if (scale_ti != tk[k]) {
+                    scale_ti = tk[k];
+                    tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * a.absmax[scale_ti], a.range, a.inv_range))
+                                            : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
+                }
+                scale_f = tensor_scale;
             } else {
-                scale_f = (lg < 0) ? tensor_scale
-                                   : (valid ? static_cast<float>(static_cast<const F *>(a.scale_in)[idx >> lg]) : 1.0f);
+                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[li >> lg]) : 1.0f;
             }
             // write_scale: the scale is cast to the param type, stored, and that value (cast
             // back to F) is the divisor (crates/cubek-quant/src/quantize.rs:83-98).
@@ -483,9 +502,9 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
             const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
             if (valid) {
                 if (lg < 0) {
-                    if (idx == 0) store_dyn(a.out_scale, a.param, 0, s_fs);
-                } else if ((idx & ((1ll << lg) - 1)) == 0) {
-                    store_dyn(a.out_scale, a.param, idx >> lg, s_fs);
+                    if (li == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
+                } else if ((li & ((1ll << lg) - 1)) == 0) {
+                    store_dyn(T.out_scale, a.param, li >> lg, s_fs);
                 }
             }
             uint32_t w[OW];
@@ -493,7 +512,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
                 quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], s, a.lo, a.hi, w);
             else
                 quantize_unit_exact<FDT, KIND, UB>(raw[k], s, a.lo, a.hi, w);
-            if (valid) store_words<OW>(out + idx * OW, w, aligned32);
+            if (valid) store_words<OW>(static_cast<uint32_t *>(T.out) + li * OW, w, aligned32);
         }
     }
 }

@@ -31,3 +31,26 @@ class Prepared:
         status = self._fn(*self._args)
         if status:
             _ffi.check(status)
+
+
+class PreparedBatch:
+    """Dequantize of a set of tensors, one launch per group of up to 64 compatible tensors
+    (``qk_dequantize_batch``); same results as ``launch_ref`` per tensor."""
+
+    def __init__(self, client: ComputeClient, values, outputs, params, scheme: QuantScheme, input_dtype: ElemType):
+        self._v, self._o, self._p = _ffi.CTensorArray(values), _ffi.CTensorArray(outputs), _ffi.CTensorArray(params)
+        if not (self._v.count == self._o.count == self._p.count):
+            raise ValueError("values, outputs and params must have the same length")
+        self._scheme = _ffi.c_scheme(scheme)
+        self._args = (self._v.count, self._v.array, self._o.array, self._p.array, self._scheme, int(input_dtype),
+                      client.stream)
+        self._fn = _ffi.lib().qk_dequantize_batch
+
+    def __call__(self) -> None:
+        status = self._fn(*self._args)
+        if status:
+            _ffi.check(status)
+
+
+def launch_batch(client: ComputeClient, values, outputs, params, scheme: QuantScheme, input_dtype: ElemType) -> None:
+    PreparedBatch(client, values, outputs, params, scheme, input_dtype)()

@@ -83,3 +83,30 @@ class PreparedDynamic:
         status = self._fn(*self._args)
         if status:
             _ffi.check(status)
+
+
+class PreparedDynamicBatch:
+    """Fused quantize of a set of tensors with one launch per group of up to 64 compatible tensors
+    (``qk_quantize_dynamic_batch``); same results as ``launch_dynamic`` per tensor."""
+
+    def __init__(self, client: ComputeClient, inputs, outputs, out_scales, scheme: QuantScheme,
+                 input_elem: ElemType, workspace: TensorHandleRef | None = None):
+        self._in, self._out, self._sc = (_ffi.CTensorArray(inputs), _ffi.CTensorArray(outputs),
+                                         _ffi.CTensorArray(out_scales))
+        if not (self._in.count == self._out.count == self._sc.count):
+            raise ValueError("inputs, outputs and out_scales must have the same length")
+        self._scheme = _ffi.c_scheme(scheme)
+        ws_ptr, ws_bytes = (workspace.handle, workspace.shape[0] * workspace.elem_size) if workspace else (None, 0)
+        self._args = (self._in.count, self._in.array, self._out.array, self._sc.array, self._scheme, int(input_elem),
+                      ws_ptr, ws_bytes, client.stream)
+        self._fn = _ffi.lib().qk_quantize_dynamic_batch
+
+    def __call__(self) -> None:
+        status = self._fn(*self._args)
+        if status:
+            _ffi.check(status)
+
+
+def launch_dynamic_batch(client: ComputeClient, inputs, outputs, out_scales, scheme: QuantScheme,
+                         input_elem: ElemType, workspace: TensorHandleRef | None = None) -> None:
+    PreparedDynamicBatch(client, inputs, outputs, out_scales, scheme, input_elem, workspace)()

@@ -134,6 +134,20 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
                         void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Sets of tensors (e.g. the weights of a model): the same results as calling
+ * qk_quantize_dynamic / qk_dequantize once per tensor, but consecutive tensors that need the same
+ * kernel go out as ONE launch (up to 64 tensors each), so that small tensors do not pay a launch
+ * gap each.  `inputs`, `outputs`, ... are host arrays of `count` QkTensor.  Per-tensor schemes need
+ * 4 bytes of workspace per tensor (at least qk_workspace_bytes()); per-block schemes as
+ * qk_quantize_dynamic.  No reference counterpart: the reference launches tensor by tensor.
+ */
+int qk_quantize_dynamic_batch(int count, const QkTensor *inputs, const QkTensor *outputs,
+                              const QkTensor *out_scales, const QkScheme *scheme, int input_dtype,
+                              void *workspace, size_t workspace_bytes, void *stream);
+int qk_dequantize_batch(int count, const QkTensor *values, const QkTensor *outputs, const QkTensor *params,
+                        const QkScheme *scheme, int output_dtype, void *stream);
+
+/*
  * Per-tensor quantize split for tensors sharded over several GPUs: phase 1 leaves the
  * shard's absmax as one f32 in `absmax_out` (device); the caller max-reduces that scalar
  * across ranks (qk_allreduce_max_f32 or any allreduce); phase 2 quantizes with the scale
