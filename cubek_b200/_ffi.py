@@ -29,7 +29,7 @@ QK_ERR_CUDA = 1000
 # Status codes that stand for a `panic!` / `assert!` in the reference.
 PANIC_CLASS = (QK_ERR_UNSUPPORTED_SCHEME, QK_ERR_BLOCK_SIZE, QK_ERR_SHAPE, QK_ERR_DTYPE)
 
-TUNE_THREADS, TUNE_CTAS_PER_SM, TUNE_FORCE_EXACT, TUNE_FORCE_GENERAL, TUNE_PDL = range(5)
+TUNE_THREADS, TUNE_CTAS_PER_SM, TUNE_FORCE_EXACT, TUNE_FORCE_GENERAL, TUNE_PDL, TUNE_QUANT_WAVES, TUNE_DEQUANT_WAVES = range(7)
 
 
 class QkScheme(C.Structure):

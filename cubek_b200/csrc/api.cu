@@ -45,8 +45,9 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 }
 
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
-enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4, TUNE_COUNT = 5 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}};  // ctas_per_sm 0 = one full wave
+enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
+       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COUNT = 7 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -68,6 +69,8 @@ static LaunchCfg current_cfg()
     c.ctas_per_sm = g_tune[TUNE_CTAS_PER_SM].load();
     c.force_exact = g_tune[TUNE_FORCE_EXACT].load();
     c.pdl = g_tune[TUNE_PDL].load();
+    c.quant_waves = g_tune[TUNE_QUANT_WAVES].load();
+    c.dequant_waves = g_tune[TUNE_DEQUANT_WAVES].load();
     c.sm_count = sm_count_of_current_device();
     return c;
 }

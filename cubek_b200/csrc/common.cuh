@@ -283,7 +283,9 @@ static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int 
 
 struct LaunchCfg {
     int threads;      // threads per CTA
-    int ctas_per_sm;  // grid cap = SM count * ctas_per_sm
+    int ctas_per_sm;  // grid cap = SM count * ctas_per_sm; 0 = resident CTAs per SM * waves
+    int quant_waves;  // grid cap of the quantize kernels, in waves of resident CTAs
+    int dequant_waves;
     int sm_count;
     int force_exact;  // 1: every unit takes the reference-arithmetic route
     int pdl;          // 1: launch with programmatic stream serialization

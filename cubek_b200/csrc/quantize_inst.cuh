@@ -6,8 +6,9 @@
 
 namespace qk {
 
-// One wave exactly: the grid is the number of CTAs the device holds at once (or fewer when the
-// tensor is small), so that no CTA waits for a slot and all finish together.
+// Grids are whole waves of resident CTAs (or fewer CTAs when the tensor is small): a partial
+// last wave leaves SMs idle while the others finish (measured: 3 or 6 CTAs/SM for a kernel that
+// holds 3 run at 6500 GB/s, 4 or 8 at 5100-6100).
 template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int threads)
 {
     int n = 0;
@@ -21,8 +22,7 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     constexpr int UNR = (UB >= 64) ? 2 : 4;
     const int threads = cfg.threads;
     static const int occ256 = resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, 256);
-    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm
-                                             : (threads == 256 ? occ256 : resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, threads));
+    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm : occ256 * (cfg.quant_waves > 0 ? cfg.quant_waves : 1);
     long long need = (args.nunits + (long long)threads * UNR - 1) / ((long long)threads * UNR);
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
