@@ -22,6 +22,21 @@ cudaError_t launch_block_scales_f32(const void *, void *, long long, int, float,
 cudaError_t launch_block_scales_f16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
 
+cudaError_t launch_quantize_tensor_f32(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_tensor_f16(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_tensor_bf16(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
+
+cudaError_t launch_quantize_tensor(int fdt, int kind, QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
+                                   cudaStream_t stream)
+{
+    switch (fdt) {
+    case QK_F32: return launch_quantize_tensor_f32(kind, args, partials_capacity, cfg, stream);
+    case QK_F16: return launch_quantize_tensor_f16(kind, args, partials_capacity, cfg, stream);
+    case QK_BF16: return launch_quantize_tensor_bf16(kind, args, partials_capacity, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
 cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream)
 {
@@ -46,8 +61,8 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
-       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COUNT = 7 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}};
+       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_COUNT = 8 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -254,9 +269,10 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
         if (scale && !is_contiguous(scale)) return -2;
         if (out_scale && !is_contiguous(out_scale)) return -2;
     }
-    const int candidates[2] = {64, min_unit_bytes(fdt, g.kind)};
-    for (int ci = 0; ci < 2; ++ci) {
+    const int candidates[3] = {64, 32, min_unit_bytes(fdt, g.kind)};
+    for (int ci = 0; ci < 3; ++ci) {
         const int ub = candidates[ci];
+        if (ub < min_unit_bytes(fdt, g.kind)) continue;
         const int U = ub / esz;
         if (g.n % U != 0) continue;
         const int out_words = U / kind_elems_per_u32(g.kind);
@@ -336,6 +352,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
                            const QkScheme *scheme, int input_dtype, cudaStream_t stream, QuantBatch *batch = nullptr);
 static int dequantize_common(const QkTensor *values, const QkTensor *output, const QkTensor *params,
                              const QkScheme *scheme, int output_dtype, cudaStream_t stream, DequantBatch *batch = nullptr);
+static int try_quantize_tensor_coop(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                                    const QkScheme *scheme, int input_dtype, void *workspace, size_t workspace_bytes,
+                                    cudaStream_t stream);
 
 }  // namespace qk
 
@@ -368,18 +387,21 @@ int qk_value_range(int value, float *lo, float *hi)
     return QK_OK;
 }
 
-size_t qk_workspace_bytes(void) { return 256; }
+size_t qk_workspace_bytes(void) { return 8192; }
 
 size_t qk_workspace_bytes_for(const QkTensor *input, const QkScheme *scheme, int input_dtype)
 {
-    // Per tensor: one absmax cell.  Per block: the fused kernel needs nothing; layouts that
-    // fall back to the general kernels stage F-typed scales behind the cell.
+    // Per tensor: the partial absmax of every resident CTA (or, with less than that, one cell and
+    // the two-kernel route).  Per block: the fused kernel needs nothing; layouts that fall back to
+    // the general kernels stage F-typed scales 256 bytes into the workspace.
     size_t bytes = 256;
-    if (!input || !scheme || dtype_size(input_dtype) == 0 || check_scheme(scheme) != QK_OK) return bytes;
-    if (!input->shape || input->rank < 1 || input->rank > QK_MAX_RANK) return bytes;
-    Geometry g;
-    if (build_geometry(g, scheme, input, nullptr) != QK_OK) return bytes;
-    if (!g.per_tensor) bytes += (size_t)g.nscales * (size_t)dtype_size(input_dtype);
+    if (input && scheme && dtype_size(input_dtype) != 0 && check_scheme(scheme) == QK_OK && input->shape &&
+        input->rank >= 1 && input->rank <= QK_MAX_RANK) {
+        Geometry g;
+        if (build_geometry(g, scheme, input, nullptr) == QK_OK && !g.per_tensor)
+            bytes += (size_t)g.nscales * (size_t)dtype_size(input_dtype);
+    }
+    if (bytes < qk_workspace_bytes()) bytes = qk_workspace_bytes();
     return (bytes + 255) & ~(size_t)255;
 }
 
@@ -435,10 +457,29 @@ int qk_quantize_dynamic_batch(int count, const QkTensor *inputs, const QkTensor 
         const int fsize = dtype_size(input_dtype);
         if (fsize == 0) return QK_ERR_DTYPE;
         unsigned int *cells = static_cast<unsigned int *>(workspace);
+        // Tensors that fit the L2 go one by one through the cooperative single-launch kernel
+        // (its partials live behind the cells); the others share batched launches.
+        const size_t cells_bytes = (sizeof(unsigned int) * (size_t)count + 255) & ~(size_t)255;
+        bool pending[QK_MAX_BATCH * 16];
+        if (count > (int)(sizeof(pending) / sizeof(pending[0]))) return QK_ERR_TOO_LARGE;
+        int npending = 0;
+        for (int i = 0; i < count; ++i) {
+            pending[i] = true;
+            if (workspace_bytes > cells_bytes) {
+                rc = try_quantize_tensor_coop(&inputs[i], &outputs[i], &out_scales[i], scheme, input_dtype,
+                                              static_cast<char *>(workspace) + cells_bytes, workspace_bytes - cells_bytes,
+                                              stream);
+                if (rc == QK_OK) pending[i] = false;
+                else if (rc != QK_ERR_TOO_LARGE) return rc;
+            }
+            npending += pending[i] ? 1 : 0;
+        }
+        if (npending == 0) return QK_OK;
         cudaError_t e = cudaMemsetAsync(cells, 0, sizeof(unsigned int) * (size_t)count, stream);
         if (e != cudaSuccess) return cuda_status(e);
         count_launch();
         for (int i = 0; i < count; ++i) {
+            if (!pending[i]) continue;
             if ((rc = check_tensor(&inputs[i], fsize))) return rc;
             if (!is_contiguous(&inputs[i])) return QK_ERR_LAYOUT;
             const long long n = numel(&inputs[i]);
@@ -447,6 +488,7 @@ int qk_quantize_dynamic_batch(int count, const QkTensor *inputs, const QkTensor 
             if (e != cudaSuccess) return cuda_status(e);
         }
         for (int i = 0; i < count; ++i) {
+            if (!pending[i]) continue;
             rc = quantize_common(&inputs[i], &outputs[i], nullptr, &out_scales[i],
                                  reinterpret_cast<const float *>(cells + i), false, nullptr, scheme, input_dtype, stream,
                                  &batch);
@@ -535,6 +577,8 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
         if (!is_contiguous(input)) return QK_ERR_LAYOUT;
         unsigned int *cell = static_cast<unsigned int *>(workspace);
         const long long n = numel(input);
+        rc = try_quantize_tensor_coop(input, output, out_scale, scheme, input_dtype, workspace, workspace_bytes, stream);
+        if (rc != QK_ERR_TOO_LARGE) return rc;   // done, or a real error; TOO_LARGE = route not applicable
         count_launch(n > 0 ? 2 : 1);
         cudaError_t e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
         if (e != cudaSuccess) return cuda_status(e);
@@ -811,6 +855,54 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     a.param = scheme->param;
     count_launch();
     return cuda_status(launch_general_dequantize(a, cfg, stream));
+}
+
+// Per tensor in one cooperative launch (absmax, grid barrier, quantize; second pass served from
+// L2).  Returns QK_ERR_TOO_LARGE when the route does not apply (geometry, workspace, tuning) and
+// the caller should take the two-kernel route; any other status is final.
+static int try_quantize_tensor_coop(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
+                                    const QkScheme *scheme, int input_dtype, void *workspace, size_t workspace_bytes,
+                                    cudaStream_t stream)
+{
+    if (!g_tune[TUNE_COOP_TENSOR].load() || g_tune[TUNE_FORCE_GENERAL].load()) return QK_ERR_TOO_LARGE;
+    if (!input || !output || !out_scale) return QK_ERR_NULL;
+    const int fsize = dtype_size(input_dtype);
+    int rc;
+    if ((rc = check_tensor(input, fsize))) return rc;
+    if ((rc = check_tensor(output, scheme->store == QK_STORE_U32 ? 4 : 1))) return rc;
+    if ((rc = check_tensor(out_scale, dtype_size(scheme->param)))) return rc;
+    Geometry g;
+    if ((rc = build_geometry(g, scheme, input, output))) return rc;
+    if ((rc = check_scales_shape(g, out_scale))) return rc;
+    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    const int U = 64 / fsize;
+    if (g.n == 0 || g.n % U != 0 || !aligned(input->ptr, 16) || !aligned(output->ptr, 16) || !aligned(workspace, 4))
+        return QK_ERR_TOO_LARGE;
+    // Beyond the L2 the second pass comes from HBM anyway and the barrier only costs.
+    if ((size_t)g.n * fsize > (size_t)100 << 20) return QK_ERR_TOO_LARGE;
+    float lo, hi;
+    qk_value_range(scheme->value, &lo, &hi);
+    const LaunchCfg cfg = current_cfg();
+    QuantTensorArgs a;
+    a.in = input->ptr;
+    a.out = output->ptr;
+    a.out_scale = out_scale->ptr;
+    a.partials = static_cast<float *>(workspace);
+    a.nunits = g.n / U;
+    a.param = scheme->param;
+    a.lo = lo;
+    a.hi = hi;
+    a.range = hi - lo;
+    a.inv_range = 1.0f / (hi - lo);
+    a.force_exact = cfg.force_exact;
+    a.aligned32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
+    const cudaError_t e = launch_quantize_tensor(input_dtype, g.kind, a, (int)(workspace_bytes / sizeof(float)), cfg, stream);
+    if (e == cudaErrorInvalidValue) {
+        (void)cudaGetLastError();
+        return QK_ERR_TOO_LARGE;   // workspace smaller than the resident grid: two-kernel route
+    }
+    count_launch();
+    return cuda_status(e);
 }
 
 }  // namespace qk

@@ -90,7 +90,9 @@ Plan make_plan(const QkTensor *input, const QkScheme *scheme, int input_dtype)
     p.out_off = align_up(p.scale_off + (size_t)p.slice_scales * dtype_size(scheme->param), 256);
     p.ws_off = align_up(p.out_off + p.out_row * p.slice_rows, 256);
     // workspace: absmax cell (+ staged scales for general layouts)
-    p.slot_bytes = align_up(p.ws_off + 256 + (size_t)p.slice_scales * fsize, 256);
+    size_t ws_bytes = 256 + (size_t)p.slice_scales * fsize;
+    if (ws_bytes < qk_workspace_bytes()) ws_bytes = qk_workspace_bytes();
+    p.slot_bytes = align_up(p.ws_off + ws_bytes, 256);
     p.ok = 1;
     return p;
 }

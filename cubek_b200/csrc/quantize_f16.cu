@@ -12,4 +12,9 @@ cudaError_t launch_block_scales_f16(const void *in, void *scale_out, long long n
 {
     return launch_block_scales_t<QK_F16>(in, scale_out, nchunks, lg, range, inv_range, cfg, stream);
 }
+cudaError_t launch_quantize_tensor_f16(int kind, QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
+                                      cudaStream_t stream)
+{
+    return launch_quantize_tensor_t<QK_F16>(kind, args, partials_capacity, cfg, stream);
+}
 }  // namespace qk

@@ -44,6 +44,9 @@ static cudaError_t launch_unit(int unit_bytes, bool dyn, bool clamp, const Quant
 {
     constexpr int MINB = min_unit_bytes(FDT, KIND);
     if (unit_bytes == 64) return launch_mode<FDT, KIND, 64>(dyn, clamp, args, cfg, stream);
+    if constexpr (MINB < 32) {
+        if (unit_bytes == 32) return launch_mode<FDT, KIND, 32>(dyn, clamp, args, cfg, stream);
+    }
     if constexpr (MINB < 64) {
         if (unit_bytes == MINB) return launch_mode<FDT, KIND, MINB>(dyn, clamp, args, cfg, stream);
     }
@@ -62,6 +65,38 @@ static cudaError_t launch_quantize_t(int kind, int unit_bytes, bool dyn, bool cl
     case KIND_E2M1: return launch_unit<FDT, KIND_E2M1>(unit_bytes, dyn, clamp, args, cfg, stream);
     case KIND_E4M3: return launch_unit<FDT, KIND_E4M3>(unit_bytes, dyn, clamp, args, cfg, stream);
     case KIND_E5M2: return launch_unit<FDT, KIND_E5M2>(unit_bytes, dyn, clamp, args, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+template <int FDT, int KIND>
+static cudaError_t launch_tensor_one(QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
+                                     cudaStream_t stream)
+{
+    constexpr int UNR = 2;
+    static const int occ = resident_ctas_per_sm(quantize_tensor_kernel<FDT, KIND, 64>, 256);
+    long long need = (args.nunits + 256ll * UNR - 1) / (256ll * UNR);
+    const long long cap = (long long)cfg.sm_count * occ;   // all CTAs must be resident (grid barrier)
+    if (need > cap) need = cap;
+    if (need < 1) need = 1;
+    if (need > partials_capacity) return cudaErrorInvalidValue;
+    void *params[] = {&args};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(quantize_tensor_kernel<FDT, KIND, 64>), dim3((unsigned)need),
+                                       dim3(256), params, 0, stream);
+}
+
+template <int FDT>
+static cudaError_t launch_quantize_tensor_t(int kind, QuantTensorArgs &args, int partials_capacity,
+                                            const LaunchCfg &cfg, cudaStream_t stream)
+{
+    switch (kind) {
+    case KIND_PACK8: return launch_tensor_one<FDT, KIND_PACK8>(args, partials_capacity, cfg, stream);
+    case KIND_PACK4: return launch_tensor_one<FDT, KIND_PACK4>(args, partials_capacity, cfg, stream);
+    case KIND_PACK2: return launch_tensor_one<FDT, KIND_PACK2>(args, partials_capacity, cfg, stream);
+    case KIND_I8: return launch_tensor_one<FDT, KIND_I8>(args, partials_capacity, cfg, stream);
+    case KIND_E2M1: return launch_tensor_one<FDT, KIND_E2M1>(args, partials_capacity, cfg, stream);
+    case KIND_E4M3: return launch_tensor_one<FDT, KIND_E4M3>(args, partials_capacity, cfg, stream);
+    case KIND_E5M2: return launch_tensor_one<FDT, KIND_E5M2>(args, partials_capacity, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -21,6 +21,8 @@
 // the fast route against.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace qk {
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
     constexpr int OW = UT::OW;
-    constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread
+    constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread (128 bytes; 64 for 16-byte units)
     using F = typename ElemOf<FDT>::type;
 
     const bool aligned32 = a.aligned32 != 0;
@@ -518,6 +520,121 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
 }
 
 // -------------------------------------------------------------------------------------
+// Per tensor, fused in ONE cooperative launch: absmax over the whole tensor, a grid-wide
+// barrier, then quantize.  Every CTA leaves its partial absmax in `partials[blockIdx.x]`
+// (no atomics, nothing to clear), and after the barrier every CTA reduces those partials.
+// The second pass walks the tensor in the opposite direction, so it starts on the data the
+// first pass read last, which is still in the 126 MB L2: a 64 MB tensor is read from HBM
+// once instead of twice.  Results are bit-identical to absmax_kernel + quantize_kernel.
+// Must be launched cooperatively with a grid that is resident all at once.
+// -------------------------------------------------------------------------------------
+struct QuantTensorArgs {
+    const void *in;
+    void *out;
+    void *out_scale;
+    float *partials;     // gridDim.x floats of scratch
+    long long nunits;
+    int param;
+    float lo, hi, range, inv_range;
+    int force_exact;
+    int aligned32;
+};
+
+template <int FDT, int KIND, int UB>
+__global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorArgs a)
+{
+    using UT = UnitT<FDT, KIND, UB>;
+    constexpr int RAW = UT::RAW;
+    constexpr int OW = UT::OW;
+    constexpr int UNR = (UB >= 64) ? 2 : 4;
+    const char *in = static_cast<const char *>(a.in);
+    uint32_t *out = static_cast<uint32_t *>(a.out);
+    const bool aligned32 = a.aligned32 != 0;
+    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
+    const long long first = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x;
+    const long long niter = (a.nunits + stride - 1) / stride;
+
+    // ---- pass 1: absmax ------------------------------------------------------------------
+    float amax = 0.0f;
+    for (long long it = 0; it < niter; ++it) {
+        const long long base = it * stride + first;
+        uint32_t raw[UNR][RAW];
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            const long long idx = base + (long long)k * blockDim.x;
+            if (idx < a.nunits) {
+                load_unit<UB>(raw[k], in + idx * UB, aligned32);
+            } else {
+#pragma unroll
+                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) amax = fmaxf(amax, unit_absmax<FDT, RAW>(raw[k]));
+    }
+    __shared__ float warp_max[8];
+    __shared__ float block_max;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float v = warp_max[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) v = fmaxf(v, warp_max[i]);
+        a.partials[blockIdx.x] = v;
+    }
+    __threadfence();
+    cooperative_groups::this_grid().sync();
+
+    // ---- every CTA reduces the partials --------------------------------------------------
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) v = fmaxf(v, __ldcg(a.partials + i));
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    __syncthreads();
+    if (lane == 0) warp_max[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = warp_max[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) t = fmaxf(t, warp_max[i]);
+        block_max = t;
+    }
+    __syncthreads();
+    const float scale_f = round_to<FDT>(div_by_range(2.0f * block_max, a.range, a.inv_range));
+    const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
+    const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
+    if (blockIdx.x == 0 && threadIdx.x == 0) store_dyn(a.out_scale, a.param, 0, s_fs);
+    const bool fast = kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s);
+
+    // ---- pass 2: quantize, last iteration first ---------------------------------------------
+    for (long long it = niter - 1; it >= 0; --it) {
+        const long long base = it * stride + first;
+        uint32_t raw[UNR][RAW];
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            const long long idx = base + (long long)k * blockDim.x;
+            if (idx < a.nunits) {
+                load_unit<UB>(raw[k], in + idx * UB, aligned32);
+            } else {
+#pragma unroll
+                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            const long long idx = base + (long long)k * blockDim.x;
+            uint32_t w[OW];
+            if (fast) quantize_unit_fast<FDT, KIND, UB, true, false>(raw[k], s, a.lo, a.hi, w);
+            else quantize_unit_exact<FDT, KIND, UB>(raw[k], s, a.lo, a.hi, w);
+            if (idx < a.nunits) store_words<OW>(out + idx * OW, w, aligned32);
+        }
+    }
+}
+
+// -------------------------------------------------------------------------------------
 // Scales only (per block), for the two-call form: absmax over each block then the scale
 // formula, written as F.  16-byte chunks, blocks are aligned runs of 2^lg lanes.
 // -------------------------------------------------------------------------------------
@@ -563,5 +680,9 @@ cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool cl
                             const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
                                 float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
+// Cooperative per-tensor launch (64-byte units).  `partials_capacity` floats are available at
+// args.partials; returns cudaErrorInvalidValue if the resident grid needs more.
+cudaError_t launch_quantize_tensor(int fdt, int kind, QuantTensorArgs &args, int partials_capacity,
+                                   const LaunchCfg &cfg, cudaStream_t stream);
 
 }  // namespace qk

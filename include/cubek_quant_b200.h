@@ -119,7 +119,7 @@ int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor
  * instructions/maxabs.rs:31-87) followed by `scale = 2*absmax / (q_max - q_min)`
  * (crates/cubek-quant/tests/suite/symmetric.rs:35-38, :175-178).  Writes `scale`
  * typed `input_dtype`, ready to be handed to qk_quantize.
- * Per tensor it needs `qk_workspace_bytes()` bytes of device workspace; per block none.
+ * Per tensor it needs 4 bytes of device workspace; per block none.
  */
 int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkScheme *scheme,
                       int input_dtype, void *workspace, size_t workspace_bytes, void *stream);
@@ -194,7 +194,8 @@ int qk_quantize_dynamic_noalloc(const QkTensor *input, const QkTensor *output, c
                                 const QkScheme *scheme, int input_dtype, void *stream);
 size_t qk_noalloc_scratch_bytes(void);
 
-/* Device workspace needed by the per-tensor paths (a fixed, small size). */
+/* Device workspace for the per-tensor paths (a fixed, small size: 8 KiB).  With at least 4 bytes
+ * they still work, through two launches instead of one. */
 size_t qk_workspace_bytes(void);
 /* Workspace for qk_quantize_dynamic on this input: qk_workspace_bytes() plus, per block, room
  * to stage F-typed scales when the layout is not the streaming one (N-d blocks, ragged sizes). */

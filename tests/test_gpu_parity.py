@@ -197,3 +197,31 @@ def test_scale_extremes_take_the_reference_route():
     assert_bits_equal(g_codes, codes, "codes")
     d_codes, _ = gpu_quantize_dynamic(x, scheme)
     assert_bits_equal(d_codes, O.quantize_dynamic(x, scheme)[0], "codes (fused)")
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+def test_per_tensor_routes_agree(fname, tuning):
+    """Per tensor, the fused call has two routes: one cooperative launch (absmax, grid barrier,
+    quantize) when the workspace holds a partial per CTA, else absmax kernel + quantize kernel.
+    Both must give the oracle's bits, on tensors of many CTAs and of a single one."""
+    import torch
+    from cubek_b200 import ComputeClient, TensorHandleRef, quantize
+    from tests._util import code_dtype, elem_of, empty_device, to_device, to_numpy
+
+    F = FLOATS[fname]
+    H = TensorHandleRef.from_torch
+    for value, store in ((QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4F, QuantStore.U32),
+                         (QuantValue.E2M1, QuantStore.Native)):
+        scheme = QuantScheme(value=value, store=store)
+        for shape in ((1024, 4096), (8, 256), (3, 32)):
+            x = random_tensor(shape, F, 77)
+            want_codes, want_scale = O.quantize_dynamic(x, scheme)
+            for ws_bytes in (8192, 256):
+                dx = to_device(x)
+                dq = empty_device(scheme.packed_shape(shape), code_dtype(scheme))
+                ds = empty_device((1,), np.float32)
+                ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+                quantize.launch_dynamic(ComputeClient.current(), H(dx), H(dq), H(ds), scheme, elem_of(F), H(ws))
+                torch.cuda.synchronize()
+                assert_bits_equal(to_numpy(dq, code_dtype(scheme)), want_codes, f"codes ws={ws_bytes}")
+                assert_bits_equal(to_numpy(ds, np.float32), want_scale, f"scale ws={ws_bytes}")
