@@ -129,12 +129,12 @@ template <int FDT> __device__ __forceinline__ uint32_t h2_const(float v) { retur
 template <int FDT> __device__ __forceinline__ float h_lo_to_f32(uint32_t p)
 {
     if constexpr (FDT == QK_BF16) return bf16_lo_to_f32(p);
-    else return __half2float(__ushort_as_half((unsigned short)(p & 0xffffu)));
+    else return __low2float(*reinterpret_cast<const __half2 *>(&p));   // half selected by the instruction
 }
 template <int FDT> __device__ __forceinline__ float h_hi_to_f32(uint32_t p)
 {
     if constexpr (FDT == QK_BF16) return bf16_hi_to_f32(p);
-    else return __half2float(__ushort_as_half((unsigned short)(p >> 16)));
+    else return __high2float(*reinterpret_cast<const __half2 *>(&p));
 }
 
 // Element i of the raw registers, widened to f32.
