@@ -49,15 +49,6 @@ __host__ __device__ constexpr int kind_bits(int kind)
 }
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
-// A "unit" is the run of consecutive elements one thread turns into whole output words:
-// at least one 128-bit input access and at least one 32-bit output word.
-template <int FDT, int KIND> struct Unit {
-    static constexpr int ELEMS = cmax(FInfo<FDT>::PER16, kind_elems_per_u32(KIND));
-    static constexpr int IN_BYTES = ELEMS * FInfo<FDT>::SIZE;             // 16, 32 or 64
-    static constexpr int OUT_WORDS = ELEMS / kind_elems_per_u32(KIND);    // 1 or 2
-    static constexpr int IN_VEC16 = IN_BYTES / 16;
-};
-
 // ---- raw memory access ----------------------------------------------------------------
 
 struct alignas(16) Vec16 { uint32_t w[4]; };
@@ -111,8 +102,6 @@ __device__ __forceinline__ void stg256_stream(void *p, const Vec32 &v)
 
 __device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi_to_f32(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
-
-__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 // Two f32 -> packed bf16x2 / f16x2, round to nearest even; `lo` lands in bits 0..15.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
@@ -179,13 +168,6 @@ template <int FDT> __device__ __forceinline__ void widen16(const Vec16 &v, float
 }
 
 // ---- scale arithmetic -----------------------------------------------------------------
-
-// scale = (2 * absmax) / (hi - lo), evaluated in f32 then narrowed to F
-// (crates/cubek-quant/tests/suite/symmetric.rs:35-38, :175-178).
-template <int FDT> __device__ __forceinline__ float scale_from_absmax(float absmax, float range)
-{
-    return round_to<FDT>(__fdiv_rn(2.0f * absmax, range));
-}
 
 // clamp(round(t)) with round-half-to-even; a NaN quotient (0/0) gives code 0.
 __device__ __forceinline__ float round_clamp(float t, float lo, float hi)

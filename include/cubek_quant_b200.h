@@ -220,7 +220,10 @@ const char *qk_version(void);
 /* Number of kernels this library has launched in the calling process (for accounting). */
 uint64_t qk_launch_count(void);
 
-/* Kernel variant selection for measurements: 0 = default, see DESIGN notes in the source. */
+/* Process-wide launch knobs, for measurements and tests only (keys: 0 threads per CTA, 1 CTAs per SM,
+ * 2 force the reference-arithmetic route, 3 force the layout-general kernels, 4 programmatic dependent
+ * launch on/off, 5 / 6 grid size of the quantize / dequantize kernels in waves, 7 cooperative per-tensor
+ * kernel on/off). */
 void qk_set_tuning(int key, int value);
 int qk_get_tuning(int key);
 
