@@ -70,6 +70,7 @@ _SIGNATURES = {
                                                                C.c_size_t, C.c_void_p]),
     "qk_quantize_dynamic": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                                  C.c_size_t, C.c_void_p]),
+    "qk_reduce_maxabs": (C.c_int, [C.POINTER(QkTensor)] * 2 + [C.c_int, C.c_int, C.c_void_p]),
     "qk_quantize_dynamic_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                     C.c_size_t, C.c_void_p]),
     "qk_dequantize_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p]),

@@ -232,8 +232,10 @@ static int check_scales_shape(const Geometry &g, const QkTensor *sc)
     return QK_OK;
 }
 
-static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *scales, const QkTensor *out_scales)
+static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *scales, const QkTensor *out_scales,
+                        const QkTensor *data)
 {
+    L.data_contiguous = (!data || is_contiguous(data)) ? 1 : 0;
     L.rank = g.rank;
     L.per_tensor = g.per_tensor ? 1 : 0;
     for (int d = 0; d < QK_MAX_RANK; ++d) {
@@ -241,6 +243,7 @@ static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *sca
         L.block[d] = d < g.rank ? g.block[d] : 1;
         L.scale_strides[d] = (!g.per_tensor && scales && d < g.rank) ? scales->strides[d] : 0;
         L.out_scale_strides[d] = (!g.per_tensor && out_scales && d < g.rank) ? out_scales->strides[d] : 0;
+        L.data_strides[d] = (data && d < g.rank) ? data->strides[d] : 0;
     }
 }
 
@@ -263,7 +266,7 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
-    if (!aligned(in->ptr, 16)) return -2;
+    if (!aligned(in->ptr, 16) || !is_contiguous(in)) return -2;
     if (!g.per_tensor) {
         if (!g.last_dim_blocks) return -2;
         if (scale && !is_contiguous(scale)) return -2;
@@ -293,7 +296,7 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
-    if (!aligned(out->ptr, 16)) return -2;
+    if (!aligned(out->ptr, 16) || !is_contiguous(out)) return -2;
     if (!g.per_tensor && (!g.last_dim_blocks || !is_contiguous(params))) return -2;
     const int candidates[2] = {64, min_dequant_bytes(fdt, g.kind)};
     for (int ci = 0; ci < 2; ++ci) {
@@ -481,7 +484,7 @@ int qk_quantize_dynamic_batch(int count, const QkTensor *inputs, const QkTensor 
         for (int i = 0; i < count; ++i) {
             if (!pending[i]) continue;
             if ((rc = check_tensor(&inputs[i], fsize))) return rc;
-            if (!is_contiguous(&inputs[i])) return QK_ERR_LAYOUT;
+            if (!is_contiguous(&inputs[i])) return QK_ERR_LAYOUT;   // batches take contiguous tensors only
             const long long n = numel(&inputs[i]);
             if (n > 0) count_launch();
             e = launch_absmax(input_dtype, inputs[i].ptr, n, cells + i, cfg, stream, false);
@@ -527,7 +530,7 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
     Geometry g;
     if ((rc = build_geometry(g, scheme, input, nullptr))) return rc;
     if ((rc = check_scales_shape(g, scale))) return rc;
-    if (!is_contiguous(input)) return QK_ERR_LAYOUT;
+    const bool contiguous = is_contiguous(input);
     float lo, hi;
     qk_value_range(scheme->value, &lo, &hi);
     const float range = hi - lo;
@@ -538,19 +541,27 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
         if (!aligned(workspace, 4)) return QK_ERR_ALIGN;
         unsigned int *cell = static_cast<unsigned int *>(workspace);
         count_launch(g.n > 0 ? 3 : 2);
-        cudaError_t e = launch_absmax(input_dtype, input->ptr, g.n, cell, cfg, stream);
+        cudaError_t e;
+        if (contiguous) {
+            e = launch_absmax(input_dtype, input->ptr, g.n, cell, cfg, stream);
+        } else {
+            GeneralLayout L;
+            fill_layout(L, g, nullptr, nullptr, input);
+            e = launch_absmax_strided(L, input->ptr, input_dtype, g.n, cell, cfg, stream);
+        }
         if (e != cudaSuccess) return cuda_status(e);
         return cuda_status(launch_finalize_scale(cell, scale->ptr, input_dtype, range, stream));
     }
     if (g.n == 0) return QK_OK;
     const int per16 = 16 / fsize;
     const int lg = (g.last_dim_blocks && g.B % per16 == 0) ? log2_exact(g.B / per16) : -1;
-    if (!g_tune[TUNE_FORCE_GENERAL].load() && lg >= 0 && lg <= 5 && aligned(input->ptr, 16) && is_contiguous(scale)) {
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && contiguous && lg >= 0 && lg <= 5 && aligned(input->ptr, 16) &&
+        is_contiguous(scale)) {
         count_launch();
         return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / per16, lg, range, 1.0f / range, cfg, stream));
     }
     GeneralScalesArgs a;
-    fill_layout(a.layout, g, scale, nullptr);
+    fill_layout(a.layout, g, scale, nullptr, input);
     a.in = input->ptr;
     a.scale_out = scale->ptr;
     a.nblocks = g.nscales;
@@ -574,13 +585,21 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
         const int fsize = dtype_size(input_dtype);
         if (fsize == 0) return QK_ERR_DTYPE;
         if ((rc = check_tensor(input, fsize))) return rc;
-        if (!is_contiguous(input)) return QK_ERR_LAYOUT;
         unsigned int *cell = static_cast<unsigned int *>(workspace);
         const long long n = numel(input);
         rc = try_quantize_tensor_coop(input, output, out_scale, scheme, input_dtype, workspace, workspace_bytes, stream);
         if (rc != QK_ERR_TOO_LARGE) return rc;   // done, or a real error; TOO_LARGE = route not applicable
         count_launch(n > 0 ? 2 : 1);
-        cudaError_t e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
+        cudaError_t e;
+        if (is_contiguous(input)) {
+            e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
+        } else {
+            Geometry g;
+            if ((rc = build_geometry(g, scheme, input, nullptr))) return rc;
+            GeneralLayout L;
+            fill_layout(L, g, nullptr, nullptr, input);
+            e = launch_absmax_strided(L, input->ptr, input_dtype, n, cell, current_cfg(), stream);
+        }
         if (e != cudaSuccess) return cuda_status(e);
         return quantize_common(input, output, nullptr, out_scale, reinterpret_cast<const float *>(cell), false,
                                nullptr, scheme, input_dtype, stream);
@@ -592,6 +611,30 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
     return quantize_common(input, output, nullptr, out_scale, nullptr, true, gen_scales, scheme, input_dtype, stream);
 }
 
+int qk_reduce_maxabs(const QkTensor *input, const QkTensor *output, int axis, int dtype, void *stream)
+{
+    if (!input || !output) return QK_ERR_NULL;
+    const int fsize = dtype_size(dtype);
+    if (fsize == 0) return QK_ERR_DTYPE;
+    int rc;
+    if ((rc = check_tensor(input, fsize))) return rc;
+    if ((rc = check_tensor(output, fsize))) return rc;
+    // validate_axis / valid_output_shape (crates/cubek-reduce/src/lib.rs:134-150)
+    if (axis < 0 || axis >= input->rank) return QK_ERR_SHAPE;
+    if (output->rank != input->rank) return QK_ERR_SHAPE;
+    for (int d = 0; d < input->rank; ++d)
+        if (output->shape[d] != (d == axis ? 1 : input->shape[d])) return QK_ERR_SHAPE;
+    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    long long outer = 1, inner = 1;
+    for (int d = 0; d < axis; ++d) outer *= input->shape[d];
+    for (int d = axis + 1; d < input->rank; ++d) inner *= input->shape[d];
+    const long long len = input->shape[axis];
+    if (outer * inner == 0) return QK_OK;
+    count_launch();
+    return cuda_status(launch_maxabs(dtype, input->ptr, output->ptr, outer, len, inner, current_cfg(),
+                                     static_cast<cudaStream_t>(stream)));
+}
+
 int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, void *stream)
 {
     if (!input || !absmax_out) return QK_ERR_NULL;
@@ -599,10 +642,24 @@ int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, voi
     if (fsize == 0) return QK_ERR_DTYPE;
     int rc = check_tensor(input, fsize);
     if (rc) return rc;
-    if (!is_contiguous(input)) return QK_ERR_LAYOUT;
     if (!aligned(absmax_out, 4)) return QK_ERR_ALIGN;
     const long long n = numel(input);
     count_launch(n > 0 ? 2 : 1);
+    if (!is_contiguous(input)) {
+        if (input->rank > QK_MAX_RANK) return QK_ERR_SHAPE;
+        GeneralLayout L;
+        L.rank = input->rank;
+        L.per_tensor = 1;
+        L.data_contiguous = 0;
+        for (int d = 0; d < QK_MAX_RANK; ++d) {
+            L.shape[d] = d < input->rank ? input->shape[d] : 1;
+            L.data_strides[d] = d < input->rank ? input->strides[d] : 0;
+            L.block[d] = 1;
+            L.scale_strides[d] = L.out_scale_strides[d] = 0;
+        }
+        return cuda_status(launch_absmax_strided(L, input->ptr, input_dtype, n, reinterpret_cast<unsigned int *>(absmax_out),
+                                                 current_cfg(), static_cast<cudaStream_t>(stream)));
+    }
     return cuda_status(launch_absmax(input_dtype, input->ptr, n, reinterpret_cast<unsigned int *>(absmax_out),
                                      current_cfg(), static_cast<cudaStream_t>(stream)));
 }
@@ -646,7 +703,7 @@ const char *qk_strerror(int status)
     case QK_ERR_BLOCK_SIZE: return "block size must be non-zero, fit the tensor rank and be divisible by num_quants";
     case QK_ERR_SHAPE: return "shape mismatch (last dim must be a multiple of num_quants; scales must hold one value per block)";
     case QK_ERR_DTYPE: return "element size does not match the declared element type";
-    case QK_ERR_LAYOUT: return "values, input and output must be contiguous";
+    case QK_ERR_LAYOUT: return "the quantized tensor must be contiguous";
     case QK_ERR_ALIGN: return "pointer is not aligned to its element size";
     case QK_ERR_NULL: return "null argument";
     case QK_ERR_WORKSPACE: return "workspace missing or too small";
@@ -692,7 +749,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     if (!g.per_tensor && g.B % g.nq != 0) return QK_ERR_BLOCK_SIZE;
     if (scale && (rc = check_scales_shape(g, scale))) return rc;
     if ((rc = check_scales_shape(g, out_scale))) return rc;
-    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    // The float tensor may be strided (the reference reads it through `linear_view`); the quantized
+    // tensor must be contiguous.
+    if (!is_contiguous(output)) return QK_ERR_LAYOUT;
     if (g.n == 0) return QK_OK;
 
     float lo, hi;
@@ -765,7 +824,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         staged.strides = staged_strides;
         staged.elem_size = fsize;
         GeneralScalesArgs sa;
-        fill_layout(sa.layout, g, &staged, nullptr);
+        fill_layout(sa.layout, g, &staged, nullptr, input);
         sa.in = input->ptr;
         sa.scale_out = gen_scales;
         sa.nblocks = g.nscales;
@@ -775,9 +834,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         cudaError_t e = launch_general_scales(sa, cfg, stream);
         if (e != cudaSuccess) return cuda_status(e);
         scale_ptr = gen_scales;
-        fill_layout(a.layout, g, &staged, out_scale);
+        fill_layout(a.layout, g, &staged, out_scale, input);
     } else {
-        fill_layout(a.layout, g, scale, out_scale);
+        fill_layout(a.layout, g, scale, out_scale, input);
     }
     a.in = input->ptr;
     a.out = output->ptr;
@@ -811,7 +870,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     Geometry g;
     if ((rc = build_geometry(g, scheme, output, values))) return rc;
     if ((rc = check_scales_shape(g, params))) return rc;
-    if (!is_contiguous(values) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (!is_contiguous(values)) return QK_ERR_LAYOUT;   // the float output may be strided
     if (g.n == 0) return QK_OK;
 
     const LaunchCfg cfg = current_cfg();
@@ -844,7 +903,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     }
     if (batch && (rc = flush_dequant(*batch, cfg, stream))) return rc;
     GeneralDequantArgs a;
-    fill_layout(a.layout, g, params, nullptr);
+    fill_layout(a.layout, g, params, nullptr, output);
     a.values = values->ptr;
     a.params = params->ptr;
     a.out = output->ptr;
@@ -874,7 +933,8 @@ static int try_quantize_tensor_coop(const QkTensor *input, const QkTensor *outpu
     Geometry g;
     if ((rc = build_geometry(g, scheme, input, output))) return rc;
     if ((rc = check_scales_shape(g, out_scale))) return rc;
-    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (!is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (!is_contiguous(input)) return QK_ERR_TOO_LARGE;
     const int U = 64 / fsize;
     if (g.n == 0 || g.n % U != 0 || !aligned(input->ptr, 16) || !aligned(output->ptr, 16) || !aligned(workspace, 4))
         return QK_ERR_TOO_LARGE;

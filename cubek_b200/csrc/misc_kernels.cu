@@ -73,6 +73,23 @@ __global__ void __launch_bounds__(256) absmax_scalar_kernel(const void *in, int 
     if ((threadIdx.x & 31) == 0) atomicMax(cell, __float_as_uint(amax));
 }
 
+__global__ void __launch_bounds__(256) absmax_strided_kernel(const GeneralLayout L, const void *in, int fdt, long long n,
+                                                             unsigned int *cell)
+{
+    float amax = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        long long offs = i, idx = 0;
+        for (int d = L.rank - 1; d >= 0; --d) {
+            idx += (offs % L.shape[d]) * L.data_strides[d];
+            offs /= L.shape[d];
+        }
+        amax = fmaxf(amax, fabsf(load_dyn(in, fdt, idx)));
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    if ((threadIdx.x & 31) == 0) atomicMax(cell, __float_as_uint(amax));
+}
+
 __global__ void finalize_scale_kernel(const unsigned int *cell, void *scale_out, int fdt, float range)
 {
     const float amax = __uint_as_float(*cell);
@@ -111,6 +128,15 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
     }
 }
 
+cudaError_t launch_absmax_strided(const GeneralLayout &layout, const void *in, int fdt, long long n, unsigned int *cell,
+                                  const LaunchCfg &cfg, cudaStream_t stream)
+{
+    cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
+    if (e != cudaSuccess || n == 0) return e;
+    absmax_strided_kernel<<<grid_for(n, 256 * 8, cfg), 256, 0, stream>>>(layout, in, fdt, n, cell);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,
                                   cudaStream_t stream)
 {
@@ -145,6 +171,18 @@ __device__ __forceinline__ long long general_scale_pos(const GeneralLayout &L, l
     return sp;
 }
 
+// Offset (elements) of linear element `pos` of the float tensor.
+__device__ __forceinline__ long long data_index(const GeneralLayout &L, long long pos)
+{
+    if (L.data_contiguous) return pos;
+    long long offs = pos, idx = 0;
+    for (int d = L.rank - 1; d >= 0; --d) {
+        idx += (offs % L.shape[d]) * L.data_strides[d];
+        offs /= L.shape[d];
+    }
+    return idx;
+}
+
 // Native element encode of an integral, clamped value.
 __device__ __forceinline__ uint32_t encode_native(int kind, float c)
 {
@@ -170,20 +208,23 @@ __global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuan
         if (is_start) store_dyn(a.out_scale, a.param, sp_out, s_fs);
         const float s = round_to_dyn(a.fdt, s_fs);
 
+        // the nq elements of an item are consecutive along the last dim
+        const long long d0 = data_index(a.layout, pos);
+        const long long dstep = a.layout.data_contiguous ? 1 : a.layout.data_strides[a.layout.rank - 1];
         if (a.kind <= KIND_PACK2) {
             uint32_t word = 0;
             for (int i = 0; i < a.nq; ++i) {
-                const float t = round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos + i), s));
+                const float t = round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0 + i * dstep), s));
                 const float c = round_clamp(t, a.lo, a.hi);
                 word |= ((uint32_t)(int)c & mask) << (i * bits);
             }
             static_cast<uint32_t *>(a.out)[item] = word;
         } else if (a.kind == KIND_E2M1) {
-            const float c0 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos), s)), a.lo, a.hi);
-            const float c1 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos + 1), s)), a.lo, a.hi);
+            const float c0 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
+            const float c1 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0 + dstep), s)), a.lo, a.hi);
             static_cast<uint8_t *>(a.out)[item] = (uint8_t)cvt_e2m1x2(c0, c1);
         } else {
-            const float c = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, pos), s)), a.lo, a.hi);
+            const float c = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
             static_cast<uint8_t *>(a.out)[item] = (uint8_t)encode_native(a.kind, c);
         }
     }
@@ -200,18 +241,20 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
         bool is_start;
         const long long sp = general_scale_pos(a.layout, pos, &is_start);
         const float s = round_to_dyn(a.fdt, load_dyn(a.params, a.param, sp));
+        const long long d0 = data_index(a.layout, pos);
+        const long long dstep = a.layout.data_contiguous ? 1 : a.layout.data_strides[a.layout.rank - 1];
         if (a.kind <= KIND_PACK2) {
             const uint32_t word = static_cast<const uint32_t *>(a.values)[item];
             for (int i = 0; i < a.nq; ++i) {
                 const int raw = (int)((word >> (i * bits)) & mask);
                 const int q = raw - (raw >= sign_bit ? two_pow_n : 0);
-                store_dyn(a.out, a.fdt, pos + i, s * (float)q);
+                store_dyn(a.out, a.fdt, d0 + i * dstep, s * (float)q);
             }
         } else if (a.kind == KIND_E2M1) {
             uint32_t h2 = cvt_f16x2_from_e2m1x2(static_cast<const uint8_t *>(a.values)[item]);
             float2 f = __half22float2(*reinterpret_cast<__half2 *>(&h2));
-            store_dyn(a.out, a.fdt, pos, s * f.x);
-            store_dyn(a.out, a.fdt, pos + 1, s * f.y);
+            store_dyn(a.out, a.fdt, d0, s * f.x);
+            store_dyn(a.out, a.fdt, d0 + dstep, s * f.y);
         } else {
             const uint32_t b = static_cast<const uint8_t *>(a.values)[item];
             float q;
@@ -220,7 +263,7 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
                 uint32_t h2 = (a.kind == KIND_E4M3) ? cvt_f16x2_from_e4m3x2(b) : cvt_f16x2_from_e5m2x2(b);
                 q = __half22float2(*reinterpret_cast<__half2 *>(&h2)).x;
             }
-            store_dyn(a.out, a.fdt, pos, s * q);
+            store_dyn(a.out, a.fdt, d0, s * q);
         }
     }
 }
@@ -250,7 +293,7 @@ __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScales
             for (int d = L.rank - 1; d >= 0; --d) {
                 const long long coord = bc[d] * L.block[d] + r % ext[d];
                 r /= ext[d];
-                lin += coord * mul;
+                lin += coord * (L.data_contiguous ? mul : L.data_strides[d]);
                 mul *= L.shape[d];
             }
             amax = fmaxf(amax, fabsf(load_dyn(a.in, a.fdt, lin)));

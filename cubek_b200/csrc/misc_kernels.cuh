@@ -18,6 +18,10 @@ struct GeneralLayout {
     // strides of the second scales tensor of a quantize call (`out_scale`); the reference builds
     // one view per scales handle (crates/cubek-quant/src/quantize.rs:313, :317)
     long long out_scale_strides[QK_MAX_RANK];
+    // strides (elements) of the float tensor: the input of quantize / compute_scales, the output of
+    // dequantize.  The reference reaches it through `linear_view`, which honours strides.
+    long long data_strides[QK_MAX_RANK];
+    int data_contiguous;
 };
 
 struct GeneralQuantArgs {
@@ -59,5 +63,12 @@ cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_general_dequantize(const GeneralDequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_general_scales(const GeneralScalesArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
+// absmax of a strided tensor into `*cell` (cleared first on the stream).
+cudaError_t launch_absmax_strided(const GeneralLayout &layout, const void *in, int fdt, long long n, unsigned int *cell,
+                                  const LaunchCfg &cfg, cudaStream_t stream);
+
+// max |x| over `len` elements of stride `inner`, for every (outer, inner) position.
+cudaError_t launch_maxabs(int fdt, const void *in, void *out, long long outer, long long len, long long inner,
+                          const LaunchCfg &cfg, cudaStream_t stream);
 
 }  // namespace qk

@@ -75,7 +75,7 @@ enum {
     QK_ERR_BLOCK_SIZE = 2,         /* lib.rs:28-31 */
     QK_ERR_SHAPE = 3,              /* last dim not a multiple of num_quants, or shapes that disagree */
     QK_ERR_DTYPE = 4,              /* elem_size does not match the declared element type */
-    QK_ERR_LAYOUT = 5,             /* non-contiguous values / input / output */
+    QK_ERR_LAYOUT = 5,             /* non-contiguous quantized tensor */
     QK_ERR_ALIGN = 6,              /* pointer not aligned to its element / word size */
     QK_ERR_NULL = 7,
     QK_ERR_WORKSPACE = 8,          /* workspace missing or too small */
@@ -93,7 +93,7 @@ int qk_value_range(int value, float *lo, float *hi);
 
 /*
  * Replaces `cubek_quant::quantize::launch_ref` (quantize.rs:174-221), same argument order.
- *   input     float tensor of type `input_dtype`, contiguous
+ *   input     float tensor of type `input_dtype`; may be strided (contiguous ones take the fast kernels)
  *   output    quantized tensor: u32 words of shape [.., n/num_quants] (QK_STORE_U32), or
  *             1-byte items (QK_STORE_NATIVE: i8, e4m3, e5m2; fp4 pairs of shape [.., n/2])
  *   scale     scales typed `input_dtype`: shape [1] per tensor, else one per block
@@ -107,7 +107,7 @@ int qk_quantize(const QkTensor *input, const QkTensor *output, const QkTensor *s
 /*
  * Replaces `cubek_quant::dequantize::launch_ref` (dequantize.rs:171-229), same argument order.
  *   values  quantized tensor (as written by qk_quantize)
- *   output  float tensor of type `output_dtype`, contiguous, shape = unpacked shape
+ *   output  float tensor of type `output_dtype`, shape = unpacked shape; may be strided
  *   params  scales typed as the scheme's param
  */
 int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor *params,
@@ -123,6 +123,14 @@ int qk_dequantize(const QkTensor *values, const QkTensor *output, const QkTensor
  */
 int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkScheme *scheme,
                       int input_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * max |x| along `axis`: `cubek_reduce::reduce::<R, MaxAbs>(client, input, output, axis, ..)`
+ * (crates/cubek-reduce/src/lib.rs:93-131, instructions/maxabs.rs:31-87) for contiguous tensors.
+ * `output` has the input's shape with extent 1 at `axis` and the input's element type
+ * (the reference accumulates MaxAbs in the input type; the result is exact).
+ */
+int qk_reduce_maxabs(const QkTensor *input, const QkTensor *output, int axis, int dtype, void *stream);
 
 /*
  * Fused form of qk_compute_scales + qk_quantize with identical results: per block one

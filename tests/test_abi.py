@@ -95,8 +95,8 @@ def test_dtype_layout_alignment_and_null():
         quantize.launch_ref(CLIENT, fake((4, 32), 4), args["output"], args["scale"], args["out_scale"], sch,
                             ElemType.BF16)
     assert e.value.status == _ffi.QK_ERR_DTYPE
-    with pytest.raises(LaunchError) as e:  # transposed input
-        quantize.launch_ref(CLIENT, fake((4, 32), 4, strides=(1, 4)), args["output"], args["scale"],
+    with pytest.raises(LaunchError) as e:  # the quantized tensor must be contiguous (the float one may be strided)
+        quantize.launch_ref(CLIENT, fake((4, 32), 4), fake((4, 8), 4, strides=(1, 4)), args["scale"],
                             args["out_scale"], sch, ElemType.F32)
     assert e.value.status == _ffi.QK_ERR_LAYOUT
     with pytest.raises(LaunchError) as e:

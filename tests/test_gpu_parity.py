@@ -225,3 +225,47 @@ def test_per_tensor_routes_agree(fname, tuning):
                 torch.cuda.synchronize()
                 assert_bits_equal(to_numpy(dq, code_dtype(scheme)), want_codes, f"codes ws={ws_bytes}")
                 assert_bits_equal(to_numpy(ds, np.float32), want_scale, f"scale ws={ws_bytes}")
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+def test_strided_float_tensors(fname):
+    """Inputs of quantize / compute_scales and outputs of dequantize may be strided views
+    (transposed, sliced): the reference reads them through `linear_view`."""
+    import torch
+    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
+    from tests._util import code_dtype, elem_of, empty_device, to_device, to_numpy
+
+    F = FLOATS[fname]
+    H = TensorHandleRef.from_torch
+    client = ComputeClient.current()
+    for scheme in (QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([32])),
+                   QuantScheme(value=QuantValue.Q4S), QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native,
+                                                                  level=QuantLevel.block([2, 16]))):
+        base = random_tensor((96, 80), F, 88)
+        views = {"transposed": (to_device(base).t(), np.ascontiguousarray(base.T)),
+                 "sliced": (to_device(base)[8:72, 16:80], np.ascontiguousarray(base[8:72, 16:80]))}
+        for name, (dv, x) in views.items():
+            assert not dv.is_contiguous()
+            want_scale = O.compute_scales(x, scheme)
+            want_codes, want_out_scale = O.quantize(x, want_scale, scheme)
+            ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+            dscale = empty_device(want_scale.shape, F)
+            quantize.compute_scales(client, H(dv), H(dscale), scheme, elem_of(F), H(ws))
+            dq = empty_device(want_codes.shape, code_dtype(scheme))
+            dos = empty_device(want_out_scale.shape, np.float32)
+            quantize.launch_ref(client, H(dv), H(dq), H(dscale), H(dos), scheme, elem_of(F))
+            dq2 = empty_device(want_codes.shape, code_dtype(scheme))
+            dos2 = empty_device(want_out_scale.shape, np.float32)
+            quantize.launch_dynamic(client, H(dv), H(dq2), H(dos2), scheme, elem_of(F), H(ws))
+            # dequantize into a strided view of a larger buffer
+            big = torch.zeros((x.shape[0], 2 * x.shape[1]), dtype=dv.dtype, device="cuda")
+            dout = big[:, ::2]
+            dequantize.launch_ref(client, H(dq), H(dout), H(dos), scheme, elem_of(F))
+            torch.cuda.synchronize()
+            assert_bits_equal(to_numpy(dscale, F), want_scale, f"{name} scale")
+            assert_bits_equal(to_numpy(dq, code_dtype(scheme)), want_codes, f"{name} codes")
+            assert_bits_equal(to_numpy(dq2, code_dtype(scheme)), want_codes, f"{name} codes (fused)")
+            assert_bits_equal(to_numpy(dos2, np.float32), want_out_scale, f"{name} out_scale (fused)")
+            assert_bits_equal(to_numpy(dout.contiguous(), F), O.dequantize(want_codes, want_out_scale, scheme, F),
+                              f"{name} restored")
+            assert float(big[:, 1::2].float().abs().max()) == 0.0
