@@ -368,6 +368,91 @@ def run_gpu(args, workload):
         dist.destroy_process_group()
 
 
+def run_weight_set(args, per_tensor: bool):
+    """BASELINE config 5: the 225 bf16 matrices of a Llama-3-8B-shaped model (15 GB), q8 with
+    block-128 scales or per-tensor scales, whole tensors placed round-robin over the ranks (strong
+    scaling: the set is fixed).  One step = fused quantize + dequantize of every tensor a rank owns."""
+    import torch
+    import torch.distributed as dist
+
+    from cubek_b200 import (ComputeClient, ElemType, QuantLevel, QuantScheme, QuantStore, QuantValue, TensorHandleRef,
+                            dequantize, quantize)
+    from cubek_b200 import _ffi
+    from cubek_b200.shard import assign_round_robin
+    from cubek_b200.weights import llama3_8b_shapes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _ffi.lib()
+    level = QuantLevel.Tensor if per_tensor else QuantLevel.block([128])
+    scheme = QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32, level=level)
+    shapes = llama3_8b_shapes()
+    owned = assign_round_robin([r * c for _, r, c in shapes], world)[rank]
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED0004 + rank)
+    xs = [(torch.randn((shapes[i][1], shapes[i][2]), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+          for i in owned]
+    codes = [torch.empty(scheme.packed_shape(x.shape), dtype=torch.int32, device=dev) for x in xs]
+    scales = [torch.empty(scheme.scales_shape(x.shape), dtype=torch.float32, device=dev) for x in xs]
+    outs = [torch.empty_like(x) for x in xs]
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
+    H = TensorHandleRef.from_torch
+    client = ComputeClient.current()
+    qb = quantize.PreparedDynamicBatch(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], scheme,
+                                       ElemType.BF16, H(ws))
+    db = dequantize.PreparedBatch(client, [H(t) for t in codes], [H(t) for t in outs], [H(t) for t in scales], scheme,
+                                  ElemType.BF16)
+
+    def step():
+        qb()
+        db()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    before = lib.qk_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    barrier()
+    launches = lib.qk_launch_count() - before
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        n = sum(r * c for _, r, c in shapes)
+        nscales = len(shapes) if per_tensor else n // 128
+        q_bytes = n * 2 * (2 if per_tensor else 1) + n + nscales * 4
+        d_bytes = n + nscales * 4 + n * 2
+        ms = float(t.item()) / args.steps
+        value = (q_bytes + d_bytes) / ms / 1e6
+        peak, kind = measured_peak()
+        print(json.dumps({
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "tensors": len(shapes), "elements": n,
+                       "level": "tensor" if per_tensor else "block[128]", "value": "Q8S", "store": "U32",
+                       "placement": "whole tensors, largest first onto the least loaded rank",
+                       "api": "qk_quantize_dynamic_batch + qk_dequantize_batch", "distribution": "normal(0,0.02)"},
+            "pct_of_measured_peak": round(100 * value / world / peak, 1), "peak_source": f"{kind} copy bandwidth",
+            "gpu_launches": int(launches)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_e2e(args, workload, dev, local_rank, rank, world, xs):
     """Same metric through ``qk_roundtrip_host``: inputs in pinned host memory, codes + scales +
     restored tensor read back to pinned host memory, every step."""
@@ -443,6 +528,9 @@ def main():
 
     from cubek_b200.synthetic import WORKLOADS
 
+    if args.workload.startswith("llama3_8b_q8_") and args.impl != "reference":
+        run_weight_set(args, per_tensor=args.workload.endswith("tensor"))
+        return
     workload = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, workload)

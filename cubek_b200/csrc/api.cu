@@ -22,6 +22,22 @@ cudaError_t launch_block_scales_f32(const void *, void *, long long, int, float,
 cudaError_t launch_block_scales_f16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, float, float, const LaunchCfg &, cudaStream_t);
 
+cudaError_t launch_block_scales_2d_f32(const void *, void *, long long, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_2d_f16(const void *, void *, long long, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_2d_bf16(const void *, void *, long long, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
+
+cudaError_t launch_block_scales_2d(int fdt, const void *in, void *scale_out, long long rows, long long cols,
+                                   int block_rows, int block_cols, float range, float inv_range, const LaunchCfg &cfg,
+                                   cudaStream_t stream)
+{
+    switch (fdt) {
+    case QK_F32: return launch_block_scales_2d_f32(in, scale_out, rows, cols, block_rows, block_cols, range, inv_range, cfg, stream);
+    case QK_F16: return launch_block_scales_2d_f16(in, scale_out, rows, cols, block_rows, block_cols, range, inv_range, cfg, stream);
+    case QK_BF16: return launch_block_scales_2d_bf16(in, scale_out, rows, cols, block_rows, block_cols, range, inv_range, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
 cudaError_t launch_quantize_tensor_f32(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_quantize_tensor_f16(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_quantize_tensor_bf16(int, QuantTensorArgs &, int, const LaunchCfg &, cudaStream_t);
@@ -187,6 +203,9 @@ struct Geometry {
     long long shape[QK_MAX_RANK];    // unpacked shape
     bool per_tensor = true;
     bool last_dim_blocks = false;    // blocks only along the last dim, rows split evenly
+    bool blocks_2d = false;          // [block_rows, B] tiles over the last two dims (cols split evenly)
+    long long block_rows = 1;        // tile extent along dim rank-2
+    long long cols = 0;              // extent of the last dim
     long long B = 0;                 // block extent along the last dim
     long long nscales = 1;
 };
@@ -217,6 +236,15 @@ static int build_geometry(Geometry &g, const QkScheme *s, const QkTensor *unpack
         g.B = g.block[g.rank - 1];
         g.last_dim_blocks = (g.shape[g.rank - 1] % g.B == 0);
         for (int d = 0; d < g.rank - 1; ++d) g.last_dim_blocks = g.last_dim_blocks && g.block[d] == 1;
+        g.cols = g.shape[g.rank - 1];
+        if (!g.last_dim_blocks && g.rank >= 2 && g.block[g.rank - 2] > 1 && g.cols % g.B == 0) {
+            // Tiles over the last two dims; leading dims may be flattened into rows only if no tile
+            // would straddle two matrices.
+            bool ok = (g.rank == 2) || (g.shape[g.rank - 2] % g.block[g.rank - 2] == 0);
+            for (int d = 0; d < g.rank - 2; ++d) ok = ok && g.block[d] == 1;
+            g.blocks_2d = ok;
+            g.block_rows = g.block[g.rank - 2];
+        }
         for (int d = 0; d < g.rank; ++d) g.nscales *= (g.shape[d] + g.block[d] - 1) / g.block[d];
     }
     return QK_OK;
@@ -268,7 +296,7 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
     const int esz = dtype_size(fdt);
     if (!aligned(in->ptr, 16) || !is_contiguous(in)) return -2;
     if (!g.per_tensor) {
-        if (!g.last_dim_blocks) return -2;
+        if (!g.last_dim_blocks && !g.blocks_2d) return -2;
         if (scale && !is_contiguous(scale)) return -2;
         if (out_scale && !is_contiguous(out_scale)) return -2;
     }
@@ -285,10 +313,23 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
         if (g.per_tensor) return -1;
         if (g.B % U != 0) continue;
         const int lg = log2_exact(g.B / U);
-        if (lg < 0 || lg > 5) continue;
+        if (lg < 0 || (lg > 5 && !g.blocks_2d)) continue;
+        if (g.blocks_2d && g.n / U >= (1ll << 31)) continue;
         return lg;
     }
     return -2;
+}
+
+// Tile geometry for the streaming kernels (units of `unit_elems` elements).
+static Blocks2D make_blocks2d(const Geometry &g, int unit_elems, int lg)
+{
+    Blocks2D b;
+    b.enabled = g.blocks_2d ? 1 : 0;
+    b.units_per_row = make_fastdiv((unsigned)(g.blocks_2d ? g.cols / unit_elems : 1));
+    b.block_rows = make_fastdiv((unsigned)(g.blocks_2d ? g.block_rows : 1));
+    b.scales_per_row = (unsigned)(g.blocks_2d ? g.cols / g.B : 1);
+    b.lg_units_per_block_col = lg < 0 ? 0 : lg;
+    return b;
 }
 
 static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values, const QkTensor *out,
@@ -297,7 +338,7 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
     if (!aligned(out->ptr, 16) || !is_contiguous(out)) return -2;
-    if (!g.per_tensor && (!g.last_dim_blocks || !is_contiguous(params))) return -2;
+    if (!g.per_tensor && ((!g.last_dim_blocks && !g.blocks_2d) || !is_contiguous(params))) return -2;
     const int candidates[2] = {64, min_dequant_bytes(fdt, g.kind)};
     for (int ci = 0; ci < 2; ++ci) {
         const int ob = candidates[ci];
@@ -310,6 +351,7 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
         if (g.B % E != 0) continue;
         const int lg = log2_exact(g.B / E);
         if (lg < 0) continue;
+        if (g.blocks_2d && g.n / E >= (1ll << 31)) continue;
         return lg;
     }
     return -2;
@@ -321,12 +363,12 @@ struct QuantBatch {
     QuantArgs a;
     int fdt = -1, kind = -1, unit_bytes = 0;
     bool dyn = false, clamp = false;
-    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; }
+    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; }
 };
 struct DequantBatch {
     DequantArgs a;
     int fdt = -1, kind = -1, out_bytes = 0;
-    DequantBatch() { a.ntensors = 0; a.nunits = 0; }
+    DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; }
 };
 
 static int flush_quant(QuantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
@@ -560,6 +602,12 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
         count_launch();
         return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / per16, lg, range, 1.0f / range, cfg, stream));
     }
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && contiguous && g.blocks_2d && g.B % per16 == 0 && aligned(input->ptr, 16) &&
+        is_contiguous(scale)) {
+        count_launch();
+        return cuda_status(launch_block_scales_2d(input_dtype, input->ptr, scale->ptr, g.n / g.cols, g.cols,
+                                                  (int)g.block_rows, (int)g.B, range, 1.0f / range, cfg, stream));
+    }
     GeneralScalesArgs a;
     fill_layout(a.layout, g, scale, nullptr, input);
     a.in = input->ptr;
@@ -759,7 +807,23 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     const LaunchCfg cfg = current_cfg();
     int unit_bytes = 0;
     const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale, &unit_bytes);
-    if (lg >= -1) {
+    // Tiles over two dims cannot be reduced inside one thread group: the fused form first writes the
+    // tile scales (one warp per tile) into the workspace, then runs the given-scale kernel.
+    const void *tile_scales = nullptr;
+    if (lg >= -1 && g.blocks_2d && dynamic) {
+        const int per16 = 16 / fsize;
+        if (!gen_scales) return QK_ERR_WORKSPACE;
+        if (g.B % per16 == 0) {
+            if (batch && (rc = flush_quant(*batch, cfg, stream))) return rc;
+            count_launch();
+            const cudaError_t e = launch_block_scales_2d(input_dtype, input->ptr, gen_scales, g.n / g.cols, g.cols,
+                                                         (int)g.block_rows, (int)g.B, hi - lo, 1.0f / (hi - lo), cfg, stream);
+            if (e != cudaSuccess) return cuda_status(e);
+            tile_scales = gen_scales;
+            dynamic = false;
+        }
+    }
+    if (lg >= -1 && !(g.blocks_2d && dynamic)) {
         QuantBatch local;
         QuantBatch &b = batch ? *batch : local;
         const bool symmetric = (lo == -hi);
@@ -768,7 +832,8 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         const int a32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
         // A tensor joins the pending launch only if it needs the very same kernel and constants;
         // per-tensor absmax cells must be consecutive (the kernel indexes them by tensor).
-        const bool joins = b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == input_dtype &&
+        const bool joins = !g.blocks_2d && !b.a.b2.enabled &&   // tile geometry is per launch
+                           b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == input_dtype &&
                            b.kind == g.kind && b.unit_bytes == unit_bytes && b.dyn == dynamic && b.clamp == clamp &&
                            b.a.lg_units_per_block == lg && b.a.param == scheme->param && b.a.lo == lo && b.a.hi == hi &&
                            b.a.force_exact == cfg.force_exact &&
@@ -790,11 +855,12 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             b.a.inv_range = 1.0f / (hi - lo);
             b.a.force_exact = cfg.force_exact;
             b.a.aligned32 = 1;
+            b.a.b2 = make_blocks2d(g, unit_bytes / fsize, lg);
         }
         QuantTensor &t = b.a.t[b.a.ntensors];
         t.in = input->ptr;
         t.out = output->ptr;
-        t.scale_in = scale ? scale->ptr : nullptr;
+        t.scale_in = tile_scales ? tile_scales : (scale ? scale->ptr : nullptr);
         t.out_scale = out_scale->ptr;
         b.a.nunits += nunits;
         t.unit_end = b.a.nunits;
@@ -879,7 +945,8 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     if (lg >= -1) {
         DequantBatch local;
         DequantBatch &b = batch ? *batch : local;
-        const bool joins = b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == output_dtype &&
+        const bool joins = !g.blocks_2d && !b.a.b2.enabled &&
+                           b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == output_dtype &&
                            b.kind == g.kind && b.out_bytes == out_bytes && b.a.lg_units_per_block == lg &&
                            b.a.param == scheme->param;
         if (!joins) {
@@ -890,6 +957,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
             b.a.lg_units_per_block = lg;
             b.a.param = scheme->param;
             b.a.aligned32 = 1;
+            b.a.b2 = make_blocks2d(g, out_bytes / fsize, lg);
         }
         DequantTensor &t = b.a.t[b.a.ntensors];
         t.values = values->ptr;

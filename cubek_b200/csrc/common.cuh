@@ -261,6 +261,46 @@ static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int 
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- 2-D blocks ---------------------------------------------------------------------------------
+// Division of a 31-bit unsigned number by a run-time constant with one multiply-high.
+struct FastDiv {
+    unsigned mul, shift, div;
+};
+static inline FastDiv make_fastdiv(unsigned d)
+{
+    FastDiv f;
+    f.div = d;
+    unsigned s = 0;
+    while ((1ull << s) < d) ++s;
+    f.shift = s;
+    f.mul = (unsigned)((((1ull << s) - d) << 32) / d + 1);
+    return f;
+}
+__device__ __forceinline__ unsigned fastdiv(unsigned n, const FastDiv &f)
+{
+    return (unsigned)(((unsigned long long)__umulhi(n, f.mul) + n) >> f.shift);
+}
+
+// Scale geometry of a matrix quantized in [block_rows, block_cols] tiles (the layout quantized
+// matmul inputs use, crates/cubek-matmul/src/components/global/memory/layout.rs:213-262): units are
+// runs along a row; unit `u` lies in row u / units_per_row and block column (u % units_per_row) >> lg.
+struct Blocks2D {
+    int enabled;
+    FastDiv units_per_row;
+    FastDiv block_rows;
+    unsigned scales_per_row;
+    int lg_units_per_block_col;
+};
+// Scale index of unit `u`, and whether the unit is the first of its tile.
+__device__ __forceinline__ unsigned blocks2d_scale_index(const Blocks2D &b, unsigned u, bool *is_start)
+{
+    const unsigned row = fastdiv(u, b.units_per_row);
+    const unsigned cu = u - row * b.units_per_row.div;
+    const unsigned rb = fastdiv(row, b.block_rows);
+    *is_start = (row - rb * b.block_rows.div == 0) && ((cu & ((1u << b.lg_units_per_block_col) - 1u)) == 0);
+    return rb * b.scales_per_row + (cu >> b.lg_units_per_block_col);
+}
+
 // ---- launch bookkeeping -----------------------------------------------------------------
 
 struct LaunchCfg {

@@ -31,6 +31,7 @@ struct DequantArgs {
     int ntensors;
     long long nunits;        // dequant units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
+    Blocks2D b2;             // [rows, cols] tiles instead of runs
     int param;               // QkParam
     int aligned32;           // every output base 32-byte aligned (256-bit stores allowed)
 };
@@ -204,7 +205,9 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                     }
                 }
                 // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
-                const long long si = (lg < 0) ? 0 : (li >> lg);
+                bool unused;
+                const long long si = a.b2.enabled ? (long long)blocks2d_scale_index(a.b2, (unsigned)li, &unused)
+                                                  : ((lg < 0) ? 0 : (li >> lg));
                 if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(T.params) + si));
                 else s[k] = round_to<FDT>(load_dyn(T.params, a.param, si));
             } else {

@@ -17,4 +17,10 @@ cudaError_t launch_quantize_tensor_bf16(int kind, QuantTensorArgs &args, int par
 {
     return launch_quantize_tensor_t<QK_BF16>(kind, args, partials_capacity, cfg, stream);
 }
+cudaError_t launch_block_scales_2d_bf16(const void *in, void *scale_out, long long rows, long long cols, int block_rows,
+                                      int block_cols, float range, float inv_range, const LaunchCfg &cfg,
+                                      cudaStream_t stream)
+{
+    return launch_block_scales_2d_t<QK_BF16>(in, scale_out, rows, cols, block_rows, block_cols, range, inv_range, cfg, stream);
+}
 }  // namespace qk

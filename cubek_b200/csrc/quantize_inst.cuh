@@ -115,4 +115,18 @@ static cudaError_t launch_block_scales_t(const void *in, void *scale_out, long l
                          range, inv_range);
 }
 
+template <int FDT>
+static cudaError_t launch_block_scales_2d_t(const void *in, void *scale_out, long long rows, long long cols,
+                                            int block_rows, int block_cols, float range, float inv_range,
+                                            const LaunchCfg &cfg, cudaStream_t stream)
+{
+    const long long tiles = ((rows + block_rows - 1) / block_rows) * (cols / block_cols);
+    long long need = (tiles + 7) / 8;   // 8 warps per CTA, one tile per warp
+    const long long cap = (long long)cfg.sm_count * 8;
+    if (need > cap) need = cap;
+    if (need < 1) need = 1;
+    return launch_kernel(block_scales_2d_kernel<FDT>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, rows, cols,
+                         block_rows, block_cols, range, inv_range);
+}
+
 }  // namespace qk

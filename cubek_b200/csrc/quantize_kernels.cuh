@@ -46,6 +46,7 @@ struct QuantArgs {
                              // (overrides scale_in)
     long long nunits;        // units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
+    Blocks2D b2;             // [rows, cols] tiles instead of runs (given-scale form only)
     int param;               // QkParam of out_scale
     float lo, hi, range;     // clamp bounds, hi - lo
     float inv_range;         // RN(1 / range), computed on the host
@@ -481,32 +482,41 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
             const long long li = lidx[k];
 
             float scale_f;
+            long long sidx = 0;      // index of the unit's scale
+            bool starts = false;     // the unit is the first of its block
             if constexpr (DYN) {
+                sidx = li >> lg;
+                starts = (li & ((1ll << lg) - 1)) == 0;
                 float amax = unit_absmax<FDT, RAW>(raw[k]);
                 // Blocks are aligned runs of 2^lg lanes; every lane of the warp takes part.
 #pragma unroll
                 for (int m = 1; m < 32; m <<= 1)
                     if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
                 scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
-            } else if (lg < 0) {
+            } else if (lg < 0 && !a.b2.enabled) {
                 if (scale_ti != tk[k]) {
                     scale_ti = tk[k];
                     tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * a.absmax[scale_ti], a.range, a.inv_range))
                                             : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
                 }
                 scale_f = tensor_scale;
+            } else if (a.b2.enabled) {
+                sidx = blocks2d_scale_index(a.b2, (unsigned)li, &starts);
+                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
             } else {
-                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[li >> lg]) : 1.0f;
+                sidx = li >> lg;
+                starts = (li & ((1ll << lg) - 1)) == 0;
+                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
             }
             // write_scale: the scale is cast to the param type, stored, and that value (cast
             // back to F) is the divisor (crates/cubek-quant/src/quantize.rs:83-98).
             const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
             const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
             if (valid) {
-                if (lg < 0) {
+                if (lg < 0 && !a.b2.enabled) {
                     if (li == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
-                } else if ((li & ((1ll << lg) - 1)) == 0) {
-                    store_dyn(T.out_scale, a.param, li >> lg, s_fs);
+                } else if (starts) {
+                    store_dyn(T.out_scale, a.param, sidx, s_fs);
                 }
             }
             uint32_t w[OW];
@@ -675,11 +685,50 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
     }
 }
 
+// -------------------------------------------------------------------------------------
+// Scales of [block_rows, block_cols] tiles: one warp per tile, 128-bit loads along the rows of
+// the tile, shuffle reduction.  Tiles at the bottom edge are clipped.
+// -------------------------------------------------------------------------------------
+template <int FDT>
+__global__ void __launch_bounds__(256) block_scales_2d_kernel(const void *in_, void *scale_out, long long rows,
+                                                              long long cols, int block_rows, int block_cols,
+                                                              float range, float inv_range)
+{
+    using F = typename ElemOf<FDT>::type;
+    constexpr int PER = FInfo<FDT>::PER16;
+    const char *in = static_cast<const char *>(in_);
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const long long ncb = cols / block_cols, nrb = (rows + block_rows - 1) / block_rows;
+    const int chunks_per_row = block_cols / PER;
+    pdl_entry();
+    for (long long t = warp; t < nrb * ncb; t += nwarps) {
+        const long long rb = t / ncb, cb = t % ncb;
+        const long long r0 = rb * block_rows;
+        const int nr = (int)((rows - r0 < block_rows) ? rows - r0 : block_rows);
+        float amax = 0.0f;
+        for (int c = lane; c < nr * chunks_per_row; c += 32) {
+            const int r = c / chunks_per_row, cc = c % chunks_per_row;
+            uint32_t raw[4];
+            load_unit<16>(raw, in + ((r0 + r) * cols + cb * block_cols + (long long)cc * PER) * FInfo<FDT>::SIZE, false);
+            amax = fmaxf(amax, unit_absmax<FDT, 4>(raw));
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        if (lane == 0)
+            static_cast<F *>(scale_out)[t] = static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
+    }
+}
+
 // Host-side launchers, one translation unit per float type.
 cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
                                 float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_block_scales_2d(int fdt, const void *in, void *scale_out, long long rows, long long cols,
+                                   int block_rows, int block_cols, float range, float inv_range, const LaunchCfg &cfg,
+                                   cudaStream_t stream);
 // Cooperative per-tensor launch (64-byte units).  `partials_capacity` floats are available at
 // args.partials; returns cudaErrorInvalidValue if the resident grid needs more.
 cudaError_t launch_quantize_tensor(int fdt, int kind, QuantTensorArgs &args, int partials_capacity,
