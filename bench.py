@@ -509,7 +509,7 @@ def run_e2e(args, workload, dev, local_rank, rank, world, xs):
     return {"value": round((q_bytes + d_bytes) * nb * steps * world / secs / 1e9, 2), "unit": "GB/s",
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
             "tensors_per_step": nb, "ms_per_step": round(secs / steps * 1e3, 3),
-            "api": "qk_roundtrip_host (pinned host buffers, 3-slot pipelined copies)"}
+            "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies)"}
 
 
 def main():

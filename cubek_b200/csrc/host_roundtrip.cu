@@ -1,6 +1,6 @@
 // Round trip through host buffers: slices of whole rows travel host -> device, are quantized
 // (fused absmax + scale + pack) and dequantized on the device, and codes, scales and restored
-// values travel back.  Three staging slots on three streams overlap the copies in both
+// values travel back.  Four staging slots on four streams overlap the copies in both
 // directions with the kernels.  This is the call a host-resident caller of the reference's
 // test flow makes (create_tensor_from_slice -> quantize -> dequantize -> read_one_tensor,
 // crates/cubek-quant/tests/suite/symmetric.rs:32-127), as one entry point.
@@ -11,11 +11,12 @@
 
 namespace {
 
-constexpr int kSlots = 3;
-constexpr size_t kSliceTargetBytes = 32u << 20;  // input bytes per slice
+constexpr int kSlots = 4;
+constexpr size_t kSliceTargetBytes = 8u << 20;  // input bytes per slice: small enough that filling and
+                                                // draining the pipeline costs little per call
 
 struct DeviceStreams {
-    cudaStream_t stream[kSlots] = {nullptr, nullptr, nullptr};
+    cudaStream_t stream[kSlots] = {};
     bool ready = false;
 };
 DeviceStreams g_streams[64];

@@ -127,4 +127,4 @@ def test_host_roundtrip_staging_size():
     sch = QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([32]))
     t = _ffi.CTensor(fake((14336, 4096), 2))
     n = _ffi.lib().qk_host_roundtrip_staging_bytes(t.ref(), _ffi.c_scheme(sch), int(ElemType.BF16))
-    assert 3 * 32 * 2**20 < n < 3 * 96 * 2**20
+    assert 4 * 8 * 2**20 < n < 4 * 24 * 2**20
