@@ -73,3 +73,61 @@ def test_row_shards_match_single_gpu(tmp_path):
     world = min(torch.cuda.device_count(), 8)
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
+
+
+def _nccl_rank_main(rank, world, port, out_dir):
+    """`qk_allreduce_max_f32` on a communicator the caller owns (created here through ctypes on the
+    NCCL library already loaded in the process)."""
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    from cubek_b200 import _ffi
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.zeros(1, device="cuda")                      # CUDA context
+        nccl = None
+        for line in open("/proc/self/maps"):
+            if "libnccl.so" in line:
+                nccl = C.CDLL(line.split()[-1])
+                break
+        if nccl is None:
+            nccl = C.CDLL("libnccl.so.2")
+
+        class UniqueId(C.Structure):
+            _fields_ = [("internal", C.c_char * 128)]
+
+        uid = UniqueId()
+        if rank == 0:
+            assert nccl.ncclGetUniqueId(C.byref(uid)) == 0
+        t = torch.tensor(list(bytes(uid)), dtype=torch.uint8)
+        dist.broadcast(t, 0)
+        C.memmove(C.byref(uid), bytes(t.tolist()), 128)
+        comm = C.c_void_p()
+        nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+        assert nccl.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
+        buf = torch.tensor([1.0 + rank, 100.0 - rank, 0.0, float(rank == world - 1) * 7.5], device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = _ffi.lib().qk_allreduce_max_f32(buf.data_ptr(), buf.numel(), comm, stream)
+        assert rc == 0, _ffi.strerror(rc)
+        torch.cuda.synchronize()
+        assert buf.tolist() == [float(world), 100.0, 0.0, 7.5], buf.tolist()
+        nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+        nccl.ncclCommDestroy(comm)
+        open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_allreduce_max_entry_point_on_a_caller_owned_communicator(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_nccl_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

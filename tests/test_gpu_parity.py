@@ -269,3 +269,45 @@ def test_strided_float_tensors(fname):
             assert_bits_equal(to_numpy(dout.contiguous(), F), O.dequantize(want_codes, want_out_scale, scheme, F),
                               f"{name} restored")
             assert float(big[:, 1::2].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("offset_bytes", [16, 8, 4, 48])
+def test_odd_base_alignments(fname, offset_bytes):
+    """Tensors that start 4, 8, 16 or 48 bytes into an allocation: 256-bit accesses are not allowed
+    (128-bit route), or not even those (general kernels).  Same bits either way."""
+    import torch
+    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
+    from tests._util import code_dtype, elem_of, to_numpy
+
+    F = FLOATS[fname]
+    H = TensorHandleRef.from_torch
+    client = ComputeClient.current()
+    shape = (64, 512)
+    n = shape[0] * shape[1]
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[fname]
+    esz = np.dtype(F).itemsize
+    for scheme in (QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([32])),
+                   QuantScheme(value=QuantValue.Q8S), QuantScheme(value=QuantValue.Q2S, level=QuantLevel.block([64]))):
+        x = random_tensor(shape, F, 91)
+        want_codes, want_scale = O.quantize_dynamic(x, scheme)
+        want_restored = O.dequantize(want_codes, want_scale, scheme, F)
+        raw_in = torch.zeros(n * esz + 256, dtype=torch.uint8, device="cuda")
+        dx = raw_in[offset_bytes: offset_bytes + n * esz].view(tdt).view(shape)
+        dx.copy_(torch.from_numpy(x.view(np.int16) if fname == "bf16" else x).cuda().view(tdt))
+        ncode = want_codes.size * 4
+        raw_codes = torch.zeros(ncode + 256, dtype=torch.uint8, device="cuda")
+        dq = raw_codes[offset_bytes: offset_bytes + ncode].view(torch.int32).view(want_codes.shape)
+        ds = torch.zeros(want_scale.shape, dtype=torch.float32, device="cuda")
+        raw_out = torch.zeros(n * esz + 256, dtype=torch.uint8, device="cuda")
+        do = raw_out[offset_bytes: offset_bytes + n * esz].view(tdt).view(shape)
+        ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+        quantize.launch_dynamic(client, H(dx), H(dq), H(ds), scheme, elem_of(F), H(ws))
+        dequantize.launch_ref(client, H(dq), H(do), H(ds), scheme, elem_of(F))
+        torch.cuda.synchronize()
+        assert_bits_equal(to_numpy(dq.contiguous(), np.uint32), want_codes, "codes")
+        assert_bits_equal(to_numpy(ds, np.float32), want_scale, "scales")
+        assert_bits_equal(to_numpy(do.contiguous(), F), want_restored, "restored")
+        # nothing outside the views was touched
+        assert int(raw_codes[:offset_bytes].sum()) == 0 and int(raw_codes[offset_bytes + ncode:].sum()) == 0
+        assert int(raw_out[:offset_bytes].sum()) == 0 and int(raw_out[offset_bytes + n * esz:].sum()) == 0
