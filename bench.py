@@ -32,8 +32,7 @@ SPEC_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of each kernel on a
-# 32768-row case, scaled by rows to the bench tensor (profiles/quantize_kernel_q4_block32_bf16.md,
-# profiles/dequantize_kernel_q4_block32_bf16.md).
+# 32768-row case, scaled by rows to the bench tensor (summaries of those captures are kept under profiles/).
 NCU_TRAFFIC_BYTES = {
     "q4_block32_bf16_14336x4096": {"quantize_dynamic": 145.2e6, "dequantize": 130.4e6},   # per tensor
 }

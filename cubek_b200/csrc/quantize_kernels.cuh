@@ -564,23 +564,23 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
     const long long first = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x;
     const long long niter = (a.nunits + stride - 1) / stride;
 
-    // ---- pass 1: absmax ------------------------------------------------------------------
+    // ---- pass 1: absmax.  The units of the last iteration stay in registers for pass 2. -----------
     float amax = 0.0f;
+    uint32_t last[UNR][RAW];
     for (long long it = 0; it < niter; ++it) {
         const long long base = it * stride + first;
-        uint32_t raw[UNR][RAW];
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             if (idx < a.nunits) {
-                load_unit<UB>(raw[k], in + idx * UB, aligned32);
+                load_unit<UB>(last[k], in + idx * UB, aligned32);
             } else {
 #pragma unroll
-                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+                for (int i = 0; i < RAW; ++i) last[k][i] = 0u;
             }
         }
 #pragma unroll
-        for (int k = 0; k < UNR; ++k) amax = fmaxf(amax, unit_absmax<FDT, RAW>(raw[k]));
+        for (int k = 0; k < UNR; ++k) amax = fmaxf(amax, unit_absmax<FDT, RAW>(last[k]));
     }
     __shared__ float warp_max[8];
     __shared__ float block_max;
@@ -619,26 +619,28 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
     if (blockIdx.x == 0 && threadIdx.x == 0) store_dyn(a.out_scale, a.param, 0, s_fs);
     const bool fast = kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s);
 
-    // ---- pass 2: quantize, last iteration first ---------------------------------------------
+    // ---- pass 2: quantize, last iteration first (its units are still in registers; the ones
+    // before it are the most recently read, hence the most likely to be in L2) ----------------------
     for (long long it = niter - 1; it >= 0; --it) {
         const long long base = it * stride + first;
-        uint32_t raw[UNR][RAW];
+        if (it != niter - 1) {
 #pragma unroll
-        for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            if (idx < a.nunits) {
-                load_unit<UB>(raw[k], in + idx * UB, aligned32);
-            } else {
+            for (int k = 0; k < UNR; ++k) {
+                const long long idx = base + (long long)k * blockDim.x;
+                if (idx < a.nunits) {
+                    load_unit<UB>(last[k], in + idx * UB, aligned32);
+                } else {
 #pragma unroll
-                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+                    for (int i = 0; i < RAW; ++i) last[k][i] = 0u;
+                }
             }
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             uint32_t w[OW];
-            if (fast) quantize_unit_fast<FDT, KIND, UB, true, false>(raw[k], s, a.lo, a.hi, w);
-            else quantize_unit_exact<FDT, KIND, UB>(raw[k], s, a.lo, a.hi, w);
+            if (fast) quantize_unit_fast<FDT, KIND, UB, true, false>(last[k], s, a.lo, a.hi, w);
+            else quantize_unit_exact<FDT, KIND, UB>(last[k], s, a.lo, a.hi, w);
             if (idx < a.nunits) store_words<OW>(out + idx * OW, w, aligned32);
         }
     }
