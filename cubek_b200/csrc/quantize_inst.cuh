@@ -121,12 +121,14 @@ static cudaError_t launch_block_scales_2d_t(const void *in, void *scale_out, lon
                                             const LaunchCfg &cfg, cudaStream_t stream)
 {
     const long long tiles = ((rows + block_rows - 1) / block_rows) * (cols / block_cols);
-    long long need = (tiles + 7) / 8;   // 8 warps per CTA, one tile per warp
+    const long long chunks = (long long)block_rows * block_cols * ((FDT == QK_F32) ? 4 : 2) / 16;
+    const int cta_per_tile = chunks >= 1024 ? 1 : 0;
+    long long need = cta_per_tile ? tiles : (tiles + 7) / 8;   // else 8 warps per CTA, one tile per warp
     const long long cap = (long long)cfg.sm_count * 8;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
     return launch_kernel(block_scales_2d_kernel<FDT>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, rows, cols,
-                         block_rows, block_cols, range, inv_range);
+                         block_rows, block_cols, range, inv_range, cta_per_tile);
 }
 
 }  // namespace qk

@@ -688,37 +688,62 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
 }
 
 // -------------------------------------------------------------------------------------
-// Scales of [block_rows, block_cols] tiles: one warp per tile, 128-bit loads along the rows of
-// the tile, shuffle reduction.  Tiles at the bottom edge are clipped.
+// Scales of [block_rows, block_cols] tiles.  A tile is reduced by one warp (small tiles) or by a
+// whole CTA (tiles of 1024 chunks = 16 KB and more), with four independent 128-bit loads in
+// flight per thread along the rows of the tile.  Tiles at the bottom edge are clipped.
 // -------------------------------------------------------------------------------------
 template <int FDT>
 __global__ void __launch_bounds__(256) block_scales_2d_kernel(const void *in_, void *scale_out, long long rows,
                                                               long long cols, int block_rows, int block_cols,
-                                                              float range, float inv_range)
+                                                              float range, float inv_range, int cta_per_tile)
 {
     using F = typename ElemOf<FDT>::type;
     constexpr int PER = FInfo<FDT>::PER16;
     const char *in = static_cast<const char *>(in_);
     const int lane = threadIdx.x & 31;
-    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int group = cta_per_tile ? 256 : 32;                       // threads that share a tile
+    const int rank_in_group = cta_per_tile ? threadIdx.x : lane;
+    const long long team = cta_per_tile ? blockIdx.x : (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const long long nteams = cta_per_tile ? gridDim.x : (((long long)gridDim.x * blockDim.x) >> 5);
     const long long ncb = cols / block_cols, nrb = (rows + block_rows - 1) / block_rows;
     const int chunks_per_row = block_cols / PER;
+    __shared__ float warp_max[8];
     pdl_entry();
-    for (long long t = warp; t < nrb * ncb; t += nwarps) {
+    for (long long t = team; t < nrb * ncb; t += nteams) {
         const long long rb = t / ncb, cb = t % ncb;
         const long long r0 = rb * block_rows;
         const int nr = (int)((rows - r0 < block_rows) ? rows - r0 : block_rows);
+        const int nchunks = nr * chunks_per_row;
         float amax = 0.0f;
-        for (int c = lane; c < nr * chunks_per_row; c += 32) {
-            const int r = c / chunks_per_row, cc = c % chunks_per_row;
-            uint32_t raw[4];
-            load_unit<16>(raw, in + ((r0 + r) * cols + cb * block_cols + (long long)cc * PER) * FInfo<FDT>::SIZE, false);
-            amax = fmaxf(amax, unit_absmax<FDT, 4>(raw));
+        for (int c0 = rank_in_group; c0 < nchunks; c0 += 4 * group) {
+            uint32_t raw[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + group * j;
+                if (c < nchunks) {
+                    const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+                    load_unit<16>(raw[j], in + ((r0 + r) * cols + cb * block_cols + (long long)cc * PER) * FInfo<FDT>::SIZE,
+                                  false);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) raw[j][i] = 0u;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) amax = fmaxf(amax, unit_absmax<FDT, 4>(raw[j]));
         }
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-        if (lane == 0)
+        if (cta_per_tile) {
+            __syncthreads();   // warp_max of the previous tile has been read
+            if (lane == 0) warp_max[threadIdx.x >> 5] = amax;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
+            }
+        }
+        if (rank_in_group == 0)
             static_cast<F *>(scale_out)[t] = static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
     }
 }
