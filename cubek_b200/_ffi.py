@@ -29,7 +29,8 @@ QK_ERR_CUDA = 1000
 # Status codes that stand for a `panic!` / `assert!` in the reference.
 PANIC_CLASS = (QK_ERR_UNSUPPORTED_SCHEME, QK_ERR_BLOCK_SIZE, QK_ERR_SHAPE, QK_ERR_DTYPE)
 
-TUNE_THREADS, TUNE_CTAS_PER_SM, TUNE_FORCE_EXACT, TUNE_FORCE_GENERAL, TUNE_PDL, TUNE_QUANT_WAVES, TUNE_DEQUANT_WAVES = range(7)
+(TUNE_THREADS, TUNE_CTAS_PER_SM, TUNE_FORCE_EXACT, TUNE_FORCE_GENERAL, TUNE_PDL, TUNE_QUANT_WAVES, TUNE_DEQUANT_WAVES,
+ TUNE_COOP_TENSOR, TUNE_STAGED) = range(9)
 
 
 class QkScheme(C.Structure):
@@ -88,6 +89,7 @@ _SIGNATURES = {
     "qk_strerror": (C.c_char_p, [C.c_int]),
     "qk_version": (C.c_char_p, []),
     "qk_launch_count": (C.c_uint64, []),
+    "qk_device_error": (C.c_int, [C.POINTER(C.c_int)]),
     "qk_set_tuning": (None, [C.c_int, C.c_int]),
     "qk_get_tuning": (C.c_int, [C.c_int]),
 }

@@ -77,10 +77,27 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
-       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_COUNT = 8 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}};
+       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_COUNT = 9 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
+
+// Flag the staged kernels raise when a bounded mbarrier wait gives up.  One per device image of this
+// translation unit; the host needs its device address (once per device, with that device current).
+static __device__ int g_stage_error;
+static std::atomic<int *> g_stage_error_addr[64];
+
+int *stage_error_flag()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    int *p = g_stage_error_addr[dev].load();
+    if (p) return p;
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_stage_error) != cudaSuccess) return nullptr;
+    g_stage_error_addr[dev].store(static_cast<int *>(addr));
+    return static_cast<int *>(addr);
+}
 
 static int sm_count_of_current_device()
 {
@@ -101,6 +118,7 @@ static LaunchCfg current_cfg()
     c.force_exact = g_tune[TUNE_FORCE_EXACT].load();
     c.pdl = g_tune[TUNE_PDL].load();
     c.quant_waves = g_tune[TUNE_QUANT_WAVES].load();
+    c.staged = g_tune[TUNE_STAGED].load();
     c.dequant_waves = g_tune[TUNE_DEQUANT_WAVES].load();
     c.sm_count = sm_count_of_current_device();
     return c;
@@ -767,6 +785,15 @@ const char *qk_version(void) { return "cubek-quant-b200 0.1.0 (sm_100a)"; }
 
 uint64_t qk_launch_count(void) { return g_launches.load(); }
 
+int qk_device_error(int *flag_out)
+{
+    if (!flag_out) return QK_ERR_NULL;
+    int *p = stage_error_flag();
+    if (!p) return QK_ERR_CUDA;
+    const cudaError_t e = cudaMemcpy(flag_out, p, sizeof(int), cudaMemcpyDeviceToHost);   // synchronises
+    return cuda_status(e);
+}
+
 void qk_set_tuning(int key, int value)
 {
     if (key >= 0 && key < TUNE_COUNT) g_tune[key].store(value);
@@ -864,6 +891,8 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         t.out_scale = out_scale->ptr;
         b.a.nunits += nunits;
         t.unit_end = b.a.nunits;
+        const long long tile_units = QK_TILE_BYTES / unit_bytes;
+        t.tile_end = (b.a.ntensors ? b.a.t[b.a.ntensors - 1].tile_end : 0) + (nunits + tile_units - 1) / tile_units;
         b.a.aligned32 &= a32;
         b.a.ntensors += 1;
         return batch ? QK_OK : flush_quant(b, cfg, stream);

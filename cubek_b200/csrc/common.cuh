@@ -311,6 +311,7 @@ struct LaunchCfg {
     int sm_count;
     int force_exact;  // 1: every unit takes the reference-arithmetic route
     int pdl;          // 1: launch with programmatic stream serialization
+    int staged;       // 1: quantize reads its input through the shared-memory bulk-copy pipeline
 };
 
 }  // namespace qk

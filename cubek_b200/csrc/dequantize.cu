@@ -10,11 +10,11 @@ template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int th
     return n;
 }
 
-template <int FDT, int KIND, int OB>
-static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+template <int FDT, int KIND, int OB, bool TILES>
+static cudaError_t launch_tiles(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
     const int threads = cfg.threads;
-    static const int occ256 = resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB>, 256);
+    static const int occ256 = resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB, TILES>, 256);
     // The write-heavy kernel runs faster as many short CTAs than as one persistent wave (CTAs
     // drift apart, so loads, arithmetic and stores of different CTAs overlap): 12 waves by default
     // (bf16 q4 batch: 5750 GB/s as one wave, 6480 at 8 waves, 6540 at 12).
@@ -23,7 +23,14 @@ static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cud
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    return launch_kernel(dequantize_kernel<FDT, KIND, OB>, (int)need, threads, stream, cfg.pdl != 0, args);
+    return launch_kernel(dequantize_kernel<FDT, KIND, OB, TILES>, (int)need, threads, stream, cfg.pdl != 0, args);
+}
+
+template <int FDT, int KIND, int OB>
+static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    return args.b2.enabled ? launch_tiles<FDT, KIND, OB, true>(args, cfg, stream)
+                           : launch_tiles<FDT, KIND, OB, false>(args, cfg, stream);
 }
 
 template <int FDT, int KIND>

@@ -157,7 +157,9 @@ __device__ __forceinline__ void dequant_word(uint32_t w, float s, uint32_t s2, u
     }
 }
 
-template <int FDT, int KIND, int OB>
+// TILES selects the [rows, cols] tile scale indexing at compile time: folding it into the common
+// kernel costs 16 registers and with them one resident CTA per SM.
+template <int FDT, int KIND, int OB, bool TILES>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
 {
     using DU = DUnitT<FDT, KIND, OB>;
@@ -205,9 +207,13 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                     }
                 }
                 // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
-                bool unused;
-                const long long si = a.b2.enabled ? (long long)blocks2d_scale_index(a.b2, (unsigned)li, &unused)
-                                                  : ((lg < 0) ? 0 : (li >> lg));
+                long long si;
+                if constexpr (TILES) {
+                    bool unused;
+                    si = (long long)blocks2d_scale_index(a.b2, (unsigned)li, &unused);
+                } else {
+                    si = (lg < 0) ? 0 : (li >> lg);
+                }
                 if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(T.params) + si));
                 else s[k] = round_to<FDT>(load_dyn(T.params, a.param, si));
             } else {

@@ -27,6 +27,38 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
+    // cfg.staged: 0 = units below 64 bytes, 1 = always, 2 = never
+    if ((cfg.staged == 1 || (cfg.staged == 0 && UB < 64)) && threads == 256) {
+        // bulk-copy staged variant: 4 x 16 KB stages + barriers per CTA, a whole number of waves
+        constexpr int SMEM = QK_STAGES * QK_TILE_BYTES + QK_STAGES * 8;
+        static const int occ_staged = [] {
+            cudaFuncSetAttribute(quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>, 256,
+                                                              SMEM) != cudaSuccess || n < 1)
+                n = 1;
+            return n;
+        }();
+        int *flag = stage_error_flag();
+        if (flag != nullptr) {
+            long long tiles = args.t[args.ntensors - 1].tile_end;
+            const long long cap2 = (long long)cfg.sm_count * occ_staged;
+            if (tiles > cap2) tiles = cap2;
+            if (tiles < 1) tiles = 1;
+            cudaLaunchConfig_t lc = {};
+            lc.gridDim = dim3((unsigned)tiles, 1, 1);
+            lc.blockDim = dim3(256, 1, 1);
+            lc.dynamicSmemBytes = SMEM;
+            lc.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            lc.attrs = attr;
+            lc.numAttrs = cfg.pdl ? 1 : 0;
+            return cudaLaunchKernelEx(&lc, quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>, args, flag);
+        }
+    }
     return launch_kernel(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, (int)need, threads, stream, cfg.pdl != 0, args);
 }
 

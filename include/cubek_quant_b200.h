@@ -225,13 +225,18 @@ size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *sc
 const char *qk_strerror(int status);
 const char *qk_version(void);
 
+/* Reads (synchronously) the device-side error flag of the current device: non-zero if a kernel gave up
+ * on a bounded wait (only the shared-memory staged quantize variant, tuning key 8, has such waits). */
+int qk_device_error(int *flag_out);
+
 /* Number of kernels this library has launched in the calling process (for accounting). */
 uint64_t qk_launch_count(void);
 
 /* Process-wide launch knobs, for measurements and tests only (keys: 0 threads per CTA, 1 CTAs per SM,
  * 2 force the reference-arithmetic route, 3 force the layout-general kernels, 4 programmatic dependent
  * launch on/off, 5 / 6 grid size of the quantize / dequantize kernels in waves, 7 cooperative per-tensor
- * kernel on/off). */
+ * kernel on/off, 8 staging of the quantize input through shared
+ * memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never). */
 void qk_set_tuning(int key, int value);
 int qk_get_tuning(int key);
 

@@ -71,6 +71,29 @@ def test_more_tensors_than_one_launch_and_general_members():
         assert_bits_equal(s, os_, "scales")
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+def test_batches_through_staged_and_direct_kernels(mode):
+    """Tiles of the staged kernels never span two tensors of a batch; ragged tensors end in partial tiles."""
+    import ctypes
+    from cubek_b200 import _ffi
+
+    _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGED, mode)
+    try:
+        F = FLOATS["f16"]
+        scheme = QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native, level=QuantLevel.block([16]))
+        shapes = [(33, 272), (700, 512), (1, 16), (129, 1040), (64, 4096)]
+        xs = [random_tensor(s, F, 400 + i) for i, s in enumerate(shapes)]
+        codes, scales, restored = run_batch(xs, scheme, F)
+        for x, c, s in zip(xs, codes, scales):
+            oc, os_ = O.quantize_dynamic(x, scheme)
+            assert_bits_equal(c, oc, "codes")
+            assert_bits_equal(s, os_, "scales")
+        flag = ctypes.c_int(-1)
+        assert _ffi.lib().qk_device_error(ctypes.byref(flag)) == 0 and flag.value == 0
+    finally:
+        _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGED, 0)
+
+
 def test_empty_batch_and_length_mismatch():
     client = ComputeClient.current()
     scheme = QuantScheme(value=QuantValue.Q8S)

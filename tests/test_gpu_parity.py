@@ -34,7 +34,7 @@ def full_check(x, scheme, F):
 @pytest.fixture
 def tuning():
     yield lambda key, value: _ffi.lib().qk_set_tuning(key, value)
-    for key in (_ffi.TUNE_FORCE_EXACT, _ffi.TUNE_FORCE_GENERAL):
+    for key in (_ffi.TUNE_FORCE_EXACT, _ffi.TUNE_FORCE_GENERAL, _ffi.TUNE_STAGED):
         _ffi.lib().qk_set_tuning(key, 0)
 
 
@@ -311,3 +311,19 @@ def test_odd_base_alignments(fname, offset_bytes):
         # nothing outside the views was touched
         assert int(raw_codes[:offset_bytes].sum()) == 0 and int(raw_codes[offset_bytes + ncode:].sum()) == 0
         assert int(raw_out[:offset_bytes].sum()) == 0 and int(raw_out[offset_bytes + n * esz:].sum()) == 0
+
+
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("scheme", list(scheme_grid(SHAPE)), ids=scheme_id)
+def test_bulk_copy_staged_variant(fname, scheme, tuning):
+    """The quantize kernels with their input staged through shared memory by `cp.async.bulk` + mbarriers
+    give the same bits, and no bounded wait gave up."""
+    import ctypes
+
+    F = FLOATS[fname]
+    for mode in (1, 2):                                            # always staged, never staged
+        tuning(_ffi.TUNE_STAGED, mode)
+        full_check(adversarial_tensor(SHAPE, F, scheme, 5), scheme, F)
+        full_check(random_tensor((1024, 1024), F, 6), scheme, F)  # several tiles per CTA, ragged last tile
+    flag = ctypes.c_int(-1)
+    assert _ffi.lib().qk_device_error(ctypes.byref(flag)) == 0 and flag.value == 0
