@@ -367,7 +367,7 @@ def run_gpu(args, workload):
         dist.destroy_process_group()
 
 
-def run_weight_set(args, per_tensor: bool):
+def run_weight_set(args, per_tensor: bool, row_sharded: bool = False):
     """BASELINE config 5: the 225 bf16 matrices of a Llama-3-8B-shaped model (15 GB), q8 with
     block-128 scales or per-tensor scales, whole tensors placed round-robin over the ranks (strong
     scaling: the set is fixed).  One step = fused quantize + dequantize of every tensor a rank owns."""
@@ -391,19 +391,31 @@ def run_weight_set(args, per_tensor: bool):
     level = QuantLevel.Tensor if per_tensor else QuantLevel.block([128])
     scheme = QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32, level=level)
     shapes = llama3_8b_shapes()
-    owned = assign_round_robin([r * c for _, r, c in shapes], world)[rank]
     g = torch.Generator(device=dev)
     g.manual_seed(0x5EED0004 + rank)
-    xs = [(torch.randn((shapes[i][1], shapes[i][2]), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-          for i in owned]
+    if row_sharded:
+        # every tensor is split by rows over the ranks; the per-tensor absmax needs one all-reduce(MAX)
+        from cubek_b200.shard import ShardedPerTensorSet, plan_rows
+
+        my_shapes = [(plan_rows(r, c, world, ElemType.BF16, scheme)[rank].rows, c) for _, r, c in shapes]
+        my_shapes = [sh for sh in my_shapes if sh[0] > 0]
+    else:
+        owned = assign_round_robin([r * c for _, r, c in shapes], world)[rank]
+        my_shapes = [(shapes[i][1], shapes[i][2]) for i in owned]
+    xs = [(torch.randn(sh, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16) for sh in my_shapes]
     codes = [torch.empty(scheme.packed_shape(x.shape), dtype=torch.int32, device=dev) for x in xs]
     scales = [torch.empty(scheme.scales_shape(x.shape), dtype=torch.float32, device=dev) for x in xs]
     outs = [torch.empty_like(x) for x in xs]
     ws = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
     H = TensorHandleRef.from_torch
     client = ComputeClient.current()
-    qb = quantize.PreparedDynamicBatch(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], scheme,
-                                       ElemType.BF16, H(ws))
+    if row_sharded:
+        absmax = torch.zeros(len(xs), dtype=torch.float32, device=dev)
+        qb = ShardedPerTensorSet(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], absmax, scheme,
+                                 ElemType.BF16)
+    else:
+        qb = quantize.PreparedDynamicBatch(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales],
+                                           scheme, ElemType.BF16, H(ws))
     db = dequantize.PreparedBatch(client, [H(t) for t in codes], [H(t) for t in outs], [H(t) for t in scales], scheme,
                                   ElemType.BF16)
 
@@ -444,7 +456,8 @@ def run_weight_set(args, per_tensor: bool):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tensors": len(shapes), "elements": n,
                        "level": "tensor" if per_tensor else "block[128]", "value": "Q8S", "store": "U32",
-                       "placement": "whole tensors, largest first onto the least loaded rank",
+                       "placement": ("every tensor split by rows over the ranks; one all-reduce(MAX) of 225 floats per step"
+                                     if row_sharded else "whole tensors, largest first onto the least loaded rank"),
                        "api": "qk_quantize_dynamic_batch + qk_dequantize_batch", "distribution": "normal(0,0.02)"},
             "pct_of_measured_peak": round(100 * value / world / peak, 1), "peak_source": f"{kind} copy bandwidth",
             "gpu_launches": int(launches)}))
@@ -528,7 +541,7 @@ def main():
     from cubek_b200.synthetic import WORKLOADS
 
     if args.workload.startswith("llama3_8b_q8_") and args.impl != "reference":
-        run_weight_set(args, per_tensor=args.workload.endswith("tensor"))
+        run_weight_set(args, per_tensor="tensor" in args.workload, row_sharded=args.workload.endswith("_sharded"))
         return
     workload = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -80,6 +80,9 @@ _SIGNATURES = {
     "qk_absmax_f32": (C.c_int, [C.POINTER(QkTensor), C.c_int, C.c_void_p, C.c_void_p]),
     "qk_quantize_from_absmax": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.c_void_p, C.POINTER(QkScheme), C.c_int,
                                                                      C.c_void_p]),
+    "qk_absmax_batch": (C.c_int, [C.c_int, C.POINTER(QkTensor), C.c_int, C.c_void_p, C.c_void_p]),
+    "qk_quantize_from_absmax_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.c_void_p, C.POINTER(QkScheme), C.c_int,
+                                                        C.c_void_p]),
     "qk_allreduce_max_f32": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "qk_workspace_bytes": (C.c_size_t, []),
     "qk_workspace_bytes_for": (C.c_size_t, [C.POINTER(QkTensor), C.POINTER(QkScheme), C.c_int]),

@@ -11,6 +11,7 @@
 // units.  They restate BlockScaledLayout::to_source_pos / is_block_start
 // (crates/cubek-quant/src/layout/scales.rs:144-195) per stored item, as the reference does.
 #include "misc_kernels.cuh"
+#include "quantize_kernels.cuh"   // unit_absmax
 
 namespace qk {
 
@@ -59,6 +60,86 @@ __global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long 
 #pragma unroll
         for (int m = 4; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
         if (lane == 0) atomicMax(cell, __float_as_uint(v));
+    }
+}
+
+// One launch for a batch of tensors.  A thread keeps the running absmax of the tensor it is in; when a
+// warp crosses into the next tensor it flushes (rare: CTAs work on contiguous spans), and at the end a
+// warp whose lanes all sit in the same tensor reduces with shuffles and issues one atomic.
+template <int FDT>
+__global__ void __launch_bounds__(256) absmax_batch_kernel(const AbsmaxBatchArgs a)
+{
+    constexpr int UNR = 4;
+    const long long total = a.chunk_end[a.ntensors - 1];
+    pdl_entry();
+    // Every CTA takes one contiguous span of the batch, so that it crosses few tensor boundaries (a
+    // grid-stride walk would land in a different tensor on almost every step and flush each time).
+    const long long step = (long long)blockDim.x * UNR;
+    const long long span = ((total + gridDim.x - 1) / gridDim.x + step - 1) / step * step;
+    const long long begin = (long long)blockIdx.x * span;
+    const long long end = (begin + span < total) ? begin + span : total;
+    int ti = 0, cur = -1;
+    float amax = 0.0f;
+    for (long long base = begin + threadIdx.x; base - threadIdx.x < end; base += step) {
+        Vec16 raw[UNR];
+        int tk[UNR];
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            const long long idx = base + (long long)k * blockDim.x;
+            if (idx < end) {
+                while (ti + 1 < a.ntensors && idx >= a.chunk_end[ti]) ++ti;
+                const long long li = idx - (ti ? a.chunk_end[ti - 1] : 0);
+                raw[k] = ldg128_stream(static_cast<const char *>(a.in[ti]) + li * 16);
+            } else {
+                raw[k] = Vec16{{0u, 0u, 0u, 0u}};
+            }
+            tk[k] = ti;
+        }
+#pragma unroll
+        for (int k = 0; k < UNR; ++k) {
+            if (cur < 0) cur = tk[k];
+            if (__any_sync(0xffffffffu, tk[k] != cur)) {
+                // the warp enters another tensor: lanes still in the old one contribute through a warp
+                // reduction when they all agree, else one by one
+                const int c0 = __shfl_sync(0xffffffffu, cur, 0);
+                if (__all_sync(0xffffffffu, cur == c0)) {
+                    float m = amax;
+#pragma unroll
+                    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+                    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(a.cells + c0, __float_as_uint(m));
+                } else if (amax > 0.0f) {
+                    atomicMax(a.cells + cur, __float_as_uint(amax));
+                }
+                cur = tk[k];
+                amax = 0.0f;
+            }
+            amax = fmaxf(amax, unit_absmax<FDT, 4>(raw[k].w));
+        }
+    }
+    if (cur < 0) return;   // this CTA's span is empty (the whole warp agrees: spans are per CTA)
+    const int first = __shfl_sync(0xffffffffu, cur, 0);
+    if (__all_sync(0xffffffffu, cur == first)) {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        if ((threadIdx.x & 31) == 0 && amax > 0.0f) atomicMax(a.cells + cur, __float_as_uint(amax));
+    } else if (amax > 0.0f) {
+        atomicMax(a.cells + cur, __float_as_uint(amax));
+    }
+}
+
+cudaError_t launch_absmax_batch(int fdt, const AbsmaxBatchArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (args.ntensors < 1) return cudaSuccess;
+    const long long total = args.chunk_end[args.ntensors - 1];
+    if (total == 0) return cudaSuccess;
+    long long need = (total + 1023) / 1024;
+    const long long cap = (long long)cfg.sm_count * 8;
+    if (need > cap) need = cap;
+    const bool pdl = cfg.pdl != 0;
+    switch (fdt) {
+    case QK_F32: return launch_kernel(absmax_batch_kernel<QK_F32>, (int)need, 256, stream, pdl, args);
+    case QK_F16: return launch_kernel(absmax_batch_kernel<QK_F16>, (int)need, 256, stream, pdl, args);
+    default: return launch_kernel(absmax_batch_kernel<QK_BF16>, (int)need, 256, stream, pdl, args);
     }
 }
 

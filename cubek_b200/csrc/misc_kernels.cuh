@@ -58,6 +58,17 @@ struct GeneralScalesArgs {
 // must hold zero (or an earlier partial result) beforehand; `zero_first` clears it on the stream.
 cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
                           cudaStream_t stream, bool zero_first = true);
+// absmax of every tensor of a batch in one launch.  `chunk_end` counts 16-byte chunks across the batch;
+// every tensor must start on a 16-byte boundary and hold a whole number of chunks.  `cells[i]` must be
+// zero (or hold an earlier partial result) beforehand.
+constexpr int QK_ABSMAX_BATCH = 128;
+struct AbsmaxBatchArgs {
+    const void *in[QK_ABSMAX_BATCH];
+    long long chunk_end[QK_ABSMAX_BATCH];
+    int ntensors;
+    unsigned int *cells;
+};
+cudaError_t launch_absmax_batch(int fdt, const AbsmaxBatchArgs &args, const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_finalize_scale(const unsigned int *cell, void *scale_out, int fdt, float range,
                                   cudaStream_t stream);
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream);

@@ -95,3 +95,29 @@ def quantize_per_tensor_sharded(client: ComputeClient, shard: TensorHandleRef, o
     _quantize.absmax(client, shard, elem, absmax.data_ptr())
     allreduce_absmax(absmax, group)
     _quantize.launch_from_absmax(client, shard, output, out_scale, absmax.data_ptr(), scheme, elem)
+
+
+class ShardedPerTensorSet:
+    """Per-tensor quantization of a set of row-sharded tensors: this rank's shards are reduced to one
+    absmax each (``qk_absmax_batch``), ONE all-reduce(MAX) of ``len(shards)`` floats makes them global, and
+    the shards are quantized in batched launches with scales derived on the device.  Everything is
+    enqueued on the current stream; nothing synchronises with the host."""
+
+    def __init__(self, client: ComputeClient, shards, outputs, out_scales, absmax, scheme: QuantScheme,
+                 elem: ElemType, group=None):
+        from . import _ffi
+
+        if not scheme.level.is_tensor:
+            raise ValueError("per-tensor schemes only; per-block shards need no exchange")
+        self._in, self._out, self._sc = _ffi.CTensorArray(shards), _ffi.CTensorArray(outputs), _ffi.CTensorArray(out_scales)
+        if not (self._in.count == self._out.count == self._sc.count == absmax.numel()):
+            raise ValueError("one output, one scale and one absmax cell per shard")
+        self._absmax, self._group, self._scheme = absmax, group, _ffi.c_scheme(scheme)
+        self._elem, self._stream, self._lib, self._ffi = int(elem), client.stream, _ffi.lib(), _ffi
+
+    def __call__(self) -> None:
+        f = self._ffi
+        f.check(self._lib.qk_absmax_batch(self._in.count, self._in.array, self._elem, self._absmax.data_ptr(), self._stream))
+        allreduce_absmax(self._absmax, self._group)
+        f.check(self._lib.qk_quantize_from_absmax_batch(self._in.count, self._in.array, self._out.array, self._sc.array,
+                                                        self._absmax.data_ptr(), self._scheme, self._elem, self._stream))

@@ -166,6 +166,14 @@ int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, voi
 int qk_quantize_from_absmax(const QkTensor *input, const QkTensor *output, const QkTensor *out_scale,
                             const float *absmax, const QkScheme *scheme, int input_dtype, void *stream);
 
+/* The same split for a set of row-sharded tensors: `absmax_out` / `absmax` hold one f32 per tensor, so a
+ * single all-reduce(MAX) of `count` scalars serves the whole set; the quantize launches take up to 64
+ * tensors each. */
+int qk_absmax_batch(int count, const QkTensor *inputs, int input_dtype, float *absmax_out, void *stream);
+int qk_quantize_from_absmax_batch(int count, const QkTensor *inputs, const QkTensor *outputs,
+                                  const QkTensor *out_scales, const float *absmax, const QkScheme *scheme,
+                                  int input_dtype, void *stream);
+
 /* ncclAllReduce(buf, buf, count, ncclFloat32, ncclMax, comm, stream) on a library-resolved
  * NCCL (libnccl.so.2 already loaded in the process, else dlopen).  `comm` is an ncclComm_t. */
 int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream);

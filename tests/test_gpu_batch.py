@@ -15,14 +15,14 @@ pytestmark = pytest.mark.gpu
 H = TensorHandleRef.from_torch
 
 
-def run_batch(xs, scheme, F):
+def run_batch(xs, scheme, F, ws_bytes=1 << 20):
     elem = {np.dtype(np.float32): ElemType.F32, np.dtype(np.float16): ElemType.F16}.get(np.dtype(F), ElemType.BF16)
     client = ComputeClient.current()
     dx = [to_device(x) for x in xs]
     dq = [empty_device(scheme.packed_shape(x.shape), code_dtype(scheme)) for x in xs]
     ds = [empty_device(scheme.scales_shape(x.shape), np.float32) for x in xs]
     do = [empty_device(x.shape, F) for x in xs]
-    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
     quantize.launch_dynamic_batch(client, [H(t) for t in dx], [H(t) for t in dq], [H(t) for t in ds], scheme, elem, H(ws))
     dequantize.launch_batch(client, [H(t) for t in dq], [H(t) for t in do], [H(t) for t in ds], scheme, elem)
     torch.cuda.synchronize()
@@ -43,6 +43,22 @@ def test_batch_equals_single_tensor_calls(fname, scheme):
     shapes = [(64, 256), (8, 128), (300, 512), (1, 128), (128, 1024), (16, 256)]
     xs = [random_tensor(s, F, 50 + i) * np.float32(1 + i).astype(F) for i, s in enumerate(shapes)]
     codes, scales, restored = run_batch(xs, scheme, F)
+    for x, c, s, r in zip(xs, codes, scales, restored):
+        oc, os_ = O.quantize_dynamic(x, scheme)
+        assert_bits_equal(c, oc, "codes")
+        assert_bits_equal(s, os_, "scales")
+        assert_bits_equal(r, O.dequantize(oc, os_, scheme, F), "restored")
+
+
+@pytest.mark.parametrize("fname", ["f32", "bf16"])
+def test_per_tensor_batch_with_minimal_workspace(fname):
+    """With only the absmax cells as workspace the per-tensor batch takes one batched absmax launch and
+    batched quantize launches (no cooperative kernels); ragged members get their own absmax launch."""
+    F = FLOATS[fname]
+    scheme = QuantScheme(value=QuantValue.Q8S)
+    shapes = [(64, 256), (3, 36), (300, 512), (1, 128), (128, 1024), (5, 4), (16, 256)] + [(8, 64)] * 140
+    xs = [random_tensor(s, F, 500 + i) * np.float32(1 + i % 7).astype(F) for i, s in enumerate(shapes)]
+    codes, scales, restored = run_batch(xs, scheme, F, ws_bytes=1024)
     for x, c, s, r in zip(xs, codes, scales, restored):
         oc, os_ = O.quantize_dynamic(x, scheme)
         assert_bits_equal(c, oc, "codes")

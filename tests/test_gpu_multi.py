@@ -131,3 +131,60 @@ def test_allreduce_max_entry_point_on_a_caller_owned_communicator(tmp_path):
     world = 2
     mp.spawn(_nccl_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def _set_rank_main(rank, world, port, out_dir):
+    """A set of row-sharded tensors, per-tensor scheme: one all-reduce of all absmax scalars; every rank's
+    codes equal the single-device codes of its rows and every rank holds the single-device scales."""
+    import torch.distributed as dist
+
+    from cubek_b200 import (ComputeClient, ElemType, QuantScheme, QuantStore, QuantValue, TensorHandleRef, quantize)
+    from cubek_b200.shard import ShardedPerTensorSet, plan_rows
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        H = TensorHandleRef.from_torch
+        client = ComputeClient.current()
+        scheme = QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32)
+        g = torch.Generator(device="cuda").manual_seed(7)
+        shapes = [(512, 1024), (64, 4096), (1024, 256), (8, 128)]
+        full = [torch.randn(s, generator=g, device="cuda").to(torch.bfloat16) * (1 + i) for i, s in enumerate(shapes)]
+        for i, t in enumerate(full):
+            t[-1, -1] = 50.0 + i                      # every global absmax sits in the last rank's rows
+        ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+        want_codes = [torch.empty(scheme.packed_shape(s), dtype=torch.int32, device="cuda") for s in shapes]
+        want_scale = [torch.empty(1, dtype=torch.float32, device="cuda") for _ in shapes]
+        quantize.launch_dynamic_batch(client, [H(t) for t in full], [H(t) for t in want_codes], [H(t) for t in want_scale],
+                                      scheme, ElemType.BF16, H(ws))
+        plans = [plan_rows(s[0], s[1], world, ElemType.BF16, scheme)[rank] for s in shapes]
+        keep = [i for i, p in enumerate(plans) if p.rows > 0]
+        mine = [full[i][plans[i].row_start: plans[i].row_start + plans[i].rows] for i in keep]
+        codes = [torch.empty(scheme.packed_shape(m.shape), dtype=torch.int32, device="cuda") for m in mine]
+        scale = [torch.empty(1, dtype=torch.float32, device="cuda") for _ in mine]
+        absmax = torch.zeros(len(mine), dtype=torch.float32, device="cuda")
+        # ranks may hold different subsets only if a tensor has fewer row granules than ranks; the
+        # all-reduce needs equal lengths, which these shapes guarantee
+        assert len(mine) == len(shapes)
+        ShardedPerTensorSet(client, [H(t) for t in mine], [H(t) for t in codes], [H(t) for t in scale], absmax, scheme,
+                            ElemType.BF16)()
+        torch.cuda.synchronize()
+        for j, i in enumerate(keep):
+            p = plans[i]
+            assert torch.equal(scale[j].view(torch.int32), want_scale[i].view(torch.int32)), f"scale {i}"
+            assert torch.equal(codes[j], want_codes[i][p.row_start: p.row_start + p.rows]), f"codes {i}"
+        open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_row_sharded_set_with_one_allreduce(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_set_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
