@@ -194,12 +194,13 @@ def run_reference(args, workload):
             times.append(time.perf_counter() - t0)
     secs = sum(times) / len(times)
     value = round((q + d) / secs / 1e9, 3)
-    sample = f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor per step"
+    sample = (f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor per step "
+              f"(one of the {args.batch} tensors of a step of the GPU arm)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.elem.name.lower(),
-        "data": "synthetic", "config": config_of(workload, args, rows),
+        "data": "synthetic", "config": config_of(workload, args),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": O.max_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU port of the reference arithmetic (the oracle); the reference's own CubeCL CPU runtime "
@@ -207,10 +208,10 @@ def run_reference(args, workload):
     }))
 
 
-def config_of(workload, args, rows=None):
+def config_of(workload, args):
     s = workload.scheme
-    return {"workload": workload.name, "shape": list(workload.shape) if rows is None else [rows, workload.shape[1]],
-            "batch_tensors_per_step": args.batch if rows is None else 1,
+    return {"workload": workload.name, "shape": list(workload.shape),
+            "batch_tensors_per_step": args.batch,
             "value": s.value.name, "store": s.store.name, "param": s.param.name,
             "level": "tensor" if s.level.is_tensor else f"block{list(s.level.block_size.as_slice())}",
             "distribution": workload.distribution,
