@@ -77,8 +77,9 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
-       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_COUNT = 9 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}};
+       TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_SLICE_KIB = 9,
+       TUNE_SLOTS = 10, TUNE_COUNT = 11 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -375,6 +376,22 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
     return -2;
 }
 
+// Layout of a strided float tensor for the whole-tensor absmax (no blocks, no scales).
+static GeneralLayout strided_data_layout(const QkTensor *t)
+{
+    GeneralLayout L;
+    L.rank = t->rank;
+    L.per_tensor = 1;
+    L.data_contiguous = 0;
+    for (int d = 0; d < QK_MAX_RANK; ++d) {
+        L.shape[d] = d < t->rank ? t->shape[d] : 1;
+        L.data_strides[d] = d < t->rank ? t->strides[d] : 0;
+        L.block[d] = 1;
+        L.scale_strides[d] = L.out_scale_strides[d] = 0;
+    }
+    return L;
+}
+
 // absmax of `count` tensors into `cells[0..count)` (already zero): tensors that are contiguous, start on
 // a 16-byte boundary and hold whole 16-byte chunks share launches of up to QK_ABSMAX_BATCH tensors; the
 // others get a launch each.
@@ -400,10 +417,17 @@ static int absmax_into_cells(int count, const QkTensor *inputs, const bool *skip
             continue;
         }
         if ((rc = check_tensor(&inputs[i], fsize))) return rc;
-        if (!is_contiguous(&inputs[i])) return QK_ERR_LAYOUT;
         const long long n = numel(&inputs[i]);
         if (n == 0) {
             if ((rc = flush())) return rc;
+            continue;
+        }
+        if (!is_contiguous(&inputs[i])) {
+            if ((rc = flush())) return rc;
+            count_launch();
+            const GeneralLayout L = strided_data_layout(&inputs[i]);
+            const cudaError_t e = launch_absmax_strided(L, inputs[i].ptr, input_dtype, n, cells + i, cfg, stream);
+            if (e != cudaSuccess) return cuda_status(e);
             continue;
         }
         const bool chunkable = (n % per16 == 0) && aligned(inputs[i].ptr, 16);
@@ -757,17 +781,7 @@ int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, voi
     const long long n = numel(input);
     count_launch(n > 0 ? 2 : 1);
     if (!is_contiguous(input)) {
-        if (input->rank > QK_MAX_RANK) return QK_ERR_SHAPE;
-        GeneralLayout L;
-        L.rank = input->rank;
-        L.per_tensor = 1;
-        L.data_contiguous = 0;
-        for (int d = 0; d < QK_MAX_RANK; ++d) {
-            L.shape[d] = d < input->rank ? input->shape[d] : 1;
-            L.data_strides[d] = d < input->rank ? input->strides[d] : 0;
-            L.block[d] = 1;
-            L.scale_strides[d] = L.out_scale_strides[d] = 0;
-        }
+        const GeneralLayout L = strided_data_layout(input);
         return cuda_status(launch_absmax_strided(L, input->ptr, input_dtype, n, reinterpret_cast<unsigned int *>(absmax_out),
                                                  current_cfg(), static_cast<cudaStream_t>(stream)));
     }

@@ -87,6 +87,25 @@ def test_more_tensors_than_one_launch_and_general_members():
         assert_bits_equal(s, os_, "scales")
 
 
+def test_per_tensor_batch_with_strided_members():
+    """Float tensors of a per-tensor batch may be strided views (a transposed matrix, every other column):
+    their absmax comes from the strided kernel, their codes from the layout-general one."""
+    scheme = QuantScheme(value=QuantValue.Q8S)
+    client = ComputeClient.current()
+    base = [torch.from_numpy(random_tensor((64, 128), np.float32, 900 + i)).cuda() for i in range(4)]
+    views = [base[0], base[1].t(), base[2][:, ::2], base[3]]
+    dq = [empty_device(scheme.packed_shape(tuple(v.shape)), code_dtype(scheme)) for v in views]
+    ds = [empty_device((1,), np.float32) for _ in views]
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    quantize.launch_dynamic_batch(client, [H(v) for v in views], [H(t) for t in dq], [H(t) for t in ds], scheme,
+                                  ElemType.F32, H(ws))
+    torch.cuda.synchronize()
+    for v, c, s in zip(views, dq, ds):
+        oc, os_ = O.quantize_dynamic(np.ascontiguousarray(v.cpu().numpy()), scheme)
+        assert_bits_equal(to_numpy(c, code_dtype(scheme)), oc, "codes")
+        assert_bits_equal(to_numpy(s, np.float32), os_, "scales")
+
+
 @pytest.mark.parametrize("mode", [1, 2])
 def test_batches_through_staged_and_direct_kernels(mode):
     """Tiles of the staged kernels never span two tensors of a batch; ragged tensors end in partial tiles."""
