@@ -111,3 +111,48 @@ def test_embedding_sized_tensor_q8_block128():
     o_codes, o_scale = O.quantize_dynamic(xs, w.scheme)
     assert_bits_equal(to_numpy(codes[pick].contiguous(), np.uint32), o_codes, "codes")
     assert_bits_equal(to_numpy(restored[pick].contiguous(), F), O.dequantize(o_codes, o_scale, w.scheme, F), "restored")
+
+
+@pytest.mark.parametrize("level", ["block32", "tensor"])
+def test_more_than_2_31_elements(level):
+    """A bf16 tensor of 2^31 + 2^20 elements (4.3 GB): unit, element and byte offsets pass 2^31 and 2^32.
+    Whole rows at the start, around the 2^31-element boundary and at the very end are compared with the
+    oracle; for the per-tensor scheme the largest magnitude is the tensor's last element."""
+    from cubek_b200 import QuantLevel, QuantScheme, QuantValue
+
+    rows, cols = (1 << 19) + 256, 4096
+    assert rows * cols > 1 << 31
+    if level == "block32":
+        s = QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([32]))
+    else:
+        s = QuantScheme(value=QuantValue.Q8S)
+    elem, F = ElemType.BF16, NP_FLOAT[ElemType.BF16]
+    x = torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda").normal_(0.0, 0.02, generator=torch.Generator("cuda").manual_seed(31))
+    if level == "tensor":
+        x[-1, -1] = 3.0
+    client = ComputeClient.current()
+    codes = torch.empty(s.packed_shape(x.shape), dtype=torch.int32, device="cuda")
+    out_scale = torch.empty(s.scales_shape(x.shape), dtype=torch.float32, device="cuda")
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    quantize.launch_dynamic(client, H(x), H(codes), H(out_scale), s, elem, H(ws))
+    restored = torch.empty_like(x)
+    dequantize.launch_ref(client, H(codes), H(restored), H(out_scale), s, elem)
+    torch.cuda.synchronize()
+    half = (1 << 31) // cols
+    pick = torch.tensor([0, 1, half - 1, half, half + 1, rows - 2, rows - 1], device="cuda")
+    xs = to_numpy(x[pick].contiguous(), F)
+    if level == "tensor":
+        lo, hi = s.value.range()
+        want_scale = np.array([np.float32(2) * np.float32(3.0) / np.float32(hi - lo)], dtype=np.float32).astype(F)
+        o_codes, o_scale = O.quantize(xs, want_scale, s)
+        assert_bits_equal(to_numpy(out_scale, np.float32), o_scale, "scale")
+    else:
+        o_codes, o_scale = O.quantize_dynamic(xs, s)
+        assert_bits_equal(to_numpy(out_scale[pick].contiguous(), np.float32), o_scale, "scales")
+    assert_bits_equal(to_numpy(codes[pick].contiguous(), np.uint32), o_codes, "codes")
+    assert_bits_equal(to_numpy(restored[pick].contiguous(), F), O.dequantize(o_codes, o_scale, s, F), "restored")
+    # every element took part: the restored tensor is within half a step everywhere
+    step = out_scale.reshape(1, 1) if level == "tensor" else None
+    if step is not None:
+        err = (restored.float() - x.float()).abs().max()
+        assert float(err) <= float(step.max()) * 0.5 * (1 + 1e-4) + 3.0 * 2.0 ** -6
