@@ -3,8 +3,6 @@
 
 #include "common.cuh"
 
-#define QK_MAX_RANK 8
-
 namespace qk {
 
 // Host-built description of the scales layout, mirroring BlockScaledLayout /

@@ -58,7 +58,8 @@ typedef struct {
 
 /* The fields the reference reads from `TensorHandleRef` (`handle`, `shape`, `strides`,
  * `elem_size`: layout/scales.rs:213-215, quantize.rs:234-239).  Strides in elements.
- * `shape`/`strides` are host arrays of `rank` entries. */
+ * `shape`/`strides` are host arrays of `rank` entries, 1 <= rank <= QK_MAX_RANK. */
+#define QK_MAX_RANK 8
 typedef struct {
     void *ptr;
     int32_t rank;

@@ -127,4 +127,7 @@ def test_host_roundtrip_staging_size():
     sch = QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([32]))
     t = _ffi.CTensor(fake((14336, 4096), 2))
     n = _ffi.lib().qk_host_roundtrip_staging_bytes(t.ref(), _ffi.c_scheme(sch), int(ElemType.BF16))
-    assert 4 * 8 * 2**20 < n < 4 * 24 * 2**20
+    lib = _ffi.lib()
+    slots, slice_bytes = lib.qk_get_tuning(_ffi.TUNE_SLOTS), lib.qk_get_tuning(_ffi.TUNE_SLICE_KIB) << 10
+    assert (slots, slice_bytes) == (4, 16 << 20)
+    assert slots * slice_bytes < n < slots * 3 * slice_bytes     # input + codes + scales + restored per slot
