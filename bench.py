@@ -241,6 +241,9 @@ def run_gpu(args, workload):
     lib = _ffi.lib()      # raises if the CUDA library is missing: there is no fallback
     if args.no_pdl:
         lib.qk_set_tuning(_ffi.TUNE_PDL, 0)
+    for kv in filter(None, args.tune.split(",")):
+        key, value = kv.split("=")
+        lib.qk_set_tuning(int(key), int(value))
     scheme, elem = workload.scheme, workload.elem
     r, c = workload.shape
     B = args.batch
@@ -536,6 +539,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B runs)")
+    ap.add_argument("--tune", default="", help="library tuning keys for A/B runs, e.g. 11=2,8=1 (see qk_set_tuning)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

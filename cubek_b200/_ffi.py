@@ -30,7 +30,7 @@ QK_ERR_CUDA = 1000
 PANIC_CLASS = (QK_ERR_UNSUPPORTED_SCHEME, QK_ERR_BLOCK_SIZE, QK_ERR_SHAPE, QK_ERR_DTYPE)
 
 (TUNE_THREADS, TUNE_CTAS_PER_SM, TUNE_FORCE_EXACT, TUNE_FORCE_GENERAL, TUNE_PDL, TUNE_QUANT_WAVES, TUNE_DEQUANT_WAVES,
- TUNE_COOP_TENSOR, TUNE_STAGED, TUNE_SLICE_KIB, TUNE_SLOTS) = range(11)
+ TUNE_COOP_TENSOR, TUNE_STAGED, TUNE_SLICE_KIB, TUNE_SLOTS, TUNE_STAGES) = range(12)
 
 
 class QkScheme(C.Structure):

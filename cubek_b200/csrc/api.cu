@@ -78,8 +78,8 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
        TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_SLICE_KIB = 9,
-       TUNE_SLOTS = 10, TUNE_COUNT = 11 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}};
+       TUNE_SLOTS = 10, TUNE_STAGES = 11, TUNE_COUNT = 12 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}, {2}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -120,6 +120,7 @@ static LaunchCfg current_cfg()
     c.pdl = g_tune[TUNE_PDL].load();
     c.quant_waves = g_tune[TUNE_QUANT_WAVES].load();
     c.staged = g_tune[TUNE_STAGED].load();
+    c.stages = g_tune[TUNE_STAGES].load();
     c.dequant_waves = g_tune[TUNE_DEQUANT_WAVES].load();
     c.sm_count = sm_count_of_current_device();
     return c;

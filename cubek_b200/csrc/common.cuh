@@ -312,6 +312,7 @@ struct LaunchCfg {
     int force_exact;  // 1: every unit takes the reference-arithmetic route
     int pdl;          // 1: launch with programmatic stream serialization
     int staged;       // 1: quantize reads its input through the shared-memory bulk-copy pipeline
+    int stages;       // ring depth of that pipeline (2..4 tiles of 16 KB per CTA)
 };
 
 }  // namespace qk

@@ -29,17 +29,27 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     if (need < 1) need = 1;
     // cfg.staged: 0 = units below 64 bytes, 1 = always, 2 = never
     if ((cfg.staged == 1 || (cfg.staged == 0 && UB < 64)) && threads == 256) {
-        // bulk-copy staged variant: 4 x 16 KB stages + barriers per CTA, a whole number of waves
-        constexpr int SMEM = QK_STAGES * QK_TILE_BYTES + QK_STAGES * 8;
-        static const int occ_staged = [] {
-            cudaFuncSetAttribute(quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-            int n = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>, 256,
-                                                              SMEM) != cudaSuccess || n < 1)
-                n = 1;
-            return n;
-        }();
+        // bulk-copy staged variant: cfg.stages x 16 KB stages + barriers per CTA, a whole number of waves
+        const int nstages = cfg.stages < 2 ? 2 : (cfg.stages > QK_MAX_STAGES ? QK_MAX_STAGES : cfg.stages);
+        const int SMEM = nstages * QK_TILE_BYTES + QK_MAX_STAGES * 8;
+        static const struct Occupancy {
+            int per_sm[QK_MAX_STAGES + 1];
+            Occupancy()
+            {
+                cudaFuncSetAttribute(quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     QK_MAX_STAGES * QK_TILE_BYTES + QK_MAX_STAGES * 8);
+                for (int n = 0; n <= QK_MAX_STAGES; ++n) {
+                    per_sm[n] = 1;
+                    if (n >= 2 &&
+                        (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm[n], quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>,
+                                                                       256, n * QK_TILE_BYTES + QK_MAX_STAGES * 8) != cudaSuccess ||
+                         per_sm[n] < 1))
+                        per_sm[n] = 1;
+                }
+            }
+        } occupancy;
+        const int occ_staged = occupancy.per_sm[nstages];
         int *flag = stage_error_flag();
         if (flag != nullptr) {
             long long tiles = args.t[args.ntensors - 1].tile_end;
@@ -56,7 +66,7 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             lc.attrs = attr;
             lc.numAttrs = cfg.pdl ? 1 : 0;
-            return cudaLaunchKernelEx(&lc, quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>, args, flag);
+            return cudaLaunchKernelEx(&lc, quantize_staged_kernel<FDT, KIND, UB, DYN, CLAMP>, args, flag, nstages);
         }
     }
     return launch_kernel(quantize_kernel<FDT, KIND, UB, DYN, CLAMP>, (int)need, threads, stream, cfg.pdl != 0, args);

@@ -533,15 +533,21 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
 // -------------------------------------------------------------------------------------
 // The same kernel with the input staged through shared memory by the bulk-copy engine:
 // one thread issues `cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes` for
-// 16 KB tiles into a 4-stage ring, the CTA waits on the stage's mbarrier, copies its units to
-// registers, releases the stage (one __syncthreads, then the refill is issued) and does the
-// arithmetic while up to three further tiles are in flight.
+// 16 KB tiles into a ring of `nstages` tiles, the CTA waits on the stage's mbarrier, copies its units
+// to registers, releases the stage (one __syncthreads, then the refill is issued) and does the
+// arithmetic while the other tiles are in flight.
 //
 // Measured against the direct loads: slower for 64-byte units (a thread's 64 bytes sit 64 bytes
 // apart in shared memory: 4-way bank conflicts; 5115 vs 5713 GB/s on bf16 q4), faster for 16- and
 // 32-byte units, where the direct kernel has too few bytes in flight per thread (4341 vs 3771 GB/s on
 // f16 e2m1 block 16).  The launcher therefore stages units below 64 bytes and loads 64-byte units
 // directly; a tuning key forces either route, and the parity tests run both.
+//
+// Ring depth: these small-unit kernels are bound by instruction issue, not by bytes in flight, so
+// resident warps matter more than a deep ring.  Two tiles per CTA (32 KB) leave room for the 5 CTAs
+// per SM the 48 registers allow; 3 / 4 tiles allow 4 / 3.  f16 e2m1 block 16, batch of 8 tensors:
+// 5244 / 5178 / 4917 GB/s with 2 / 3 / 4 tiles.  Forcing 6 CTAs per SM (40 registers) spills and
+// drops to 4949 GB/s.
 //
 // Every mbarrier wait is bounded: after ~2^22 polls a thread records the failure in
 // `*a_error` and leaves the kernel instead of spinning forever.
@@ -571,11 +577,11 @@ __device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_
                  : "memory");
 }
 
-constexpr int QK_STAGES = 4;
+constexpr int QK_MAX_STAGES = 4;     // ring depth is a launch parameter: 2..QK_MAX_STAGES
 constexpr int QK_TILE_BYTES = 16384;
 
 template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
-__global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a, int *a_error)
+__global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a, int *a_error, int nstages)
 {
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
@@ -584,13 +590,13 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
     constexpr int TILE_UNITS = 256 * UPT;
     using F = typename ElemOf<FDT>::type;
     extern __shared__ __align__(128) unsigned char stage_mem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(stage_mem + QK_STAGES * QK_TILE_BYTES);
+    uint64_t *full = reinterpret_cast<uint64_t *>(stage_mem + nstages * QK_TILE_BYTES);
 
     const bool aligned32 = a.aligned32 != 0;
     const int lg = a.lg_units_per_block;
     const long long ntiles = a.t[a.ntensors - 1].tile_end;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < QK_STAGES; ++s) mbarrier_init(&full[s], 1);
+        for (int s = 0; s < nstages; ++s) mbarrier_init(&full[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -611,7 +617,7 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
         bulk_load_1d(stage_mem + s * QK_TILE_BYTES, static_cast<const char *>(T.in) + u0 * UB, bytes, &full[s]);
     };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < QK_STAGES; ++s) {
+        for (int s = 0; s < nstages; ++s) {
             const long long t = blockIdx.x + (long long)s * gridDim.x;
             if (t < ntiles) issue(t, s);
         }
@@ -619,10 +625,15 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
     int scale_ti = -1;
     float tensor_scale = 0.0f;
 
-    int it = 0;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
-        const int s = it % QK_STAGES;
-        const uint32_t parity = (it / QK_STAGES) & 1;
+    int next_stage = 0;          // the ring position of the coming iteration
+    uint32_t next_parity = 0;    // flips every time the ring wraps
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int s = next_stage;
+        const uint32_t parity = next_parity;
+        if (++next_stage == nstages) {
+            next_stage = 0;
+            next_parity ^= 1u;
+        }
         int polls = 0;
         while (!mbarrier_try_wait(&full[s], parity)) {
             if (++polls > (1 << 22)) {
@@ -648,7 +659,7 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
         }
         __syncthreads();   // every thread holds its units: the stage can be refilled
         if (threadIdx.x == 0) {
-            const long long t = tile + (long long)QK_STAGES * gridDim.x;
+            const long long t = tile + (long long)nstages * gridDim.x;
             if (t < ntiles) issue(t, s);
         }
 #pragma unroll

@@ -246,7 +246,8 @@ uint64_t qk_launch_count(void);
  * launch on/off, 5 / 6 grid size of the quantize / dequantize kernels in waves, 7 cooperative per-tensor
  * kernel on/off, 8 staging of the quantize input through shared
  * memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never, 9 / 10 input KiB per slice and staging
- * slots (1..8) of qk_roundtrip_host; change them only between calls, and size the staging area after). */
+ * slots (1..8) of qk_roundtrip_host; change them only between calls, and size the staging area after, 11 ring
+ * depth (2..4 tiles of 16 KB) of the staged quantize variant). */
 void qk_set_tuning(int key, int value);
 int qk_get_tuning(int key);
 

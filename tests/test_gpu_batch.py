@@ -106,13 +106,14 @@ def test_per_tensor_batch_with_strided_members():
         assert_bits_equal(to_numpy(s, np.float32), os_, "scales")
 
 
-@pytest.mark.parametrize("mode", [1, 2])
-def test_batches_through_staged_and_direct_kernels(mode):
+@pytest.mark.parametrize("mode,stages", [(1, 2), (1, 3), (1, 4), (2, 2)])
+def test_batches_through_staged_and_direct_kernels(mode, stages):
     """Tiles of the staged kernels never span two tensors of a batch; ragged tensors end in partial tiles."""
     import ctypes
     from cubek_b200 import _ffi
 
     _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGED, mode)
+    _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGES, stages)
     try:
         F = FLOATS["f16"]
         scheme = QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native, level=QuantLevel.block([16]))
@@ -127,6 +128,7 @@ def test_batches_through_staged_and_direct_kernels(mode):
         assert _ffi.lib().qk_device_error(ctypes.byref(flag)) == 0 and flag.value == 0
     finally:
         _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGED, 0)
+        _ffi.lib().qk_set_tuning(_ffi.TUNE_STAGES, 2)
 
 
 def test_empty_batch_and_length_mismatch():
