@@ -184,11 +184,10 @@ __device__ __forceinline__ bool scale_is_safe(float s)
     return s >= 7.888609052e-31f /* 2^-100 */ && s <= 1.267650600e+30f /* 2^100 */;
 }
 
-// E5M2 clamps at +-57344, outside the window the half-precision shortcut was checked on.
-template <int FDT, int KIND> __host__ __device__ constexpr bool kind_allows_fast()
-{
-    return !(KIND == KIND_E5M2 && FDT != QK_F32);
-}
+// Every kind takes the shortcuts.  E5M2 clamps at +-57344, beyond the window of the integer kinds: for
+// 16-bit inputs the half-precision shortcut was checked on the host up to |x/s| = 2^18, overflow of
+// f16 to infinity included (the clamp then gives the bound either way).
+template <int FDT, int KIND> __host__ __device__ constexpr bool kind_allows_fast() { return true; }
 
 // ---- packing of integral f32 values -----------------------------------------------------------
 // `c` holds integral (or to-be-rounded, already clamped) f32 values in element order.
@@ -273,8 +272,9 @@ __device__ void quantize_unit_exact(const uint32_t *raw, float s, float lo, floa
 //     clamped so that a huge quotient ends as +-inf or a huge value of the right sign (never NaN).
 //   f16 / bf16 quotient: x and s carry 11 / 8 significant bits, so x/s is never closer than
 //     2^-23 / 2^-17 (relative) to a rounding boundary of F; the f32 product x*r rounds to the
-//     same F value as the exact quotient for every |x/s| in [1/8, 1024] (checked exhaustively on
-//     the host for all pairs); outside that range the code is 0 or the clamp bound either way.
+//     same F value as the exact quotient for every |x/s| in [1/8, 2^18] (checked exhaustively on
+//     the host for all pairs; the property depends on the two significands only); outside that
+//     range the code is 0 or the clamp bound either way.
 template <int FDT, int KIND, int UB, bool CLAMP, bool BOUNDED>
 __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s, float lo, float hi, uint32_t *outw)
 {

@@ -199,6 +199,36 @@ def test_scale_extremes_take_the_reference_route():
     assert_bits_equal(d_codes, O.quantize_dynamic(x, scheme)[0], "codes (fused)")
 
 
+@pytest.mark.parametrize("fname", ["f16", "bf16"])
+@pytest.mark.parametrize("value", [QuantValue.E5M2, QuantValue.E4M3])
+def test_fp8_codes_of_half_inputs_up_to_and_past_the_clamp(fname, value):
+    """fp8 codes of 16-bit inputs take the shortcut arithmetic up to the clamp bound (57344 for e5m2);
+    quotients that overflow f16 to infinity, or land between the bound and the largest finite value,
+    must clamp like the reference arithmetic.  Both routes are compared with the oracle."""
+    F = FLOATS[fname]
+    scheme = QuantScheme(value=value, store=QuantStore.Native, level=QuantLevel.block([32]))
+    lo, hi = scheme.value.range()
+    rng = np.random.default_rng(1234)
+    shape = (64, 256)
+    n = shape[0] * shape[1]
+    # quotients spread log-uniformly from 1/4 to 4 x the bound, both signs, plus exact bounds and ties
+    q = np.exp(rng.uniform(np.log(0.25), np.log(4.0 * hi), n)).astype(np.float32) * rng.choice([-1.0, 1.0], n).astype(np.float32)
+    q[::97] = hi
+    q[1::97] = -hi
+    q[2::97] = np.float32(hi) * np.float32(1.0009765625)
+    q[3::97] = 2.5
+    x = (q * np.float32(0.25)).reshape(shape).astype(F)            # given scale 0.25: exact in every F
+    scale = np.full(scheme.scales_shape(shape), 0.25, dtype=F)
+    codes, out_scale = O.quantize(x, scale, scheme)
+    g_codes, g_out_scale = gpu_quantize(x, scale, scheme)
+    assert_bits_equal(g_codes, codes, "codes (given scale)")
+    assert_bits_equal(g_out_scale, out_scale, "out_scale")
+    d_codes, d_scale = gpu_quantize_dynamic(x, scheme)
+    o_codes, o_scale = O.quantize_dynamic(x, scheme)
+    assert_bits_equal(d_codes, o_codes, "codes (fused)")
+    assert_bits_equal(d_scale, o_scale, "scales (fused)")
+
+
 @pytest.mark.parametrize("fname", list(FLOATS))
 def test_per_tensor_routes_agree(fname, tuning):
     """Per tensor, the fused call has two routes: one cooperative launch (absmax, grid barrier,
