@@ -15,6 +15,14 @@
 
 namespace qk {
 
+// CTAs of 256 threads of `kernel` that one SM holds at a time.
+template <typename Kernel> static int resident_ctas(Kernel kernel)
+{
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) n = 1;
+    return n;
+}
+
 // ---------------------------------------------------------------------------------------
 // absmax
 // ---------------------------------------------------------------------------------------
@@ -132,8 +140,11 @@ cudaError_t launch_absmax_batch(int fdt, const AbsmaxBatchArgs &args, const Laun
     if (args.ntensors < 1) return cudaSuccess;
     const long long total = args.chunk_end[args.ntensors - 1];
     if (total == 0) return cudaSuccess;
+    // One wave of resident CTAs: a partial second wave would take as long as a full one.
+    static const int occ[3] = {resident_ctas(absmax_batch_kernel<QK_F32>), resident_ctas(absmax_batch_kernel<QK_F16>),
+                               resident_ctas(absmax_batch_kernel<QK_BF16>)};
     long long need = (total + 1023) / 1024;
-    const long long cap = (long long)cfg.sm_count * 8;
+    const long long cap = (long long)cfg.sm_count * (cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : occ[fdt == QK_F32 ? 0 : fdt == QK_F16 ? 1 : 2]);
     if (need > cap) need = cap;
     const bool pdl = cfg.pdl != 0;
     switch (fdt) {
@@ -200,7 +211,13 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
         return cudaGetLastError();
     }
     const int per = (fdt == QK_F32) ? 4 : 8;
-    const int grid = grid_for(n / per + 1, threads * 4, cfg);
+    // One wave of resident CTAs (the f32 instance holds 6 per SM, the 16-bit ones 8): with a fixed 8 per SM the
+    // f32 kernel ran a third of a second wave and took 110 us instead of 78 us on 470 MB.
+    static const int occ[3] = {resident_ctas(absmax_kernel<QK_F32>), resident_ctas(absmax_kernel<QK_F16>),
+                               resident_ctas(absmax_kernel<QK_BF16>)};
+    LaunchCfg wave = cfg;
+    if (wave.ctas_per_sm <= 0) wave.ctas_per_sm = occ[fdt == QK_F32 ? 0 : fdt == QK_F16 ? 1 : 2];
+    const int grid = grid_for(n / per + 1, threads * 4, wave);
     const bool pdl = cfg.pdl != 0;
     switch (fdt) {
     case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell);

@@ -459,15 +459,35 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
         uint32_t raw[UNR][RAW];
         int tk[UNR];
         long long lidx[UNR];
+        // Given block scales are fetched together with the data, so that the two latencies overlap
+        // (loaded after the data, they cost a second round trip per iteration: 5.6 -> 6.1 TB/s on f32 q4).
+        float given[UNR];
+        long long given_idx[UNR];
+        bool given_starts[UNR];
+        const bool block_scales_given = !DYN && (lg >= 0 || a.b2.enabled);
         const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
+            given[k] = 1.0f;
+            given_idx[k] = 0;
+            given_starts[k] = false;
             if (full || idx < a.nunits) {
                 while (ti + 1 < a.ntensors && idx >= a.t[ti].unit_end) ++ti;
                 tk[k] = ti;
                 lidx[k] = idx - (ti ? a.t[ti - 1].unit_end : 0);
                 load_unit<UB>(raw[k], static_cast<const char *>(a.t[ti].in) + lidx[k] * UB, aligned32);
+                if constexpr (!DYN) {
+                    if (block_scales_given) {
+                        if (a.b2.enabled) {
+                            given_idx[k] = blocks2d_scale_index(a.b2, (unsigned)lidx[k], &given_starts[k]);
+                        } else {
+                            given_idx[k] = lidx[k] >> lg;
+                            given_starts[k] = (lidx[k] & ((1ll << lg) - 1)) == 0;
+                        }
+                        given[k] = static_cast<float>(static_cast<const F *>(a.t[ti].scale_in)[given_idx[k]]);
+                    }
+                }
             } else {
                 tk[k] = ti;
                 lidx[k] = 0;
@@ -501,13 +521,10 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
                                             : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
                 }
                 scale_f = tensor_scale;
-            } else if (a.b2.enabled) {
-                sidx = blocks2d_scale_index(a.b2, (unsigned)li, &starts);
-                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
             } else {
-                sidx = li >> lg;
-                starts = (li & ((1ll << lg) - 1)) == 0;
-                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
+                sidx = given_idx[k];
+                starts = given_starts[k];
+                scale_f = given[k];
             }
             // write_scale: the scale is cast to the param type, stored, and that value (cast
             // back to F) is the divisor (crates/cubek-quant/src/quantize.rs:83-98).
