@@ -189,6 +189,14 @@ __global__ void finalize_scale_kernel(const unsigned int *cell, void *scale_out,
     store_dyn(scale_out, fdt, 0, s);
 }
 
+// `cfg` with the grid cap set to one wave of resident CTAs of `kernel` (unless a tuning key fixed it).
+template <typename Kernel> static LaunchCfg one_wave(const LaunchCfg &cfg, Kernel kernel)
+{
+    LaunchCfg c = cfg;
+    if (c.ctas_per_sm <= 0) c.ctas_per_sm = resident_ctas(kernel);
+    return c;
+}
+
 static int grid_for(long long work_items, int per_cta, const LaunchCfg &cfg)
 {
     long long need = (work_items + per_cta - 1) / per_cta;
@@ -207,7 +215,7 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
     if (n == 0) return cudaSuccess;
     const int threads = 256;
     if ((reinterpret_cast<uintptr_t>(in) & 15u) != 0) {
-        absmax_scalar_kernel<<<grid_for(n, threads * 8, cfg), threads, 0, stream>>>(in, fdt, n, cell);
+        absmax_scalar_kernel<<<grid_for(n, threads * 8, one_wave(cfg, absmax_scalar_kernel)), threads, 0, stream>>>(in, fdt, n, cell);
         return cudaGetLastError();
     }
     const int per = (fdt == QK_F32) ? 4 : 8;
@@ -231,7 +239,7 @@ cudaError_t launch_absmax_strided(const GeneralLayout &layout, const void *in, i
 {
     cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
     if (e != cudaSuccess || n == 0) return e;
-    absmax_strided_kernel<<<grid_for(n, 256 * 8, cfg), 256, 0, stream>>>(layout, in, fdt, n, cell);
+    absmax_strided_kernel<<<grid_for(n, 256 * 8, one_wave(cfg, absmax_strided_kernel)), 256, 0, stream>>>(layout, in, fdt, n, cell);
     return cudaGetLastError();
 }
 
@@ -403,19 +411,19 @@ __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScales
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nitems == 0) return cudaSuccess;
-    general_quantize_kernel<<<grid_for(a.nitems, 256, cfg), 256, 0, stream>>>(a);
+    general_quantize_kernel<<<grid_for(a.nitems, 256, one_wave(cfg, general_quantize_kernel)), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 cudaError_t launch_general_dequantize(const GeneralDequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nitems == 0) return cudaSuccess;
-    general_dequantize_kernel<<<grid_for(a.nitems, 256, cfg), 256, 0, stream>>>(a);
+    general_dequantize_kernel<<<grid_for(a.nitems, 256, one_wave(cfg, general_dequantize_kernel)), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 cudaError_t launch_general_scales(const GeneralScalesArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nblocks == 0) return cudaSuccess;
-    general_scales_kernel<<<grid_for(a.nblocks, 256, cfg), 256, 0, stream>>>(a);
+    general_scales_kernel<<<grid_for(a.nblocks, 256, one_wave(cfg, general_scales_kernel)), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -847,39 +847,44 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
 
 // -------------------------------------------------------------------------------------
 // Scales only (per block), for the two-call form: absmax over each block then the scale
-// formula, written as F.  16-byte chunks, blocks are aligned runs of 2^lg lanes.
+// formula, written as F.  A thread reduces UB contiguous bytes (64 when blocks are made of whole
+// 64-byte units, else 32 or 16) in registers; blocks are aligned runs of 2^lg lanes, finished with
+// lg shuffle rounds (f32 blocks of 128 elements: 3 rounds on 64-byte units instead of 5 on
+// 16-byte chunks).
 // -------------------------------------------------------------------------------------
-template <int FDT>
-__global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void *scale_out, long long nchunks,
-                                                           int lg_chunks_per_block, float range, float inv_range)
+template <int FDT, int UB>
+__global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void *scale_out, long long nunits,
+                                                           int lg_units_per_block, float range, float inv_range,
+                                                           int aligned32)
 {
     using F = typename ElemOf<FDT>::type;
-    constexpr int UNR = 4;
+    constexpr int RAW = UB / 4;
+    constexpr int UNR = (UB >= 64) ? 2 : 4;
     const char *in = static_cast<const char *>(in_);
-    const int lg = lg_chunks_per_block;
+    const int lg = lg_units_per_block;
     pdl_entry();
     const long long stride = (long long)gridDim.x * blockDim.x * UNR;
-    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
+    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nunits;
          base += stride) {
-        uint32_t raw[UNR][4];
+        uint32_t raw[UNR][RAW];
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            if (idx < nchunks) {
-                load_unit<16>(raw[k], in + idx * 16, false);
+            if (idx < nunits) {
+                load_unit<UB>(raw[k], in + idx * UB, aligned32 != 0);
             } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) raw[k][i] = 0u;
+                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
             }
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            float amax = unit_absmax<FDT, 4>(raw[k]);
+            float amax = unit_absmax<FDT, RAW>(raw[k]);
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1)
                 if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-            if (idx < nchunks && (idx & ((1ll << lg) - 1)) == 0)
+            if (idx < nunits && (idx & ((1ll << lg) - 1)) == 0)
                 static_cast<F *>(scale_out)[idx >> lg] =
                     static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
         }
@@ -952,8 +957,9 @@ cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool cl
                             const LaunchCfg &cfg, cudaStream_t stream);
 // Device flag the staged kernels set when a bounded wait gives up (address of the current device).
 int *stage_error_flag();
-cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nchunks, int lg, float range,
-                                float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
+// `unit_bytes` in {16, 32, 64}; `lg` = log2(units per block), at most 5.
+cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
+                                float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_block_scales_2d(int fdt, const void *in, void *scale_out, long long rows, long long cols,
                                    int block_rows, int block_cols, float range, float inv_range, const LaunchCfg &cfg,
                                    cudaStream_t stream);

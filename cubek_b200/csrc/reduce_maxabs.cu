@@ -61,7 +61,17 @@ cudaError_t launch_maxabs(int fdt, const void *in, void *out, long long outer, l
                           const LaunchCfg &cfg, cudaStream_t stream)
 {
     const bool pdl = cfg.pdl != 0;
-    const long long cap = (long long)cfg.sm_count * 8;
+    // one wave of resident CTAs (these kernels hold 6 CTAs of 256 threads per SM)
+    auto resident = [](auto kernel) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) n = 1;
+        return n;
+    };
+    static const int occ_last[3] = {resident(maxabs_last_axis_kernel<QK_F32>), resident(maxabs_last_axis_kernel<QK_F16>),
+                                    resident(maxabs_last_axis_kernel<QK_BF16>)};
+    static const int occ_inner = resident(maxabs_inner_axis_kernel);
+    const int per_sm = (inner == 1) ? occ_last[fdt == QK_F32 ? 0 : fdt == QK_F16 ? 1 : 2] : occ_inner;
+    const long long cap = (long long)cfg.sm_count * (cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : per_sm);
     if (inner == 1) {
         const int esz = (fdt == QK_F32) ? 4 : 2;
         const int per = 16 / esz;
