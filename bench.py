@@ -31,10 +31,17 @@ METRIC = "quantize+dequantize HBM GB/s"
 SPEC_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of each kernel on a
-# 32768-row case, scaled by rows to the bench tensor (summaries of those captures are kept under profiles/).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch and per tensor from one ncu capture of each kernel
+# on a reduced number of rows (still larger than L2), scaled by rows to the bench tensor; summaries of those
+# captures are kept under profiles/.  Reads equal the algorithmic reads; writes come out lower than the
+# algorithmic writes because part of the output is still dirty in L2 when the kernel ends.
 NCU_TRAFFIC_BYTES = {
-    "q4_block32_bf16_14336x4096": {"quantize_dynamic": 145.2e6, "dequantize": 130.4e6},   # per tensor
+    "q4_block32_bf16_14336x4096": {"quantize_dynamic": 145.2e6, "dequantize": 130.4e6},
+    "e2m1_block16_f16_8192x4096": {"quantize_dynamic": 84.6e6, "dequantize": 78.3e6},
+    "q2_block64_f32_65536x4096": {"quantize_dynamic": 1145.0e6, "dequantize": 941.9e6},
+    "q8_block128_bf16_14336x4096": {"quantize_dynamic": 164.9e6, "dequantize": 154.5e6},
+    "q8_tensor_bf16_14336x4096": {"quantize_dynamic": 281.3e6},        # absmax kernel + quantize kernel
+    "q8_tensor_f32_4096x4096": {"quantize_dynamic": 70.5e6},           # cooperative kernel, second pass from L2
 }
 
 
