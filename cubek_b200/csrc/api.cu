@@ -200,6 +200,32 @@ static bool is_contiguous(const QkTensor *t)
     return true;
 }
 
+// A view whose strides are a permutation of a dense row-major layout (a transposed matrix, a permuted
+// N-d tensor): its elements fill `numel` consecutive positions from `ptr`, so an order-independent
+// reduction may walk the memory instead of the view.
+static bool is_dense_permutation(const QkTensor *t)
+{
+    int order[QK_MAX_RANK];
+    int n = 0;
+    for (int d = 0; d < t->rank; ++d) {
+        if (t->shape[d] == 1) continue;
+        if (t->strides[d] <= 0) return false;
+        order[n++] = d;
+    }
+    for (int i = 1; i < n; ++i)   // insertion sort by stride
+        for (int j = i; j > 0 && t->strides[order[j]] < t->strides[order[j - 1]]; --j) {
+            const int tmp = order[j];
+            order[j] = order[j - 1];
+            order[j - 1] = tmp;
+        }
+    long long expect = 1;
+    for (int i = 0; i < n; ++i) {
+        if (t->strides[order[i]] != expect) return false;
+        expect *= t->shape[order[i]];
+    }
+    return true;
+}
+
 static int check_tensor(const QkTensor *t, int elem_size)
 {
     if (!t || !t->shape || !t->strides) return QK_ERR_NULL;
@@ -293,6 +319,7 @@ static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *sca
         L.out_scale_strides[d] = (!g.per_tensor && out_scales && d < g.rank) ? out_scales->strides[d] : 0;
         L.data_strides[d] = (data && d < g.rank) ? data->strides[d] : 0;
     }
+    finish_layout(L);
 }
 
 static int log2_exact(long long v)
@@ -390,6 +417,7 @@ static GeneralLayout strided_data_layout(const QkTensor *t)
         L.block[d] = 1;
         L.scale_strides[d] = L.out_scale_strides[d] = 0;
     }
+    finish_layout(L);
     return L;
 }
 
@@ -423,7 +451,7 @@ static int absmax_into_cells(int count, const QkTensor *inputs, const bool *skip
             if ((rc = flush())) return rc;
             continue;
         }
-        if (!is_contiguous(&inputs[i])) {
+        if (!is_contiguous(&inputs[i]) && !is_dense_permutation(&inputs[i])) {
             if ((rc = flush())) return rc;
             count_launch();
             const GeneralLayout L = strided_data_layout(&inputs[i]);
@@ -672,7 +700,7 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
         unsigned int *cell = static_cast<unsigned int *>(workspace);
         count_launch(g.n > 0 ? 3 : 2);
         cudaError_t e;
-        if (contiguous) {
+        if (contiguous || is_dense_permutation(input)) {
             e = launch_absmax(input_dtype, input->ptr, g.n, cell, cfg, stream);
         } else {
             GeneralLayout L;
@@ -734,7 +762,7 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
         if (rc != QK_ERR_TOO_LARGE) return rc;   // done, or a real error; TOO_LARGE = route not applicable
         count_launch(n > 0 ? 2 : 1);
         cudaError_t e;
-        if (is_contiguous(input)) {
+        if (is_contiguous(input) || is_dense_permutation(input)) {
             e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
         } else {
             Geometry g;
@@ -788,7 +816,7 @@ int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, voi
     if (!aligned(absmax_out, 4)) return QK_ERR_ALIGN;
     const long long n = numel(input);
     count_launch(n > 0 ? 2 : 1);
-    if (!is_contiguous(input)) {
+    if (!is_contiguous(input) && !is_dense_permutation(input)) {
         const GeneralLayout L = strided_data_layout(input);
         return cuda_status(launch_absmax_strided(L, input->ptr, input_dtype, n, reinterpret_cast<unsigned int *>(absmax_out),
                                                  current_cfg(), static_cast<cudaStream_t>(stream)));

@@ -165,17 +165,14 @@ __global__ void __launch_bounds__(256) absmax_scalar_kernel(const void *in, int 
     if ((threadIdx.x & 31) == 0) atomicMax(cell, __float_as_uint(amax));
 }
 
+__device__ __forceinline__ long long data_index(const GeneralLayout &L, long long pos);
+
 __global__ void __launch_bounds__(256) absmax_strided_kernel(const GeneralLayout L, const void *in, int fdt, long long n,
                                                              unsigned int *cell)
 {
     float amax = 0.0f;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        long long offs = i, idx = 0;
-        for (int d = L.rank - 1; d >= 0; --d) {
-            idx += (offs % L.shape[d]) * L.data_strides[d];
-            offs /= L.shape[d];
-        }
-        amax = fmaxf(amax, fabsf(load_dyn(in, fdt, idx)));
+        amax = fmaxf(amax, fabsf(load_dyn(in, fdt, data_index(L, i))));
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
@@ -263,6 +260,23 @@ __device__ __forceinline__ long long general_scale_pos(const GeneralLayout &L, l
         if (out_pos) *out_pos = 0;
         return 0;
     }
+    if (L.fits31) {
+        unsigned offs = (unsigned)pos;
+        long long sp = 0, sp_out = 0;
+        bool start = true;
+        for (int d = L.rank - 1; d >= 0; --d) {
+            const unsigned q = fastdiv(offs, L.shape_div[d]);
+            const unsigned coord = offs - q * L.shape_div[d].div;
+            offs = q;
+            const unsigned b = fastdiv(coord, L.block_div[d]);
+            sp += (long long)b * L.scale_strides[d];
+            sp_out += (long long)b * L.out_scale_strides[d];
+            start = start && (coord - b * L.block_div[d].div == 0);
+        }
+        *is_start = start;
+        if (out_pos) *out_pos = sp_out;
+        return sp;
+    }
     long long offs = pos, sp = 0, sp_out = 0;
     bool start = true;
     for (int d = L.rank - 1; d >= 0; --d) {
@@ -281,6 +295,16 @@ __device__ __forceinline__ long long general_scale_pos(const GeneralLayout &L, l
 __device__ __forceinline__ long long data_index(const GeneralLayout &L, long long pos)
 {
     if (L.data_contiguous) return pos;
+    if (L.fits31) {
+        unsigned offs = (unsigned)pos;
+        long long idx = 0;
+        for (int d = L.rank - 1; d >= 0; --d) {
+            const unsigned q = fastdiv(offs, L.shape_div[d]);
+            idx += (long long)(offs - q * L.shape_div[d].div) * L.data_strides[d];
+            offs = q;
+        }
+        return idx;
+    }
     long long offs = pos, idx = 0;
     for (int d = L.rank - 1; d >= 0; --d) {
         idx += (offs % L.shape[d]) * L.data_strides[d];
@@ -374,37 +398,58 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
     }
 }
 
-// One thread per block of the scales tensor: absmax over the (possibly clipped) N-d block.
+// One thread per block of the scales tensor: absmax over the (possibly clipped) N-d block.  The block is
+// walked row by row (runs along the last dim) with an odometer over the other dims, so the element loop
+// has no division.
 __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScalesArgs a)
 {
     const GeneralLayout &L = a.layout;
+    const int last = L.rank - 1;
     for (long long bi = (long long)blockIdx.x * blockDim.x + threadIdx.x; bi < a.nblocks;
          bi += (long long)gridDim.x * blockDim.x) {
-        long long bc[QK_MAX_RANK], ext[QK_MAX_RANK];
-        long long rem = bi, cnt = 1, sp = 0;
+        int ext[QK_MAX_RANK], at[QK_MAX_RANK];
+        long long rem = bi, sp = 0, lin = 0, mul = 1, rows = 1;
+        long long stride[QK_MAX_RANK];
         for (int d = L.rank - 1; d >= 0; --d) {
             const long long nb = (L.shape[d] + L.block[d] - 1) / L.block[d];
-            bc[d] = rem % nb;
+            const long long bc = rem % nb;
             rem /= nb;
-        }
-        for (int d = 0; d < L.rank; ++d) {
-            const long long start = bc[d] * L.block[d];
-            ext[d] = (L.shape[d] - start < L.block[d]) ? L.shape[d] - start : L.block[d];
-            cnt *= ext[d];
-            sp += bc[d] * L.scale_strides[d];
+            const long long start = bc * L.block[d];
+            ext[d] = (int)((L.shape[d] - start < L.block[d]) ? L.shape[d] - start : L.block[d]);
+            stride[d] = L.data_contiguous ? mul : L.data_strides[d];
+            mul *= L.shape[d];
+            lin += start * stride[d];
+            sp += bc * L.scale_strides[d];
+            at[d] = 0;
+            if (d != last) rows *= ext[d];
         }
         float amax = 0.0f;
-        for (long long k = 0; k < cnt; ++k) {
-            long long r = k, lin = 0, mul = 1;
-            for (int d = L.rank - 1; d >= 0; --d) {
-                const long long coord = bc[d] * L.block[d] + r % ext[d];
-                r /= ext[d];
-                lin += coord * (L.data_contiguous ? mul : L.data_strides[d]);
-                mul *= L.shape[d];
+        for (long long r = 0; r < rows; ++r) {
+            for (int k = 0; k < ext[last]; ++k) amax = fmaxf(amax, fabsf(load_dyn(a.in, a.fdt, lin + k * stride[last])));
+            // next row of the block: advance the odometer over dims last-1 .. 0
+            for (int d = last - 1; d >= 0; --d) {
+                lin += stride[d];
+                if (++at[d] < ext[d]) break;
+                lin -= (long long)ext[d] * stride[d];
+                at[d] = 0;
             }
-            amax = fmaxf(amax, fabsf(load_dyn(a.in, a.fdt, lin)));
         }
         store_dyn(a.scale_out, a.fdt, sp, __fdiv_rn(2.0f * amax, a.range));
+    }
+}
+
+void finish_layout(GeneralLayout &L)
+{
+    long long n = 1;
+    bool ok = true;
+    for (int d = 0; d < L.rank; ++d) {
+        n *= L.shape[d];
+        ok = ok && L.shape[d] >= 1 && L.shape[d] < (1ll << 31) && L.block[d] >= 1 && L.block[d] < (1ll << 31) && n < (1ll << 31);
+    }
+    L.fits31 = ok ? 1 : 0;
+    for (int d = 0; d < QK_MAX_RANK; ++d) {
+        L.shape_div[d] = make_fastdiv((ok && d < L.rank) ? (unsigned)L.shape[d] : 1u);
+        L.block_div[d] = make_fastdiv((ok && d < L.rank) ? (unsigned)L.block[d] : 1u);
     }
 }
 

@@ -20,7 +20,15 @@ struct GeneralLayout {
     // dequantize.  The reference reaches it through `linear_view`, which honours strides.
     long long data_strides[QK_MAX_RANK];
     int data_contiguous;
+    // Tensors of fewer than 2^31 elements take 32-bit index arithmetic with one multiply-high per
+    // division (the 64-bit div/mod chain costs several hundred instructions per stored item).
+    int fits31;
+    FastDiv shape_div[QK_MAX_RANK];
+    FastDiv block_div[QK_MAX_RANK];
 };
+
+// Fills fits31 / shape_div / block_div from rank, shape and block.
+void finish_layout(GeneralLayout &layout);
 
 struct GeneralQuantArgs {
     GeneralLayout layout;
