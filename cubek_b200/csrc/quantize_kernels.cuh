@@ -433,6 +433,50 @@ template <int OW> __device__ __forceinline__ void store_words(uint32_t *dst, con
 }
 
 // -------------------------------------------------------------------------------------
+// Pieces shared by the direct and the staged kernel.
+// -------------------------------------------------------------------------------------
+
+// Scale of a fused unit: absmax of its block (the unit's own registers, then the lanes that share the
+// block: aligned runs of 2^lg lanes; every lane of the warp takes part), then the scale formula.
+template <int FDT, int RAW>
+__device__ __forceinline__ float fused_unit_scale(const uint32_t *raw, int lg, float range, float inv_range)
+{
+    float amax = unit_absmax<FDT, RAW>(raw);
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1)
+        if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    return round_to<FDT>(div_by_range(2.0f * amax, range, inv_range));
+}
+
+// Scale of a per-tensor launch (given as a tensor of one F, or derived from a device absmax cell).
+template <int FDT>
+__device__ __forceinline__ float tensor_unit_scale(const QuantArgs &a, const QuantTensor &T, int tensor)
+{
+    using F = typename ElemOf<FDT>::type;
+    return a.absmax ? round_to<FDT>(div_by_range(2.0f * a.absmax[tensor], a.range, a.inv_range))
+                    : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
+}
+
+// write_scale, quantize, store: the scale is cast to the param type, stored by the unit that starts
+// the block (unit 0 for per tensor), and that value cast back to F is the divisor
+// (crates/cubek-quant/src/quantize.rs:83-98).
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
+__device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTensor &T, const uint32_t *raw, float scale_f,
+                                            long long sidx, bool starts, long long li, bool valid, bool aligned32)
+{
+    constexpr int OW = UnitT<FDT, KIND, UB>::OW;
+    const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
+    const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
+    if (valid && starts) store_dyn(T.out_scale, a.param, sidx, s_fs);
+    uint32_t w[OW];
+    if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s))
+        quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw, s, a.lo, a.hi, w);
+    else
+        quantize_unit_exact<FDT, KIND, UB>(raw, s, a.lo, a.hi, w);
+    if (valid) store_words<OW>(static_cast<uint32_t *>(T.out) + li * OW, w, aligned32);
+}
+
+// -------------------------------------------------------------------------------------
 // The kernel.  DYN = true: scale from the block's own absmax (one pass, fused).
 // DYN = false: scale given (tensor of F, one per block) or derived from a device absmax.
 // -------------------------------------------------------------------------------------
@@ -508,41 +552,20 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
             if constexpr (DYN) {
                 sidx = li >> lg;
                 starts = (li & ((1ll << lg) - 1)) == 0;
-                float amax = unit_absmax<FDT, RAW>(raw[k]);
-                // Blocks are aligned runs of 2^lg lanes; every lane of the warp takes part.
-#pragma unroll
-                for (int m = 1; m < 32; m <<= 1)
-                    if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-                scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
+                scale_f = fused_unit_scale<FDT, RAW>(raw[k], lg, a.range, a.inv_range);
             } else if (lg < 0 && !a.b2.enabled) {
                 if (scale_ti != tk[k]) {
                     scale_ti = tk[k];
-                    tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * a.absmax[scale_ti], a.range, a.inv_range))
-                                            : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
+                    tensor_scale = tensor_unit_scale<FDT>(a, T, scale_ti);
                 }
                 scale_f = tensor_scale;
+                starts = (li == 0);
             } else {
                 sidx = given_idx[k];
                 starts = given_starts[k];
                 scale_f = given[k];
             }
-            // write_scale: the scale is cast to the param type, stored, and that value (cast
-            // back to F) is the divisor (crates/cubek-quant/src/quantize.rs:83-98).
-            const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
-            const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
-            if (valid) {
-                if (lg < 0 && !a.b2.enabled) {
-                    if (li == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
-                } else if (starts) {
-                    store_dyn(T.out_scale, a.param, sidx, s_fs);
-                }
-            }
-            uint32_t w[OW];
-            if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s))
-                quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], s, a.lo, a.hi, w);
-            else
-                quantize_unit_exact<FDT, KIND, UB>(raw[k], s, a.lo, a.hi, w);
-            if (valid) store_words<OW>(static_cast<uint32_t *>(T.out) + li * OW, w, aligned32);
+            finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
         }
     }
 }
@@ -689,41 +712,24 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
             if constexpr (DYN) {
                 sidx = li >> lg;
                 starts = (li & ((1ll << lg) - 1)) == 0;
-                float amax = unit_absmax<FDT, RAW>(raw[k]);
-#pragma unroll
-                for (int m = 1; m < 32; m <<= 1)
-                    if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-                scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
+                scale_f = fused_unit_scale<FDT, RAW>(raw[k], lg, a.range, a.inv_range);
             } else if (lg < 0 && !a.b2.enabled) {
                 if (scale_ti != ti) {
                     scale_ti = ti;
-                    tensor_scale = a.absmax ? round_to<FDT>(div_by_range(2.0f * a.absmax[ti], a.range, a.inv_range))
-                                            : static_cast<float>(static_cast<const F *>(T.scale_in)[0]);
+                    tensor_scale = tensor_unit_scale<FDT>(a, T, ti);
                 }
                 scale_f = tensor_scale;
-            } else if (a.b2.enabled) {
-                sidx = blocks2d_scale_index(a.b2, (unsigned)li, &starts);
-                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
+                starts = (li == 0);
             } else {
-                sidx = li >> lg;
-                starts = (li & ((1ll << lg) - 1)) == 0;
+                if (a.b2.enabled) {
+                    sidx = blocks2d_scale_index(a.b2, (unsigned)li, &starts);
+                } else {
+                    sidx = li >> lg;
+                    starts = (li & ((1ll << lg) - 1)) == 0;
+                }
                 scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
             }
-            const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
-            const float sc = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
-            if (valid) {
-                if (lg < 0 && !a.b2.enabled) {
-                    if (li == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
-                } else if (starts) {
-                    store_dyn(T.out_scale, a.param, sidx, s_fs);
-                }
-            }
-            uint32_t w[OW];
-            if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(sc))
-                quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], sc, a.lo, a.hi, w);
-            else
-                quantize_unit_exact<FDT, KIND, UB>(raw[k], sc, a.lo, a.hi, w);
-            if (valid) store_words<OW>(static_cast<uint32_t *>(T.out) + li * OW, w, aligned32);
+            finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
         }
     }
 }
