@@ -131,3 +131,14 @@ def test_host_roundtrip_staging_size():
     slots, slice_bytes = lib.qk_get_tuning(_ffi.TUNE_SLOTS), lib.qk_get_tuning(_ffi.TUNE_SLICE_KIB) << 10
     assert (slots, slice_bytes) == (4, 16 << 20)
     assert slots * slice_bytes < n < slots * 3 * slice_bytes     # input + codes + scales + restored per slot
+
+
+def test_device_header_probe_library_is_built():
+    """The test kernel of the public device header is compiled together with the library (sm_100a) and
+    exports its one entry point; it is only run on a GPU (tests/test_gpu_device_api.py)."""
+    import ctypes
+    from pathlib import Path
+
+    probe = Path(__file__).resolve().parent / "device_api" / "libdevice_api_probe.so"
+    assert probe.exists(), "run `python -m cubek_b200.build`"
+    assert hasattr(ctypes.CDLL(str(probe)), "probe_dequantize")
