@@ -40,8 +40,7 @@ NCU_TRAFFIC_BYTES = {
     "e2m1_block16_f16_8192x4096": {"quantize_dynamic": 84.6e6, "dequantize": 78.3e6},
     "q2_block64_f32_65536x4096": {"quantize_dynamic": 1145.0e6, "dequantize": 941.9e6},
     "q8_block128_bf16_14336x4096": {"quantize_dynamic": 164.9e6, "dequantize": 154.5e6},
-    "q8_tensor_bf16_14336x4096": {"quantize_dynamic": 281.3e6},        # absmax kernel + quantize kernel
-    "q8_tensor_f32_4096x4096": {"quantize_dynamic": 70.5e6},           # cooperative kernel, second pass from L2
+    "q8_tensor_bf16_14336x4096": {"quantize_dynamic": 281.3e6},        # absmax pass + quantize pass
 }
 
 
