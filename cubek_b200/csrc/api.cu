@@ -226,6 +226,26 @@ static bool is_dense_permutation(const QkTensor *t)
     return true;
 }
 
+// Rows (runs along the last dim) contiguous, rows a constant number of elements apart: a column slice
+// of a wider matrix, a matrix with padded rows.  Leading dims must step uniformly over the rows.
+static bool is_row_strided(const QkTensor *t, long long *row_stride)
+{
+    const int r = t->rank;
+    if (r < 2 || (t->shape[r - 1] != 1 && t->strides[r - 1] != 1)) return false;
+    long long expect = 0;
+    for (int d = r - 2; d >= 0; --d) {
+        if (t->shape[d] == 1) continue;
+        if (expect == 0) {
+            if (t->strides[d] < t->shape[r - 1]) return false;
+            *row_stride = t->strides[d];
+        } else if (t->strides[d] != expect) {
+            return false;
+        }
+        expect = (expect == 0 ? t->strides[d] : expect) * t->shape[d];
+    }
+    return expect != 0;
+}
+
 static int check_tensor(const QkTensor *t, int elem_size)
 {
     if (!t || !t->shape || !t->strides) return QK_ERR_NULL;
@@ -341,7 +361,13 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
-    if (!aligned(in->ptr, 16) || !is_contiguous(in)) return -2;
+    if (!aligned(in->ptr, 16)) return -2;
+    long long row_stride = 0;
+    const bool strided_rows = !is_contiguous(in);
+    if (strided_rows) {
+        // rows of whole units, every row 16-byte aligned, no tiles over two dims
+        if (!is_row_strided(in, &row_stride) || (row_stride * esz) % 16 != 0 || g.blocks_2d) return -2;
+    }
     if (!g.per_tensor) {
         if (!g.last_dim_blocks && !g.blocks_2d) return -2;
         if (scale && !is_contiguous(scale)) return -2;
@@ -353,6 +379,7 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
         if (ub < min_unit_bytes(fdt, g.kind)) continue;
         const int U = ub / esz;
         if (g.n % U != 0) continue;
+        if (strided_rows && (g.shape[g.rank - 1] % U != 0 || g.n / U >= (1ll << 31))) continue;
         const int out_words = U / kind_elems_per_u32(g.kind);
         const int out_align = out_words >= 4 ? 16 : 4 * out_words;
         if (!aligned(out->ptr, out_align)) continue;
@@ -384,13 +411,17 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
-    if (!aligned(out->ptr, 16) || !is_contiguous(out)) return -2;
+    if (!aligned(out->ptr, 16)) return -2;
+    long long row_stride = 0;
+    const bool strided_rows = !is_contiguous(out);
+    if (strided_rows && (!is_row_strided(out, &row_stride) || (row_stride * esz) % 16 != 0 || g.blocks_2d)) return -2;
     if (!g.per_tensor && ((!g.last_dim_blocks && !g.blocks_2d) || !is_contiguous(params))) return -2;
     const int candidates[2] = {64, min_dequant_bytes(fdt, g.kind)};
     for (int ci = 0; ci < 2; ++ci) {
         const int ob = candidates[ci];
         const int E = ob / esz;
         if (g.n % E != 0) continue;
+        if (strided_rows && (g.shape[g.rank - 1] % E != 0 || g.n / E >= (1ll << 31))) continue;
         const int in_words = E / kind_elems_per_u32(g.kind);
         if (!aligned(values->ptr, in_words >= 4 ? 16 : 4 * in_words)) continue;
         *out_bytes = ob;
@@ -419,6 +450,28 @@ static GeneralLayout strided_data_layout(const QkTensor *t)
     }
     finish_layout(L);
     return L;
+}
+
+// absmax of any float tensor into `*cell`: in memory order for contiguous and densely permuted views, row by
+// row for row-strided ones (whole 16-byte chunks per row), element by element through the strides otherwise.
+static cudaError_t absmax_of(const QkTensor *t, int dtype, long long n, unsigned int *cell, const LaunchCfg &cfg,
+                             cudaStream_t stream, bool zero_first)
+{
+    if (is_contiguous(t) || is_dense_permutation(t)) return launch_absmax(dtype, t->ptr, n, cell, cfg, stream, zero_first);
+    const int fsize = dtype_size(dtype);
+    const int per16 = 16 / fsize;
+    const long long cols = t->shape[t->rank - 1];
+    long long row_stride = 0;
+    if (is_row_strided(t, &row_stride) && aligned(t->ptr, 16) && (row_stride * fsize) % 16 == 0 && cols % per16 == 0 &&
+        n / per16 < (1ll << 31)) {
+        RowStride rs;
+        rs.enabled = 1;
+        rs.units_per_row = make_fastdiv((unsigned)(cols / per16));
+        rs.row_bytes = row_stride * fsize;
+        return launch_absmax(dtype, t->ptr, n, cell, cfg, stream, zero_first, &rs);
+    }
+    const GeneralLayout L = strided_data_layout(t);
+    return launch_absmax_strided(L, t->ptr, dtype, n, cell, cfg, stream);   // clears the cell itself
 }
 
 // absmax of `count` tensors into `cells[0..count)` (already zero): tensors that are contiguous, start on
@@ -454,8 +507,7 @@ static int absmax_into_cells(int count, const QkTensor *inputs, const bool *skip
         if (!is_contiguous(&inputs[i]) && !is_dense_permutation(&inputs[i])) {
             if ((rc = flush())) return rc;
             count_launch();
-            const GeneralLayout L = strided_data_layout(&inputs[i]);
-            const cudaError_t e = launch_absmax_strided(L, inputs[i].ptr, input_dtype, n, cells + i, cfg, stream);
+            const cudaError_t e = absmax_of(&inputs[i], input_dtype, n, cells + i, cfg, stream, false);
             if (e != cudaSuccess) return cuda_status(e);
             continue;
         }
@@ -482,12 +534,12 @@ struct QuantBatch {
     QuantArgs a;
     int fdt = -1, kind = -1, unit_bytes = 0;
     bool dyn = false, clamp = false;
-    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; }
+    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; a.rs.enabled = 0; }
 };
 struct DequantBatch {
     DequantArgs a;
     int fdt = -1, kind = -1, out_bytes = 0;
-    DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; }
+    DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; a.rs.enabled = 0; }
 };
 
 static int flush_quant(QuantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
@@ -699,14 +751,7 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
         if (!aligned(workspace, 4)) return QK_ERR_ALIGN;
         unsigned int *cell = static_cast<unsigned int *>(workspace);
         count_launch(g.n > 0 ? 3 : 2);
-        cudaError_t e;
-        if (contiguous || is_dense_permutation(input)) {
-            e = launch_absmax(input_dtype, input->ptr, g.n, cell, cfg, stream);
-        } else {
-            GeneralLayout L;
-            fill_layout(L, g, nullptr, nullptr, input);
-            e = launch_absmax_strided(L, input->ptr, input_dtype, g.n, cell, cfg, stream);
-        }
+        const cudaError_t e = absmax_of(input, input_dtype, g.n, cell, cfg, stream, true);
         if (e != cudaSuccess) return cuda_status(e);
         return cuda_status(launch_finalize_scale(cell, scale->ptr, input_dtype, range, stream));
     }
@@ -761,16 +806,7 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
         rc = try_quantize_tensor_coop(input, output, out_scale, scheme, input_dtype, workspace, workspace_bytes, stream);
         if (rc != QK_ERR_TOO_LARGE) return rc;   // done, or a real error; TOO_LARGE = route not applicable
         count_launch(n > 0 ? 2 : 1);
-        cudaError_t e;
-        if (is_contiguous(input) || is_dense_permutation(input)) {
-            e = launch_absmax(input_dtype, input->ptr, n, cell, current_cfg(), stream);
-        } else {
-            Geometry g;
-            if ((rc = build_geometry(g, scheme, input, nullptr))) return rc;
-            GeneralLayout L;
-            fill_layout(L, g, nullptr, nullptr, input);
-            e = launch_absmax_strided(L, input->ptr, input_dtype, n, cell, current_cfg(), stream);
-        }
+        const cudaError_t e = absmax_of(input, input_dtype, n, cell, current_cfg(), stream, true);
         if (e != cudaSuccess) return cuda_status(e);
         return quantize_common(input, output, nullptr, out_scale, reinterpret_cast<const float *>(cell), false,
                                nullptr, scheme, input_dtype, stream);
@@ -816,13 +852,8 @@ int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, voi
     if (!aligned(absmax_out, 4)) return QK_ERR_ALIGN;
     const long long n = numel(input);
     count_launch(n > 0 ? 2 : 1);
-    if (!is_contiguous(input) && !is_dense_permutation(input)) {
-        const GeneralLayout L = strided_data_layout(input);
-        return cuda_status(launch_absmax_strided(L, input->ptr, input_dtype, n, reinterpret_cast<unsigned int *>(absmax_out),
-                                                 current_cfg(), static_cast<cudaStream_t>(stream)));
-    }
-    return cuda_status(launch_absmax(input_dtype, input->ptr, n, reinterpret_cast<unsigned int *>(absmax_out),
-                                     current_cfg(), static_cast<cudaStream_t>(stream)));
+    return cuda_status(absmax_of(input, input_dtype, n, reinterpret_cast<unsigned int *>(absmax_out), current_cfg(),
+                                 static_cast<cudaStream_t>(stream), true));
 }
 
 int qk_absmax_batch(int count, const QkTensor *inputs, int input_dtype, float *absmax_out, void *stream_)
@@ -987,10 +1018,14 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         const bool symmetric = (lo == -hi);
         const bool clamp = need_clamp(input_dtype, g.kind, dynamic, symmetric, scheme->param);
         const long long nunits = g.n / (unit_bytes / fsize);
-        const int a32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32)) ? 1 : 0;
+        long long row_stride = 0;
+        const bool strided_rows = !is_contiguous(input) && is_row_strided(input, &row_stride);
+        const int a32 = (aligned(input->ptr, 32) && aligned(output->ptr, 32) &&
+                         (!strided_rows || (row_stride * fsize) % 32 == 0)) ? 1 : 0;
         // A tensor joins the pending launch only if it needs the very same kernel and constants;
         // per-tensor absmax cells must be consecutive (the kernel indexes them by tensor).
         const bool joins = !g.blocks_2d && !b.a.b2.enabled &&   // tile geometry is per launch
+                           !strided_rows && !b.a.rs.enabled &&  // and so is a row stride
                            b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == input_dtype &&
                            b.kind == g.kind && b.unit_bytes == unit_bytes && b.dyn == dynamic && b.clamp == clamp &&
                            b.a.lg_units_per_block == lg && b.a.param == scheme->param && b.a.lo == lo && b.a.hi == hi &&
@@ -1014,6 +1049,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             b.a.force_exact = cfg.force_exact;
             b.a.aligned32 = 1;
             b.a.b2 = make_blocks2d(g, unit_bytes / fsize, lg);
+            b.a.rs.enabled = strided_rows ? 1 : 0;
+            b.a.rs.units_per_row = make_fastdiv(strided_rows ? (unsigned)(g.shape[g.rank - 1] / (unit_bytes / fsize)) : 1u);
+            b.a.rs.row_bytes = strided_rows ? row_stride * fsize : 0;
         }
         QuantTensor &t = b.a.t[b.a.ntensors];
         t.in = input->ptr;
@@ -1105,7 +1143,9 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     if (lg >= -1) {
         DequantBatch local;
         DequantBatch &b = batch ? *batch : local;
-        const bool joins = !g.blocks_2d && !b.a.b2.enabled &&
+        long long row_stride = 0;
+        const bool strided_rows = !is_contiguous(output) && is_row_strided(output, &row_stride);
+        const bool joins = !g.blocks_2d && !b.a.b2.enabled && !strided_rows && !b.a.rs.enabled &&
                            b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == output_dtype &&
                            b.kind == g.kind && b.out_bytes == out_bytes && b.a.lg_units_per_block == lg &&
                            b.a.param == scheme->param;
@@ -1118,6 +1158,9 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
             b.a.param = scheme->param;
             b.a.aligned32 = 1;
             b.a.b2 = make_blocks2d(g, out_bytes / fsize, lg);
+            b.a.rs.enabled = strided_rows ? 1 : 0;
+            b.a.rs.units_per_row = make_fastdiv(strided_rows ? (unsigned)(g.shape[g.rank - 1] / (out_bytes / fsize)) : 1u);
+            b.a.rs.row_bytes = strided_rows ? row_stride * fsize : 0;
         }
         DequantTensor &t = b.a.t[b.a.ntensors];
         t.values = values->ptr;
@@ -1125,7 +1168,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
         t.out = output->ptr;
         b.a.nunits += g.n / (out_bytes / fsize);
         t.unit_end = b.a.nunits;
-        b.a.aligned32 &= aligned(output->ptr, 32) ? 1 : 0;
+        b.a.aligned32 &= (aligned(output->ptr, 32) && (!strided_rows || (row_stride * fsize) % 32 == 0)) ? 1 : 0;
         b.a.ntensors += 1;
         return batch ? QK_OK : flush_dequant(b, cfg, stream);
     }

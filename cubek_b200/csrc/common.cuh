@@ -301,6 +301,14 @@ __device__ __forceinline__ unsigned blocks2d_scale_index(const Blocks2D &b, unsi
     return rb * b.scales_per_row + (cu >> b.lg_units_per_block_col);
 }
 
+// A float tensor whose rows are contiguous but `row_bytes` apart (a column slice of a wider matrix, padded
+// rows): unit u lies in row u / units_per_row.  One tensor per launch.
+struct RowStride {
+    int enabled;
+    FastDiv units_per_row;
+    long long row_bytes;
+};
+
 // ---- launch bookkeeping -----------------------------------------------------------------
 
 struct LaunchCfg {

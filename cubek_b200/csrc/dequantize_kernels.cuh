@@ -32,6 +32,7 @@ struct DequantArgs {
     long long nunits;        // dequant units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     Blocks2D b2;             // [rows, cols] tiles instead of runs
+    RowStride rs;            // row-strided output (one tensor per launch)
     int param;               // QkParam
     int aligned32;           // every output base 32-byte aligned (256-bit stores allowed)
 };
@@ -189,7 +190,12 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                 const DequantTensor &T = a.t[ti];
                 const long long li = idx - (ti ? a.t[ti - 1].unit_end : 0);
                 const uint32_t *vals = static_cast<const uint32_t *>(T.values);
-                dst[k] = static_cast<char *>(T.out) + li * OB;
+                long long offset = li * OB;
+                if (a.rs.enabled) {
+                    const unsigned row = fastdiv((unsigned)li, a.rs.units_per_row);
+                    offset = (long long)row * a.rs.row_bytes + (long long)((unsigned)li - row * a.rs.units_per_row.div) * OB;
+                }
+                dst[k] = static_cast<char *>(T.out) + offset;
                 if constexpr (IW == 1) {
                     w[k][0] = __ldg(vals + li);
                 } else if constexpr (IW == 2) {

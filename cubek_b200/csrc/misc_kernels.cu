@@ -27,7 +27,7 @@ template <typename Kernel> static int resident_ctas(Kernel kernel)
 // absmax
 // ---------------------------------------------------------------------------------------
 template <int FDT>
-__global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long n, unsigned int *cell)
+__global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long n, unsigned int *cell, const RowStride rs)
 {
     constexpr int PER = FInfo<FDT>::PER16;
     constexpr int UNR = 4;
@@ -43,7 +43,12 @@ __global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long 
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
-            raw[k] = (idx < nchunks) ? ldg128_stream(in + idx * 16) : Vec16{{0u, 0u, 0u, 0u}};
+            long long offset = idx * 16;
+            if (rs.enabled) {   // rows of whole 16-byte chunks, `row_bytes` apart
+                const unsigned row = fastdiv((unsigned)idx, rs.units_per_row);
+                offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx - row * rs.units_per_row.div) * 16;
+            }
+            raw[k] = (idx < nchunks) ? ldg128_stream(in + offset) : Vec16{{0u, 0u, 0u, 0u}};
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
@@ -203,15 +208,20 @@ static int grid_for(long long work_items, int per_cta, const LaunchCfg &cfg)
 }
 
 cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
-                          cudaStream_t stream, bool zero_first)
+                          cudaStream_t stream, bool zero_first, const RowStride *row_stride)
 {
+    RowStride rs;
+    rs.enabled = 0;
+    rs.units_per_row = make_fastdiv(1u);
+    rs.row_bytes = 0;
+    if (row_stride) rs = *row_stride;
     if (zero_first) {
         cudaError_t e = cudaMemsetAsync(cell, 0, sizeof(unsigned int), stream);
         if (e != cudaSuccess) return e;
     }
     if (n == 0) return cudaSuccess;
     const int threads = 256;
-    if ((reinterpret_cast<uintptr_t>(in) & 15u) != 0) {
+    if ((reinterpret_cast<uintptr_t>(in) & 15u) != 0 && !rs.enabled) {
         absmax_scalar_kernel<<<grid_for(n, threads * 8, one_wave(cfg, absmax_scalar_kernel)), threads, 0, stream>>>(in, fdt, n, cell);
         return cudaGetLastError();
     }
@@ -225,9 +235,9 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
     const int grid = grid_for(n / per + 1, threads * 4, wave);
     const bool pdl = cfg.pdl != 0;
     switch (fdt) {
-    case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell);
-    case QK_F16: return launch_kernel(absmax_kernel<QK_F16>, grid, threads, stream, pdl, in, n, cell);
-    default: return launch_kernel(absmax_kernel<QK_BF16>, grid, threads, stream, pdl, in, n, cell);
+    case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell, rs);
+    case QK_F16: return launch_kernel(absmax_kernel<QK_F16>, grid, threads, stream, pdl, in, n, cell, rs);
+    default: return launch_kernel(absmax_kernel<QK_BF16>, grid, threads, stream, pdl, in, n, cell, rs);
     }
 }
 

@@ -62,8 +62,9 @@ struct GeneralScalesArgs {
 
 // absmax of `n` elements max-reduced into `*cell` (bit pattern of a non-negative f32).  The cell
 // must hold zero (or an earlier partial result) beforehand; `zero_first` clears it on the stream.
+// `row_stride` (optional): rows of whole 16-byte chunks, a constant number of bytes apart, 16-byte aligned.
 cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *cell, const LaunchCfg &cfg,
-                          cudaStream_t stream, bool zero_first = true);
+                          cudaStream_t stream, bool zero_first = true, const RowStride *row_stride = nullptr);
 // absmax of every tensor of a batch in one launch.  `chunk_end` counts 16-byte chunks across the batch;
 // every tensor must start on a 16-byte boundary and hold a whole number of chunks.  `cells[i]` must be
 // zero (or hold an earlier partial result) beforehand.

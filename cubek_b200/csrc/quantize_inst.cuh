@@ -28,7 +28,7 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     if (need > cap) need = cap;
     if (need < 1) need = 1;
     // cfg.staged: 0 = units below 64 bytes, 1 = always, 2 = never
-    if ((cfg.staged == 1 || (cfg.staged == 0 && UB < 64)) && threads == 256) {
+    if ((cfg.staged == 1 || (cfg.staged == 0 && UB < 64)) && threads == 256 && !args.rs.enabled) {
         // bulk-copy staged variant: cfg.stages x 16 KB stages + barriers per CTA, a whole number of waves
         const int nstages = cfg.stages < 2 ? 2 : (cfg.stages > QK_MAX_STAGES ? QK_MAX_STAGES : cfg.stages);
         const int SMEM = nstages * QK_TILE_BYTES + QK_MAX_STAGES * 8;

@@ -48,6 +48,7 @@ struct QuantArgs {
     long long nunits;        // units in the whole batch
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     Blocks2D b2;             // [rows, cols] tiles instead of runs (given-scale form only)
+    RowStride rs;            // row-strided input (direct kernel only)
     int param;               // QkParam of out_scale
     float lo, hi, range;     // clamp bounds, hi - lo
     float inv_range;         // RN(1 / range), computed on the host
@@ -520,7 +521,13 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
                 while (ti + 1 < a.ntensors && idx >= a.t[ti].unit_end) ++ti;
                 tk[k] = ti;
                 lidx[k] = idx - (ti ? a.t[ti - 1].unit_end : 0);
-                load_unit<UB>(raw[k], static_cast<const char *>(a.t[ti].in) + lidx[k] * UB, aligned32);
+                long long offset = lidx[k] * UB;
+                if (a.rs.enabled) {
+                    const unsigned row = fastdiv((unsigned)lidx[k], a.rs.units_per_row);
+                    offset = (long long)row * a.rs.row_bytes +
+                             (long long)((unsigned)lidx[k] - row * a.rs.units_per_row.div) * UB;
+                }
+                load_unit<UB>(raw[k], static_cast<const char *>(a.t[ti].in) + offset, aligned32);
                 if constexpr (!DYN) {
                     if (block_scales_given) {
                         if (a.b2.enabled) {

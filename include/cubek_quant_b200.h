@@ -94,7 +94,8 @@ int qk_value_range(int value, float *lo, float *hi);
 
 /*
  * Replaces `cubek_quant::quantize::launch_ref` (quantize.rs:174-221), same argument order.
- *   input     float tensor of type `input_dtype`; may be strided (contiguous ones take the fast kernels)
+ *   input     float tensor of type `input_dtype`; may be strided (contiguous ones, and ones whose rows are
+ *             contiguous and a constant 16-byte-aligned stride apart, take the fast kernels)
  *   output    quantized tensor: u32 words of shape [.., n/num_quants] (QK_STORE_U32), or
  *             1-byte items (QK_STORE_NATIVE: i8, e4m3, e5m2; fp4 pairs of shape [.., n/2])
  *   scale     scales typed `input_dtype`: shape [1] per tensor, else one per block
