@@ -18,9 +18,9 @@ namespace qk {
 cudaError_t launch_quantize_f32(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_quantize_f16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_quantize_bf16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_f32(const void *, void *, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_f16(const void *, void *, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f32(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_f16(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
 
 cudaError_t launch_block_scales_2d_f32(const void *, void *, long long, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_2d_f16(const void *, void *, long long, long long, int, int, float, float, const LaunchCfg &, cudaStream_t);
@@ -65,12 +65,12 @@ cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool cl
 }
 
 cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
-                                float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+                                float range, float inv_range, const RowStride &rs, const LaunchCfg &cfg, cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_block_scales_f32(in, scale_out, nunits, unit_bytes, lg, range, inv_range, cfg, stream);
-    case QK_F16: return launch_block_scales_f16(in, scale_out, nunits, unit_bytes, lg, range, inv_range, cfg, stream);
-    case QK_BF16: return launch_block_scales_bf16(in, scale_out, nunits, unit_bytes, lg, range, inv_range, cfg, stream);
+    case QK_F32: return launch_block_scales_f32(in, scale_out, nunits, unit_bytes, lg, range, inv_range, rs, cfg, stream);
+    case QK_F16: return launch_block_scales_f16(in, scale_out, nunits, unit_bytes, lg, range, inv_range, rs, cfg, stream);
+    case QK_BF16: return launch_block_scales_bf16(in, scale_out, nunits, unit_bytes, lg, range, inv_range, rs, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -757,7 +757,9 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
     }
     if (g.n == 0) return QK_OK;
     const int per16 = 16 / fsize;
-    if (!g_tune[TUNE_FORCE_GENERAL].load() && contiguous && g.last_dim_blocks && aligned(input->ptr, 16) &&
+    long long row_stride = 0;
+    const bool strided_rows = !contiguous && is_row_strided(input, &row_stride) && (row_stride * fsize) % 16 == 0;
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && (contiguous || strided_rows) && g.last_dim_blocks && aligned(input->ptr, 16) &&
         is_contiguous(scale)) {
         // the largest per-thread unit that blocks are made of, with at most 32 lanes per block
         for (int ub = 64; ub >= 16; ub >>= 1) {
@@ -765,9 +767,14 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
             if (g.B % U != 0) continue;
             const int lg = log2_exact(g.B / U);
             if (lg < 0 || lg > 5) continue;
+            if (strided_rows && g.n / U >= (1ll << 31)) continue;
+            RowStride rs;
+            rs.enabled = strided_rows ? 1 : 0;
+            rs.units_per_row = make_fastdiv(strided_rows ? (unsigned)(g.cols / U) : 1u);
+            rs.row_bytes = strided_rows ? row_stride * fsize : 0;
             count_launch();
             return cuda_status(launch_block_scales(input_dtype, input->ptr, scale->ptr, g.n / U, ub, lg, range,
-                                                   1.0f / range, cfg, stream));
+                                                   1.0f / range, rs, cfg, stream));
         }
     }
     if (!g_tune[TUNE_FORCE_GENERAL].load() && contiguous && g.blocks_2d && g.B % per16 == 0 && aligned(input->ptr, 16) &&

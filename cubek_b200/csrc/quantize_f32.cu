@@ -8,9 +8,10 @@ cudaError_t launch_quantize_f32(int kind, int unit_bytes, bool dyn, bool clamp, 
     return launch_quantize_t<QK_F32>(kind, unit_bytes, dyn, clamp, args, cfg, stream);
 }
 cudaError_t launch_block_scales_f32(const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
-                                     float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+                                     float range, float inv_range, const RowStride &rs, const LaunchCfg &cfg,
+                                     cudaStream_t stream)
 {
-    return launch_block_scales_t<QK_F32>(in, scale_out, nunits, unit_bytes, lg, range, inv_range, cfg, stream);
+    return launch_block_scales_t<QK_F32>(in, scale_out, nunits, unit_bytes, lg, range, inv_range, rs, cfg, stream);
 }
 cudaError_t launch_quantize_tensor_f32(int kind, QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
                                       cudaStream_t stream)

@@ -145,7 +145,7 @@ static cudaError_t launch_quantize_tensor_t(int kind, QuantTensorArgs &args, int
 
 template <int FDT, int UB>
 static cudaError_t launch_block_scales_unit(const void *in, void *scale_out, long long nunits, int lg, float range,
-                                            float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+                                            float inv_range, const RowStride &rs, const LaunchCfg &cfg, cudaStream_t stream)
 {
     constexpr int UNR = (UB >= 64) ? 2 : 4;
     const int threads = 256;
@@ -154,19 +154,20 @@ static cudaError_t launch_block_scales_unit(const void *in, void *scale_out, lon
     const long long cap = (long long)cfg.sm_count * occ;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    const int aligned32 = (reinterpret_cast<uintptr_t>(in) & 31u) == 0 ? 1 : 0;
+    const int aligned32 = ((reinterpret_cast<uintptr_t>(in) & 31u) == 0 && (!rs.enabled || rs.row_bytes % 32 == 0)) ? 1 : 0;
     return launch_kernel(block_scales_kernel<FDT, UB>, (int)need, threads, stream, cfg.pdl != 0, in, scale_out, nunits, lg,
-                         range, inv_range, aligned32);
+                         range, inv_range, aligned32, rs);
 }
 
 template <int FDT>
 static cudaError_t launch_block_scales_t(const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
-                                         float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+                                         float range, float inv_range, const RowStride &rs, const LaunchCfg &cfg,
+                                         cudaStream_t stream)
 {
     switch (unit_bytes) {
-    case 64: return launch_block_scales_unit<FDT, 64>(in, scale_out, nunits, lg, range, inv_range, cfg, stream);
-    case 32: return launch_block_scales_unit<FDT, 32>(in, scale_out, nunits, lg, range, inv_range, cfg, stream);
-    case 16: return launch_block_scales_unit<FDT, 16>(in, scale_out, nunits, lg, range, inv_range, cfg, stream);
+    case 64: return launch_block_scales_unit<FDT, 64>(in, scale_out, nunits, lg, range, inv_range, rs, cfg, stream);
+    case 32: return launch_block_scales_unit<FDT, 32>(in, scale_out, nunits, lg, range, inv_range, rs, cfg, stream);
+    case 16: return launch_block_scales_unit<FDT, 16>(in, scale_out, nunits, lg, range, inv_range, rs, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -868,7 +868,7 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
 template <int FDT, int UB>
 __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void *scale_out, long long nunits,
                                                            int lg_units_per_block, float range, float inv_range,
-                                                           int aligned32)
+                                                           int aligned32, const RowStride rs)
 {
     using F = typename ElemOf<FDT>::type;
     constexpr int RAW = UB / 4;
@@ -884,7 +884,12 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             if (idx < nunits) {
-                load_unit<UB>(raw[k], in + idx * UB, aligned32 != 0);
+                long long offset = idx * UB;
+                if (rs.enabled) {
+                    const unsigned row = fastdiv((unsigned)idx, rs.units_per_row);
+                    offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx - row * rs.units_per_row.div) * UB;
+                }
+                load_unit<UB>(raw[k], in + offset, aligned32 != 0);
             } else {
 #pragma unroll
                 for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
@@ -972,7 +977,7 @@ cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool cl
 int *stage_error_flag();
 // `unit_bytes` in {16, 32, 64}; `lg` = log2(units per block), at most 5.
 cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
-                                float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
+                                float range, float inv_range, const RowStride &rs, const LaunchCfg &cfg, cudaStream_t stream);
 cudaError_t launch_block_scales_2d(int fdt, const void *in, void *scale_out, long long rows, long long cols,
                                    int block_rows, int block_cols, float range, float inv_range, const LaunchCfg &cfg,
                                    cudaStream_t stream);
