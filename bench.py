@@ -319,6 +319,16 @@ def run_gpu(args, workload):
     # serialise launch and execution and time the gap, not the kernel).
     q_avg = timed(quant_batch, args.steps)
     d_avg = timed(dequant_batch, args.steps)
+    # Distribution over single steps (an event pair per step; the gaps they add are part of these figures).
+    per_step = []
+    for _ in range(min(args.steps, 50)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        per_step.append((a, b))
+    torch.cuda.synchronize()
+    per_step = sorted(a.elapsed_time(b) for a, b in per_step)
     single_ms = timed(step_single, max(args.steps // 2, 1))
     single_q = timed(lambda: [c() for c in quant_calls], max(args.steps // 2, 1)) / B
     single_d = timed(lambda: [c() for c in dequant_calls], max(args.steps // 2, 1)) / B
@@ -368,6 +378,8 @@ def run_gpu(args, workload):
             "ms_per_step": round(single_ms, 4),
             "quantize_dynamic": {"avg_ms": round(single_q, 5), "gbs": round(q_bytes / single_q / 1e6, 1)},
             "dequantize": {"avg_ms": round(single_d, 5), "gbs": round(d_bytes / single_d / 1e6, 1)}},
+        "step_ms": {"median": round(per_step[len(per_step) // 2], 4), "best": round(per_step[0], 4),
+                    "worst": round(per_step[-1], 4), "samples": len(per_step)},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "finite_output": err_ok,
     }
     if world == 1:
