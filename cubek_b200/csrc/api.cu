@@ -246,6 +246,15 @@ static bool is_row_strided(const QkTensor *t, long long *row_stride)
     return expect != 0;
 }
 
+// A transposed matrix: rank 2, element (r, c) at c * ld + r with ld >= rows.
+static bool is_transposed_matrix(const QkTensor *t, long long *ld)
+{
+    if (t->rank != 2 || t->shape[0] < 2 || t->shape[1] < 2) return false;
+    if (t->strides[0] != 1 || t->strides[1] < t->shape[0]) return false;
+    *ld = t->strides[1];
+    return true;
+}
+
 static int check_tensor(const QkTensor *t, int elem_size)
 {
     if (!t || !t->shape || !t->strides) return QK_ERR_NULL;
@@ -534,12 +543,12 @@ struct QuantBatch {
     QuantArgs a;
     int fdt = -1, kind = -1, unit_bytes = 0;
     bool dyn = false, clamp = false;
-    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; a.rs.enabled = 0; }
+    QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; a.rs.enabled = 0; a.tr.enabled = 0; }
 };
 struct DequantBatch {
     DequantArgs a;
     int fdt = -1, kind = -1, out_bytes = 0;
-    DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; a.rs.enabled = 0; }
+    DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; a.rs.enabled = 0; a.tr.enabled = 0; }
 };
 
 static int flush_quant(QuantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
@@ -1075,6 +1084,47 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     }
     if (batch && (rc = flush_quant(*batch, cfg, stream))) return rc;
 
+    // Transposed matrix views: units gathered across memory rows, coalesced over the logical rows.
+    long long ld = 0;
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(input, &ld) && !g.blocks_2d &&
+        (g.per_tensor || (g.last_dim_blocks && is_contiguous(out_scale) && (!scale || is_contiguous(scale)))) &&
+        !(dynamic && g.per_tensor)) {
+        for (int ub = 64; ub >= 32; ub >>= 1) {
+            if (ub < min_unit_bytes(input_dtype, g.kind)) break;
+            const long long U = ub / fsize;
+            if (g.shape[1] % U != 0 || (!g.per_tensor && g.B != U)) continue;
+            const int out_words = (int)(U / kind_elems_per_u32(g.kind));
+            if (!aligned(output->ptr, out_words >= 4 ? 16 : 4 * out_words)) continue;
+            if (g.n / U >= (1ll << 31) || g.shape[0] >= (1ll << 31)) continue;
+            QuantBatch one;
+            one.a.ntensors = 1;
+            one.a.nunits = g.n / U;
+            one.a.absmax = absmax;
+            one.a.lg_units_per_block = g.per_tensor ? -1 : 0;
+            one.a.param = scheme->param;
+            one.a.lo = lo;
+            one.a.hi = hi;
+            one.a.range = hi - lo;
+            one.a.inv_range = 1.0f / (hi - lo);
+            one.a.force_exact = cfg.force_exact;
+            one.a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
+            one.a.tr.enabled = 1;
+            one.a.tr.rows = make_fastdiv((unsigned)g.shape[0]);
+            one.a.tr.ld = ld;
+            one.a.tr.units_per_row = (unsigned)(g.shape[1] / U);
+            one.a.t[0].in = input->ptr;
+            one.a.t[0].out = output->ptr;
+            one.a.t[0].scale_in = scale ? scale->ptr : nullptr;
+            one.a.t[0].out_scale = out_scale->ptr;
+            one.a.t[0].unit_end = one.a.nunits;
+            one.a.t[0].tile_end = 0;
+            const bool symmetric = (lo == -hi);
+            const bool clamp = need_clamp(input_dtype, g.kind, dynamic, symmetric, scheme->param);
+            count_launch();
+            return cuda_status(launch_quantize_transposed(input_dtype, g.kind, ub, dynamic, clamp, one.a, cfg, stream));
+        }
+    }
+
     // Layout-general route.
     GeneralQuantArgs a;
     const void *scale_ptr = scale ? scale->ptr : nullptr;
@@ -1180,6 +1230,34 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
         return batch ? QK_OK : flush_dequant(b, cfg, stream);
     }
     if (batch && (rc = flush_dequant(*batch, cfg, stream))) return rc;
+    long long ld = 0;
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(output, &ld) && !g.blocks_2d &&
+        (g.per_tensor || (g.last_dim_blocks && is_contiguous(params)))) {
+        for (int ob = 64; ob >= 32; ob >>= 1) {
+            if (ob < min_dequant_bytes(output_dtype, g.kind)) break;
+            const long long E = ob / fsize;
+            if (g.shape[1] % E != 0 || (!g.per_tensor && g.B != E)) continue;
+            const int in_words = (int)(E / kind_elems_per_u32(g.kind));
+            if (!aligned(values->ptr, 4 * (in_words >= 4 ? 4 : in_words))) continue;
+            if (g.n / E >= (1ll << 31) || g.shape[0] >= (1ll << 31)) continue;
+            DequantBatch one;
+            one.a.ntensors = 1;
+            one.a.nunits = g.n / E;
+            one.a.lg_units_per_block = g.per_tensor ? -1 : 0;
+            one.a.param = scheme->param;
+            one.a.aligned32 = 0;
+            one.a.tr.enabled = 1;
+            one.a.tr.rows = make_fastdiv((unsigned)g.shape[0]);
+            one.a.tr.ld = ld;
+            one.a.tr.units_per_row = (unsigned)(g.shape[1] / E);
+            one.a.t[0].values = values->ptr;
+            one.a.t[0].params = params->ptr;
+            one.a.t[0].out = output->ptr;
+            one.a.t[0].unit_end = one.a.nunits;
+            count_launch();
+            return cuda_status(launch_dequantize_transposed(output_dtype, g.kind, ob, one.a, cfg, stream));
+        }
+    }
     GeneralDequantArgs a;
     fill_layout(a.layout, g, params, nullptr, output);
     a.values = values->ptr;

@@ -309,6 +309,15 @@ struct RowStride {
     long long row_bytes;
 };
 
+// A transposed matrix view: logical [rows, cols], element (r, c) at c * ld + r (elements).  Work items are
+// numbered with r fastest; `units_per_row` units make one logical row.  One tensor per launch.
+struct Transposed {
+    int enabled;
+    FastDiv rows;
+    long long ld;
+    unsigned units_per_row;
+};
+
 // ---- launch bookkeeping -----------------------------------------------------------------
 
 struct LaunchCfg {

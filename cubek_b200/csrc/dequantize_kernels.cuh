@@ -33,6 +33,7 @@ struct DequantArgs {
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     Blocks2D b2;             // [rows, cols] tiles instead of runs
     RowStride rs;            // row-strided output (one tensor per launch)
+    Transposed tr;           // transposed output (dequantize_transposed_kernel only)
     int param;               // QkParam
     int aligned32;           // every output base 32-byte aligned (256-bit stores allowed)
 };
@@ -261,5 +262,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
 
 cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
                               cudaStream_t stream);
+cudaError_t launch_dequantize_transposed(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+                                         cudaStream_t stream);
 
 }  // namespace qk

@@ -49,6 +49,7 @@ struct QuantArgs {
     int lg_units_per_block;  // log2(units per block); -1 = per tensor
     Blocks2D b2;             // [rows, cols] tiles instead of runs (given-scale form only)
     RowStride rs;            // row-strided input (direct kernel only)
+    Transposed tr;           // transposed input (quantize_transposed_kernel only)
     int param;               // QkParam of out_scale
     float lo, hi, range;     // clamp bounds, hi - lo
     float inv_range;         // RN(1 / range), computed on the host
@@ -973,6 +974,9 @@ __global__ void __launch_bounds__(256) block_scales_2d_kernel(const void *in_, v
 // Host-side launchers, one translation unit per float type.
 cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream);
+// Transposed matrix views (transposed_kernels.cu): one tensor, unit = block (lg 0) or per tensor (lg -1).
+cudaError_t launch_quantize_transposed(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+                                       const LaunchCfg &cfg, cudaStream_t stream);
 // Device flag the staged kernels set when a bounded wait gives up (address of the current device).
 int *stage_error_flag();
 // `unit_bytes` in {16, 32, 64}; `lg` = log2(units per block), at most 5.
