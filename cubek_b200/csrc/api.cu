@@ -1108,10 +1108,14 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             one.a.inv_range = 1.0f / (hi - lo);
             one.a.force_exact = cfg.force_exact;
             one.a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
+            // 16-bit types: two rows per work item when rows come in 4-byte aligned pairs
+            const bool pairs = fsize == 2 && g.shape[0] % 2 == 0 && ld % 2 == 0 && aligned(input->ptr, 4);
             one.a.tr.enabled = 1;
-            one.a.tr.rows = make_fastdiv((unsigned)g.shape[0]);
+            one.a.tr.pairs = pairs ? 1 : 0;
+            one.a.tr.rows = make_fastdiv((unsigned)(pairs ? g.shape[0] / 2 : g.shape[0]));
             one.a.tr.ld = ld;
             one.a.tr.units_per_row = (unsigned)(g.shape[1] / U);
+            if (pairs) one.a.nunits /= 2;     // work items; every item yields two units
             one.a.t[0].in = input->ptr;
             one.a.t[0].out = output->ptr;
             one.a.t[0].scale_in = scale ? scale->ptr : nullptr;
@@ -1246,10 +1250,13 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
             one.a.lg_units_per_block = g.per_tensor ? -1 : 0;
             one.a.param = scheme->param;
             one.a.aligned32 = 0;
+            const bool pairs = fsize == 2 && g.shape[0] % 2 == 0 && ld % 2 == 0 && aligned(output->ptr, 4);
             one.a.tr.enabled = 1;
-            one.a.tr.rows = make_fastdiv((unsigned)g.shape[0]);
+            one.a.tr.pairs = pairs ? 1 : 0;
+            one.a.tr.rows = make_fastdiv((unsigned)(pairs ? g.shape[0] / 2 : g.shape[0]));
             one.a.tr.ld = ld;
             one.a.tr.units_per_row = (unsigned)(g.shape[1] / E);
+            if (pairs) one.a.nunits /= 2;     // work items; every item writes two units
             one.a.t[0].values = values->ptr;
             one.a.t[0].params = params->ptr;
             one.a.t[0].out = output->ptr;

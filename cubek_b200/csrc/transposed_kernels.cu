@@ -85,6 +85,65 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
     }
 }
 
+// 16-bit types, even number of rows, even ld, 4-byte aligned base: a lane takes TWO adjacent logical rows and
+// reads them with one 32-bit load per column (128 bytes per warp instead of 64), then separates the two
+// units with byte permutes.  `a.tr.rows` holds rows / 2 here; a.nunits counts row pairs x column units.
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
+__global__ void __launch_bounds__(256) quantize_transposed_pair_kernel(const QuantArgs a)
+{
+    using UT = UnitT<FDT, KIND, UB>;
+    constexpr int RAW = UT::RAW;
+    constexpr int U = UT::U;
+    static_assert(FDT != QK_F32, "pairs of rows are for 16-bit types");
+    using F = typename ElemOf<FDT>::type;
+    const QuantTensor &T = a.t[0];
+    const char *in = static_cast<const char *>(T.in);
+    const bool aligned32 = a.aligned32 != 0;
+    const int lg = a.lg_units_per_block;
+    pdl_entry();
+    float tensor_scale = 0.0f;
+    bool have_tensor_scale = false;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < a.nunits;
+         w += (long long)gridDim.x * blockDim.x) {
+        const unsigned cu = fastdiv((unsigned)w, a.tr.rows);
+        const unsigned r = 2u * ((unsigned)w - cu * a.tr.rows.div);
+        const char *p = in + ((long long)cu * U * a.tr.ld + r) * 2;
+        const long long step = a.tr.ld * 2;
+        uint32_t raw[2][RAW];
+#pragma unroll
+        for (int i = 0; i < U; i += 2) {
+            const uint32_t w0 = __ldg(reinterpret_cast<const unsigned int *>(p + i * step));         // (row r, row r+1) at column i
+            const uint32_t w1 = __ldg(reinterpret_cast<const unsigned int *>(p + (i + 1) * step));   // ... at column i+1
+            raw[0][i / 2] = __byte_perm(w0, w1, 0x5410);
+            raw[1][i / 2] = __byte_perm(w0, w1, 0x7632);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long li = (long long)(r + k) * a.tr.units_per_row + cu;
+            float scale_f;
+            long long sidx = 0;
+            bool starts;
+            if constexpr (DYN) {
+                sidx = li;
+                starts = true;
+                scale_f = fused_unit_scale<FDT, RAW>(raw[k], 0, a.range, a.inv_range);
+            } else if (lg < 0) {
+                if (!have_tensor_scale) {
+                    have_tensor_scale = true;
+                    tensor_scale = tensor_unit_scale<FDT>(a, T, 0);
+                }
+                scale_f = tensor_scale;
+                starts = (li == 0);
+            } else {
+                sidx = li;
+                starts = true;
+                scale_f = static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]);
+            }
+            finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, true, aligned32);
+        }
+    }
+}
+
 template <int FDT, int KIND, int OB>
 __global__ void __launch_bounds__(256) dequantize_transposed_kernel(const DequantArgs a)
 {
@@ -125,6 +184,42 @@ __global__ void __launch_bounds__(256) dequantize_transposed_kernel(const Dequan
     }
 }
 
+// The same pairing of rows for the 16-bit output of dequantize: one 32-bit store per column and lane.
+template <int FDT, int KIND, int OB>
+__global__ void __launch_bounds__(256) dequantize_transposed_pair_kernel(const DequantArgs a)
+{
+    using DU = DUnitT<FDT, KIND, OB>;
+    constexpr int IW = DU::IW;
+    constexpr int E = DU::E;
+    constexpr int OREG_PER_WORD = DU::EPW * 2 / 4;
+    static_assert(FDT != QK_F32, "pairs of rows are for 16-bit types");
+    const DequantTensor &T = a.t[0];
+    const int lg = a.lg_units_per_block;
+    pdl_entry();
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < a.nunits;
+         w += (long long)gridDim.x * blockDim.x) {
+        const unsigned cu = fastdiv((unsigned)w, a.tr.rows);
+        const unsigned r = 2u * ((unsigned)w - cu * a.tr.rows.div);
+        uint32_t o[2][DU::OREG];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long li = (long long)(r + k) * a.tr.units_per_row + cu;
+            const uint32_t *vals = static_cast<const uint32_t *>(T.values) + li * IW;
+            const float s = round_to<FDT>(load_dyn(T.params, a.param, (lg < 0) ? 0 : li));
+            const uint32_t s2 = h2_pack<FDT>(s, s);
+#pragma unroll
+            for (int j = 0; j < IW; ++j) dequant_word<FDT, KIND>(__ldg(vals + j), s, s2, o[k] + j * OREG_PER_WORD);
+        }
+        char *p = static_cast<char *>(T.out) + ((long long)cu * E * a.tr.ld + r) * 2;
+        const long long step = a.tr.ld * 2;
+#pragma unroll
+        for (int i = 0; i < E; i += 2) {
+            *reinterpret_cast<uint32_t *>(p + i * step) = __byte_perm(o[0][i / 2], o[1][i / 2], 0x5410);        // column i of both rows
+            *reinterpret_cast<uint32_t *>(p + (i + 1) * step) = __byte_perm(o[0][i / 2], o[1][i / 2], 0x7632);  // column i + 1
+        }
+    }
+}
+
 // ---- launchers ----------------------------------------------------------------------------------
 template <typename Kernel> static int resident(Kernel kernel)
 {
@@ -146,6 +241,13 @@ static cudaError_t launch_waves(Kernel kernel, const Args &args, long long nunit
 template <int FDT, int KIND, int UB>
 static cudaError_t quantize_mode(bool dyn, bool clamp, const QuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
+    if constexpr (FDT != QK_F32) {
+        if (a.tr.pairs) {
+            if (!dyn) return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, false, true>, a, a.nunits, cfg, stream);
+            if (clamp) return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, true, true>, a, a.nunits, cfg, stream);
+            return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, true, false>, a, a.nunits, cfg, stream);
+        }
+    }
     if (!dyn) return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, false, true>, a, a.nunits, cfg, stream);
     if (clamp) return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, true, true>, a, a.nunits, cfg, stream);
     return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, true, false>, a, a.nunits, cfg, stream);
@@ -194,6 +296,15 @@ template <int FDT, int KIND>
 static cudaError_t dequantize_unit(int out_bytes, const DequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     constexpr int MINB = min_dequant_bytes(FDT, KIND);
+    if constexpr (FDT != QK_F32) {
+        if (a.tr.pairs) {
+            if (out_bytes == 64) return launch_waves(dequantize_transposed_pair_kernel<FDT, KIND, 64>, a, a.nunits, cfg, stream);
+            if constexpr (MINB <= 32) {
+                if (out_bytes == 32) return launch_waves(dequantize_transposed_pair_kernel<FDT, KIND, 32>, a, a.nunits, cfg, stream);
+            }
+            return cudaErrorInvalidValue;
+        }
+    }
     if (out_bytes == 64) return launch_waves(dequantize_transposed_kernel<FDT, KIND, 64>, a, a.nunits, cfg, stream);
     if constexpr (MINB <= 32) {
         if (out_bytes == 32) return launch_waves(dequantize_transposed_kernel<FDT, KIND, 32>, a, a.nunits, cfg, stream);
