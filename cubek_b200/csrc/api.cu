@@ -1110,12 +1110,16 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             one.a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
             // 16-bit types: two rows per work item when rows come in 4-byte aligned pairs
             const bool pairs = fsize == 2 && g.shape[0] % 2 == 0 && ld % 2 == 0 && aligned(input->ptr, 4);
+            const long long rows_per_tile = pairs ? 64 : 32;
+            const long long row_tiles = (g.shape[0] + rows_per_tile - 1) / rows_per_tile;
+            const long long unit_tiles = (g.shape[1] / U + 7) / 8;
             one.a.tr.enabled = 1;
             one.a.tr.pairs = pairs ? 1 : 0;
-            one.a.tr.rows = make_fastdiv((unsigned)(pairs ? g.shape[0] / 2 : g.shape[0]));
+            one.a.tr.rows = make_fastdiv((unsigned)row_tiles);
+            one.a.tr.nrows = (unsigned)g.shape[0];
             one.a.tr.ld = ld;
             one.a.tr.units_per_row = (unsigned)(g.shape[1] / U);
-            if (pairs) one.a.nunits /= 2;     // work items; every item yields two units
+            one.a.nunits = row_tiles * unit_tiles;     // the kernel walks tiles of rows x 8 units
             one.a.t[0].in = input->ptr;
             one.a.t[0].out = output->ptr;
             one.a.t[0].scale_in = scale ? scale->ptr : nullptr;
@@ -1254,6 +1258,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
             one.a.tr.enabled = 1;
             one.a.tr.pairs = pairs ? 1 : 0;
             one.a.tr.rows = make_fastdiv((unsigned)(pairs ? g.shape[0] / 2 : g.shape[0]));
+            one.a.tr.nrows = (unsigned)g.shape[0];
             one.a.tr.ld = ld;
             one.a.tr.units_per_row = (unsigned)(g.shape[1] / E);
             if (pairs) one.a.nunits /= 2;     // work items; every item writes two units

@@ -313,8 +313,9 @@ struct RowStride {
 // numbered with r fastest; `units_per_row` units make one logical row.  One tensor per launch.
 struct Transposed {
     int enabled;
-    int pairs;      // 16-bit types: a work item is two adjacent rows (`rows` then divides by rows / 2)
-    FastDiv rows;
+    int pairs;      // 16-bit types: a lane takes two adjacent rows
+    FastDiv rows;   // dequantize: rows (or row pairs) per column unit; quantize: row tiles
+    unsigned nrows; // logical rows
     long long ld;
     unsigned units_per_row;
 };

@@ -33,114 +33,107 @@ __device__ __forceinline__ TransposedIndex transposed_index(const Transposed &tr
     return t;
 }
 
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
+// Quantize.  A CTA takes a tile of RT logical rows x 8 column units: warp w the unit column ct*8 + w, lane l
+// the row(s) rt*RT + l (16-bit types with an even number of rows, an even ld and a 4-byte aligned base:
+// PAIR, two adjacent rows per lane read with one 32-bit load per column and separated with byte permutes).
+// The codes of a lane are only 4-32 bytes and lie a whole logical row from its neighbours', so codes and
+// scales of the tile go through shared memory and leave as runs of 8 units per logical row (32-256 bytes
+// contiguous) instead of half-filled sectors.  `a.tr.rows` divides by the number of row tiles; a.nunits
+// counts tiles, row tiles fastest (CTAs that run together then read neighbouring pieces of the same memory rows).
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, bool PAIR>
 __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArgs a)
 {
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
     constexpr int U = UT::U;
+    constexpr int OW = UT::OW;
     constexpr int ESZ = UT::ESZ;
+    constexpr int NR = PAIR ? 2 : 1;          // rows per lane
+    constexpr int RT = 32 * NR;               // rows per tile
+    constexpr int CT = 8;                     // column units per tile (one per warp)
+    constexpr int ROW_WORDS = CT * OW;        // code words of one tile row
+    static_assert(!PAIR || FDT != QK_F32, "pairs of rows are for 16-bit types");
     using F = typename ElemOf<FDT>::type;
+    __shared__ uint32_t codes_s[RT][ROW_WORDS + 1];   // +1: lanes write one column of this array
+    __shared__ float scales_s[RT][CT + 1];
     const QuantTensor &T = a.t[0];
     const char *in = static_cast<const char *>(T.in);
-    const bool aligned32 = a.aligned32 != 0;
-    const int lg = a.lg_units_per_block;   // 0 (a unit is a block) or -1 (per tensor)
+    const int lg = a.lg_units_per_block;      // 0 (a unit is a block) or -1 (per tensor)
+    const unsigned R = a.tr.nrows, upr = a.tr.units_per_row;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_entry();
     float tensor_scale = 0.0f;
-    bool have_tensor_scale = false;
-    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < a.nunits;
-         w += (long long)gridDim.x * blockDim.x) {
-        const TransposedIndex ix = transposed_index(a.tr, (unsigned)w);
-        const char *p = in + ((long long)ix.cu * U * a.tr.ld + ix.r) * ESZ;
-        const long long step = a.tr.ld * ESZ;
-        uint32_t raw[RAW];
-        if constexpr (FDT == QK_F32) {
-#pragma unroll
-            for (int i = 0; i < U; ++i) raw[i] = load_elem_bits<FDT>(p + i * step);
-        } else {
-#pragma unroll
-            for (int i = 0; i < U; i += 2)
-                raw[i / 2] = load_elem_bits<FDT>(p + i * step) | (load_elem_bits<FDT>(p + (i + 1) * step) << 16);
-        }
-        float scale_f;
-        long long sidx = 0;
-        bool starts;
-        if constexpr (DYN) {
-            sidx = ix.li;
-            starts = true;
-            scale_f = fused_unit_scale<FDT, RAW>(raw, 0, a.range, a.inv_range);
-        } else if (lg < 0) {
-            if (!have_tensor_scale) {
-                have_tensor_scale = true;
-                tensor_scale = tensor_unit_scale<FDT>(a, T, 0);
-            }
-            scale_f = tensor_scale;
-            starts = (ix.li == 0);
-        } else {
-            sidx = ix.li;
-            starts = true;
-            scale_f = static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]);
-        }
-        finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw, scale_f, sidx, starts, ix.li, true, aligned32);
-    }
-}
+    if (!DYN && lg < 0) tensor_scale = tensor_unit_scale<FDT>(a, T, 0);
 
-// 16-bit types, even number of rows, even ld, 4-byte aligned base: a lane takes TWO adjacent logical rows and
-// reads them with one 32-bit load per column (128 bytes per warp instead of 64), then separates the two
-// units with byte permutes.  `a.tr.rows` holds rows / 2 here; a.nunits counts row pairs x column units.
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
-__global__ void __launch_bounds__(256) quantize_transposed_pair_kernel(const QuantArgs a)
-{
-    using UT = UnitT<FDT, KIND, UB>;
-    constexpr int RAW = UT::RAW;
-    constexpr int U = UT::U;
-    static_assert(FDT != QK_F32, "pairs of rows are for 16-bit types");
-    using F = typename ElemOf<FDT>::type;
-    const QuantTensor &T = a.t[0];
-    const char *in = static_cast<const char *>(T.in);
-    const bool aligned32 = a.aligned32 != 0;
-    const int lg = a.lg_units_per_block;
-    pdl_entry();
-    float tensor_scale = 0.0f;
-    bool have_tensor_scale = false;
-    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < a.nunits;
-         w += (long long)gridDim.x * blockDim.x) {
-        const unsigned cu = fastdiv((unsigned)w, a.tr.rows);
-        const unsigned r = 2u * ((unsigned)w - cu * a.tr.rows.div);
-        const char *p = in + ((long long)cu * U * a.tr.ld + r) * 2;
-        const long long step = a.tr.ld * 2;
-        uint32_t raw[2][RAW];
+    for (long long tile = blockIdx.x; tile < a.nunits; tile += gridDim.x) {
+        const unsigned ct = fastdiv((unsigned)tile, a.tr.rows);
+        const unsigned rt = (unsigned)tile - ct * a.tr.rows.div;
+        const unsigned cu = ct * CT + warp;
+        const unsigned r0 = rt * RT + lane * NR;
+        const bool active = cu < upr && r0 < R;
+        uint32_t raw[NR][RAW];
+        if (active) {
+            const char *p = in + ((long long)cu * U * a.tr.ld + r0) * ESZ;
+            const long long step = a.tr.ld * ESZ;
+            if constexpr (FDT == QK_F32) {
 #pragma unroll
-        for (int i = 0; i < U; i += 2) {
-            const uint32_t w0 = __ldg(reinterpret_cast<const unsigned int *>(p + i * step));         // (row r, row r+1) at column i
-            const uint32_t w1 = __ldg(reinterpret_cast<const unsigned int *>(p + (i + 1) * step));   // ... at column i+1
-            raw[0][i / 2] = __byte_perm(w0, w1, 0x5410);
-            raw[1][i / 2] = __byte_perm(w0, w1, 0x7632);
+                for (int i = 0; i < U; ++i) raw[0][i] = load_elem_bits<FDT>(p + i * step);
+            } else if constexpr (PAIR) {
+#pragma unroll
+                for (int i = 0; i < U; i += 2) {
+                    const uint32_t w0 = __ldg(reinterpret_cast<const unsigned int *>(p + i * step));        // rows r0, r0+1 at column i
+                    const uint32_t w1 = __ldg(reinterpret_cast<const unsigned int *>(p + (i + 1) * step));  // ... at column i+1
+                    raw[0][i / 2] = __byte_perm(w0, w1, 0x5410);
+                    raw[1][i / 2] = __byte_perm(w0, w1, 0x7632);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < U; i += 2)
+                    raw[0][i / 2] = load_elem_bits<FDT>(p + i * step) | (load_elem_bits<FDT>(p + (i + 1) * step) << 16);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < NR; ++k)
+#pragma unroll
+                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
         }
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const long long li = (long long)(r + k) * a.tr.units_per_row + cu;
+        for (int k = 0; k < NR; ++k) {
             float scale_f;
-            long long sidx = 0;
-            bool starts;
             if constexpr (DYN) {
-                sidx = li;
-                starts = true;
                 scale_f = fused_unit_scale<FDT, RAW>(raw[k], 0, a.range, a.inv_range);
             } else if (lg < 0) {
-                if (!have_tensor_scale) {
-                    have_tensor_scale = true;
-                    tensor_scale = tensor_unit_scale<FDT>(a, T, 0);
-                }
                 scale_f = tensor_scale;
-                starts = (li == 0);
             } else {
-                sidx = li;
-                starts = true;
-                scale_f = static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]);
+                scale_f = active ? static_cast<float>(static_cast<const F *>(T.scale_in)[(long long)(r0 + k) * upr + cu]) : 1.0f;
             }
-            finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, true, aligned32);
+            // write_scale (crates/cubek-quant/src/quantize.rs:83-98): cast to the param type, divide by that value
+            const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
+            const float sc = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
+            uint32_t w[OW];
+            if (!a.force_exact && scale_is_safe(sc)) quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], sc, a.lo, a.hi, w);
+            else quantize_unit_exact<FDT, KIND, UB>(raw[k], sc, a.lo, a.hi, w);
+#pragma unroll
+            for (int j = 0; j < OW; ++j) codes_s[lane * NR + k][warp * OW + j] = w[j];
+            scales_s[lane * NR + k][warp] = s_fs;
+            if (lg < 0 && tile == 0 && threadIdx.x == 0 && k == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
         }
+        __syncthreads();
+        // rows of the tile leave as contiguous runs
+        uint32_t *out = static_cast<uint32_t *>(T.out);
+        for (int j = threadIdx.x; j < RT * ROW_WORDS; j += 256) {
+            const int row = j / ROW_WORDS, col = j % ROW_WORDS;
+            const unsigned grow = rt * RT + row, gcu = ct * CT + col / OW;
+            if (grow < R && gcu < upr) out[((long long)grow * upr + ct * CT) * OW + col] = codes_s[row][col];
+        }
+        if (lg >= 0) {
+            for (int j = threadIdx.x; j < RT * CT; j += 256) {
+                const int row = j / CT, c = j % CT;
+                const unsigned grow = rt * RT + row, gcu = ct * CT + c;
+                if (grow < R && gcu < upr) store_dyn(T.out_scale, a.param, (long long)grow * upr + gcu, scales_s[row][c]);
+            }
+        }
+        __syncthreads();   // the tile buffers are reused
     }
 }
 
@@ -238,19 +231,31 @@ static cudaError_t launch_waves(Kernel kernel, const Args &args, long long nunit
     return launch_kernel(kernel, (int)need, 256, stream, cfg.pdl != 0, args);
 }
 
+template <typename Kernel>
+static cudaError_t launch_tiles(Kernel kernel, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    long long need = args.nunits;   // tiles
+    const long long cap = (long long)cfg.sm_count * resident(kernel) * 4;
+    if (need > cap) need = cap;
+    if (need < 1) need = 1;
+    return launch_kernel(kernel, (int)need, 256, stream, cfg.pdl != 0, args);
+}
+
+template <int FDT, int KIND, int UB, bool PAIR>
+static cudaError_t quantize_pairing(bool dyn, bool clamp, const QuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (!dyn) return launch_tiles(quantize_transposed_kernel<FDT, KIND, UB, false, true, PAIR>, a, cfg, stream);
+    if (clamp) return launch_tiles(quantize_transposed_kernel<FDT, KIND, UB, true, true, PAIR>, a, cfg, stream);
+    return launch_tiles(quantize_transposed_kernel<FDT, KIND, UB, true, false, PAIR>, a, cfg, stream);
+}
+
 template <int FDT, int KIND, int UB>
 static cudaError_t quantize_mode(bool dyn, bool clamp, const QuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if constexpr (FDT != QK_F32) {
-        if (a.tr.pairs) {
-            if (!dyn) return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, false, true>, a, a.nunits, cfg, stream);
-            if (clamp) return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, true, true>, a, a.nunits, cfg, stream);
-            return launch_waves(quantize_transposed_pair_kernel<FDT, KIND, UB, true, false>, a, a.nunits, cfg, stream);
-        }
+        if (a.tr.pairs) return quantize_pairing<FDT, KIND, UB, true>(dyn, clamp, a, cfg, stream);
     }
-    if (!dyn) return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, false, true>, a, a.nunits, cfg, stream);
-    if (clamp) return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, true, true>, a, a.nunits, cfg, stream);
-    return launch_waves(quantize_transposed_kernel<FDT, KIND, UB, true, false>, a, a.nunits, cfg, stream);
+    return quantize_pairing<FDT, KIND, UB, false>(dyn, clamp, a, cfg, stream);
 }
 
 template <int FDT, int KIND>
