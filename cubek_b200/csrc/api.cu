@@ -255,6 +255,22 @@ static bool is_transposed_matrix(const QkTensor *t, long long *ld)
     return true;
 }
 
+// Tile geometry of the transposed quantize / scales kernels: tiles of 32 (64 with row pairs) rows x 8 units.
+static long long fill_transposed_tiles(Transposed &tr, const QkTensor *t, long long ld, int fsize, long long unit_elems)
+{
+    const bool pairs = fsize == 2 && t->shape[0] % 2 == 0 && ld % 2 == 0 && (reinterpret_cast<uintptr_t>(t->ptr) & 3u) == 0;
+    const long long rows_per_tile = pairs ? 64 : 32;
+    const long long row_tiles = (t->shape[0] + rows_per_tile - 1) / rows_per_tile;
+    const long long unit_tiles = (t->shape[1] / unit_elems + 7) / 8;
+    tr.enabled = 1;
+    tr.pairs = pairs ? 1 : 0;
+    tr.rows = make_fastdiv((unsigned)row_tiles);
+    tr.nrows = (unsigned)t->shape[0];
+    tr.ld = ld;
+    tr.units_per_row = (unsigned)(t->shape[1] / unit_elems);
+    return row_tiles * unit_tiles;
+}
+
 static int check_tensor(const QkTensor *t, int elem_size)
 {
     if (!t || !t->shape || !t->strides) return QK_ERR_NULL;
@@ -792,6 +808,15 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
         return cuda_status(launch_block_scales_2d(input_dtype, input->ptr, scale->ptr, g.n / g.cols, g.cols,
                                                   (int)g.block_rows, (int)g.B, range, 1.0f / range, cfg, stream));
     }
+    long long ld = 0;
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(input, &ld) && g.last_dim_blocks && is_contiguous(scale) &&
+        (g.B * fsize == 64 || g.B * fsize == 32) && g.n / g.B < (1ll << 31)) {
+        Transposed tr;
+        const long long ntiles = fill_transposed_tiles(tr, input, ld, fsize, g.B);
+        count_launch();
+        return cuda_status(launch_scales_transposed(input_dtype, (int)(g.B * fsize), input->ptr, scale->ptr, tr, ntiles, range,
+                                                    1.0f / range, cfg, stream));
+    }
     GeneralScalesArgs a;
     fill_layout(a.layout, g, scale, nullptr, input);
     a.in = input->ptr;
@@ -1108,18 +1133,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             one.a.inv_range = 1.0f / (hi - lo);
             one.a.force_exact = cfg.force_exact;
             one.a.aligned32 = aligned(output->ptr, 32) ? 1 : 0;
-            // 16-bit types: two rows per work item when rows come in 4-byte aligned pairs
-            const bool pairs = fsize == 2 && g.shape[0] % 2 == 0 && ld % 2 == 0 && aligned(input->ptr, 4);
-            const long long rows_per_tile = pairs ? 64 : 32;
-            const long long row_tiles = (g.shape[0] + rows_per_tile - 1) / rows_per_tile;
-            const long long unit_tiles = (g.shape[1] / U + 7) / 8;
-            one.a.tr.enabled = 1;
-            one.a.tr.pairs = pairs ? 1 : 0;
-            one.a.tr.rows = make_fastdiv((unsigned)row_tiles);
-            one.a.tr.nrows = (unsigned)g.shape[0];
-            one.a.tr.ld = ld;
-            one.a.tr.units_per_row = (unsigned)(g.shape[1] / U);
-            one.a.nunits = row_tiles * unit_tiles;     // the kernel walks tiles of rows x 8 units
+            one.a.nunits = fill_transposed_tiles(one.a.tr, input, ld, fsize, U);   // the kernel walks tiles
             one.a.t[0].in = input->ptr;
             one.a.t[0].out = output->ptr;
             one.a.t[0].scale_in = scale ? scale->ptr : nullptr;

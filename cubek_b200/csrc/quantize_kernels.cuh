@@ -977,6 +977,8 @@ cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool cl
 // Transposed matrix views (transposed_kernels.cu): one tensor, unit = block (lg 0) or per tensor (lg -1).
 cudaError_t launch_quantize_transposed(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                                        const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_scales_transposed(int fdt, int unit_bytes, const void *in, void *scale_out, const Transposed &tr,
+                                     long long ntiles, float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
 // Device flag the staged kernels set when a bounded wait gives up (address of the current device).
 int *stage_error_flag();
 // `unit_bytes` in {16, 32, 64}; `lg` = log2(units per block), at most 5.

@@ -33,6 +33,43 @@ __device__ __forceinline__ TransposedIndex transposed_index(const Transposed &tr
     return t;
 }
 
+// The unit(s) of one lane: U consecutive logical columns of row r0 (and r0 + 1 with PAIR), one element
+// (or one pair of rows) per memory row, packed in registers exactly like a contiguous unit.
+template <int FDT, int UB, bool PAIR>
+__device__ __forceinline__ void gather_units(const char *in, long long ld, unsigned cu, unsigned r0, bool active,
+                                             uint32_t (*raw)[UB / 4])
+{
+    constexpr int ESZ = FInfo<FDT>::SIZE;
+    constexpr int U = UB / ESZ;
+    constexpr int RAW = UB / 4;
+    constexpr int NR = PAIR ? 2 : 1;
+    if (!active) {
+#pragma unroll
+        for (int k = 0; k < NR; ++k)
+#pragma unroll
+            for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
+        return;
+    }
+    const char *p = in + ((long long)cu * U * ld + r0) * ESZ;
+    const long long step = ld * ESZ;
+    if constexpr (FDT == QK_F32) {
+#pragma unroll
+        for (int i = 0; i < U; ++i) raw[0][i] = load_elem_bits<FDT>(p + i * step);
+    } else if constexpr (PAIR) {
+#pragma unroll
+        for (int i = 0; i < U; i += 2) {
+            const uint32_t w0 = __ldg(reinterpret_cast<const unsigned int *>(p + i * step));        // rows r0, r0+1 at column i
+            const uint32_t w1 = __ldg(reinterpret_cast<const unsigned int *>(p + (i + 1) * step));  // ... at column i+1
+            raw[0][i / 2] = __byte_perm(w0, w1, 0x5410);
+            raw[1][i / 2] = __byte_perm(w0, w1, 0x7632);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < U; i += 2)
+            raw[0][i / 2] = load_elem_bits<FDT>(p + i * step) | (load_elem_bits<FDT>(p + (i + 1) * step) << 16);
+    }
+}
+
 // Quantize.  A CTA takes a tile of RT logical rows x 8 column units: warp w the unit column ct*8 + w, lane l
 // the row(s) rt*RT + l (16-bit types with an even number of rows, an even ld and a 4-byte aligned base:
 // PAIR, two adjacent rows per lane read with one 32-bit load per column and separated with byte permutes).
@@ -72,31 +109,7 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
         const unsigned r0 = rt * RT + lane * NR;
         const bool active = cu < upr && r0 < R;
         uint32_t raw[NR][RAW];
-        if (active) {
-            const char *p = in + ((long long)cu * U * a.tr.ld + r0) * ESZ;
-            const long long step = a.tr.ld * ESZ;
-            if constexpr (FDT == QK_F32) {
-#pragma unroll
-                for (int i = 0; i < U; ++i) raw[0][i] = load_elem_bits<FDT>(p + i * step);
-            } else if constexpr (PAIR) {
-#pragma unroll
-                for (int i = 0; i < U; i += 2) {
-                    const uint32_t w0 = __ldg(reinterpret_cast<const unsigned int *>(p + i * step));        // rows r0, r0+1 at column i
-                    const uint32_t w1 = __ldg(reinterpret_cast<const unsigned int *>(p + (i + 1) * step));  // ... at column i+1
-                    raw[0][i / 2] = __byte_perm(w0, w1, 0x5410);
-                    raw[1][i / 2] = __byte_perm(w0, w1, 0x7632);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < U; i += 2)
-                    raw[0][i / 2] = load_elem_bits<FDT>(p + i * step) | (load_elem_bits<FDT>(p + (i + 1) * step) << 16);
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < NR; ++k)
-#pragma unroll
-                for (int i = 0; i < RAW; ++i) raw[k][i] = 0u;
-        }
+        gather_units<FDT, UB, PAIR>(in, a.tr.ld, cu, r0, active, raw);
 #pragma unroll
         for (int k = 0; k < NR; ++k) {
             float scale_f;
@@ -134,6 +147,41 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
             }
         }
         __syncthreads();   // the tile buffers are reused
+    }
+}
+
+// Scales only (the two-call form) of a transposed matrix whose blocks are one unit long: same tiles, the
+// F-typed scales leave as runs of 8 per logical row.
+template <int FDT, int UB, bool PAIR>
+__global__ void __launch_bounds__(256) scales_transposed_kernel(const void *in_, void *scale_out, const Transposed tr,
+                                                                long long ntiles, float range, float inv_range)
+{
+    constexpr int RAW = UB / 4;
+    constexpr int NR = PAIR ? 2 : 1;
+    constexpr int RT = 32 * NR;
+    constexpr int CT = 8;
+    using F = typename ElemOf<FDT>::type;
+    __shared__ float scales_s[RT][CT + 1];
+    const char *in = static_cast<const char *>(in_);
+    const unsigned R = tr.nrows, upr = tr.units_per_row;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_entry();
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const unsigned ct = fastdiv((unsigned)tile, tr.rows);
+        const unsigned rt = (unsigned)tile - ct * tr.rows.div;
+        const unsigned cu = ct * CT + warp;
+        const unsigned r0 = rt * RT + lane * NR;
+        uint32_t raw[NR][RAW];
+        gather_units<FDT, UB, PAIR>(in, tr.ld, cu, r0, cu < upr && r0 < R, raw);
+#pragma unroll
+        for (int k = 0; k < NR; ++k) scales_s[lane * NR + k][warp] = fused_unit_scale<FDT, RAW>(raw[k], 0, range, inv_range);
+        __syncthreads();
+        for (int j = threadIdx.x; j < RT * CT; j += 256) {
+            const int row = j / CT, c = j % CT;
+            const unsigned grow = rt * RT + row, gcu = ct * CT + c;
+            if (grow < R && gcu < upr) static_cast<F *>(scale_out)[(long long)grow * upr + gcu] = static_cast<F>(scales_s[row][c]);
+        }
+        __syncthreads();
     }
 }
 
@@ -328,6 +376,43 @@ static cudaError_t dequantize_kind(int kind, int out_bytes, const DequantArgs &a
     case KIND_E2M1: return dequantize_unit<FDT, KIND_E2M1>(out_bytes, a, cfg, stream);
     case KIND_E4M3: return dequantize_unit<FDT, KIND_E4M3>(out_bytes, a, cfg, stream);
     case KIND_E5M2: return dequantize_unit<FDT, KIND_E5M2>(out_bytes, a, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+template <int FDT, int UB>
+static cudaError_t scales_pairing(const void *in, void *scale_out, const Transposed &tr, long long ntiles, float range,
+                                  float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    long long need = ntiles;
+    if constexpr (FDT != QK_F32) {
+        if (tr.pairs) {
+            const long long cap = (long long)cfg.sm_count * resident(scales_transposed_kernel<FDT, UB, true>) * 4;
+            if (need > cap) need = cap;
+            return launch_kernel(scales_transposed_kernel<FDT, UB, true>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, tr,
+                                 ntiles, range, inv_range);
+        }
+    }
+    const long long cap = (long long)cfg.sm_count * resident(scales_transposed_kernel<FDT, UB, false>) * 4;
+    if (need > cap) need = cap;
+    return launch_kernel(scales_transposed_kernel<FDT, UB, false>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, tr,
+                         ntiles, range, inv_range);
+}
+
+cudaError_t launch_scales_transposed(int fdt, int unit_bytes, const void *in, void *scale_out, const Transposed &tr,
+                                     long long ntiles, float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    if (ntiles < 1 || (unit_bytes != 64 && unit_bytes != 32)) return cudaErrorInvalidValue;
+    switch (fdt) {
+    case QK_F32:
+        return unit_bytes == 64 ? scales_pairing<QK_F32, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
+                                : scales_pairing<QK_F32, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
+    case QK_F16:
+        return unit_bytes == 64 ? scales_pairing<QK_F16, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
+                                : scales_pairing<QK_F16, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
+    case QK_BF16:
+        return unit_bytes == 64 ? scales_pairing<QK_BF16, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
+                                : scales_pairing<QK_BF16, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }

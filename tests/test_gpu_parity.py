@@ -456,6 +456,7 @@ def test_transposed_matrix_views(fname, scheme):
         torch.cuda.synchronize()
         assert_bits_equal(to_numpy(dq, code_dtype(scheme)), want_codes, "codes")
         assert_bits_equal(to_numpy(ds, np.float32), want_scale, "scales")
+        assert_bits_equal(to_numpy(dscale, F), O.compute_scales(x, scheme), "compute_scales")
         assert_bits_equal(to_numpy(dq2, code_dtype(scheme)), want_codes, "codes (two calls)")
         assert_bits_equal(to_numpy(ds2, np.float32), want_scale, "scales (two calls)")
         assert_bits_equal(to_numpy(out_view.contiguous(), F), O.dequantize(want_codes, want_scale, scheme, F), "restored")
