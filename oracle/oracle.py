@@ -107,11 +107,19 @@ def code_dtype(scheme: QuantScheme) -> np.dtype:
     return np.dtype(np.int8) if scheme.value in (QuantValue.Q8F, QuantValue.Q8S) else np.dtype(np.uint8)
 
 
-def compute_scales(x: np.ndarray, scheme: QuantScheme) -> np.ndarray:
+def _buffer(out, shape, dtype) -> np.ndarray:
+    """A caller-provided output buffer (checked) or a fresh zeroed one."""
+    if out is None:
+        return np.zeros(shape, dtype=dtype)
+    assert out.shape == tuple(shape) and out.dtype == np.dtype(dtype) and out.flags.c_contiguous, "bad output buffer"
+    return out
+
+
+def compute_scales(x: np.ndarray, scheme: QuantScheme, out: np.ndarray | None = None) -> np.ndarray:
     """absmax per tensor / block and ``scale = 2*absmax/(hi-lo)``, typed like ``x``."""
     x = np.ascontiguousarray(x)
     fdt = elem_type(x.dtype)
-    out = np.zeros(scheme.scales_shape(x.shape), dtype=x.dtype)
+    out = _buffer(out, tuple(scheme.scales_shape(x.shape)), x.dtype)
     blk, brank, level = _block(scheme)
     strides = _elem_strides(out) if level else [0] * x.ndim
     _check(lib().oq_compute_scales(x.ctypes.data, int(fdt), _i64(x.shape), x.ndim, int(scheme.value), level,
@@ -119,7 +127,8 @@ def compute_scales(x: np.ndarray, scheme: QuantScheme) -> np.ndarray:
     return out
 
 
-def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme) -> Tuple[np.ndarray, np.ndarray]:
+def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme, out: np.ndarray | None = None,
+             out_scale: np.ndarray | None = None) -> Tuple[np.ndarray, np.ndarray]:
     """``quantize::launch_ref``: returns (quantized tensor, out_scale typed as the param)."""
     x = np.ascontiguousarray(x)
     fdt = elem_type(x.dtype)
@@ -128,8 +137,8 @@ def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme) -> Tuple[np.
     nq = scheme.num_quants()
     if x.shape[-1] % nq:
         raise OracleError(3)
-    out = np.zeros(scheme.packed_shape(x.shape), dtype=code_dtype(scheme))
-    out_scale = np.zeros(scale.shape, dtype=np_dtype(int(scheme.param)))
+    out = _buffer(out, tuple(scheme.packed_shape(x.shape)), code_dtype(scheme))
+    out_scale = _buffer(out_scale, tuple(scale.shape), np_dtype(int(scheme.param)))
     strides = _elem_strides(scale) if level else [0] * x.ndim
     _check(lib().oq_quantize(x.ctypes.data, int(fdt), _i64(x.shape), x.ndim, scale.ctypes.data, _i64(strides),
                              int(scheme.value), int(scheme.store), int(scheme.param), level, blk, brank,
@@ -137,13 +146,14 @@ def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme) -> Tuple[np.
     return out, out_scale
 
 
-def dequantize(values: np.ndarray, params: np.ndarray, scheme: QuantScheme, out_dtype) -> np.ndarray:
+def dequantize(values: np.ndarray, params: np.ndarray, scheme: QuantScheme, out_dtype,
+               out: np.ndarray | None = None) -> np.ndarray:
     """``dequantize::launch_ref``: returns the float tensor of the unpacked shape."""
     values = np.ascontiguousarray(values)
     odt = elem_type(out_dtype)
     nq = scheme.num_quants()
     shape = tuple(values.shape[:-1]) + (values.shape[-1] * nq,)
-    out = np.zeros(shape, dtype=np_dtype(odt))
+    out = _buffer(out, shape, np_dtype(odt))
     blk, brank, level = _block(scheme)
     strides = _elem_strides(params) if level else [0] * len(shape)
     _check(lib().oq_dequantize(values.ctypes.data, _i64(shape), len(shape), params.ctypes.data, _i64(strides),
