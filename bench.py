@@ -192,6 +192,7 @@ def cpu_step(workload, x):
 def cpu_baseline(workload):
     from oracle import oracle as O
 
+    O.set_threads(len(os.sched_getaffinity(0)))
     rows = cpu_sample_rows(workload)
     secs = time_cpu(workload, rows)
     q, d = algorithmic_bytes(workload, rows)
@@ -206,6 +207,9 @@ def run_reference(args, workload):
         return
     from oracle import oracle as O
 
+    # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm is the only CPU work of the job and takes
+    # every core the process may run on.
+    O.set_threads(len(os.sched_getaffinity(0)))
     rows = cpu_sample_rows(workload, seconds_target=max(2.0, 60.0 / max(args.steps + args.warmup, 1)))
     x = cpu_input(workload, rows)
     q, d = algorithmic_bytes(workload, rows)
