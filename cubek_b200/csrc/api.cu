@@ -809,13 +809,17 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
                                                   (int)g.block_rows, (int)g.B, range, 1.0f / range, cfg, stream));
     }
     long long ld = 0;
-    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(input, &ld) && g.last_dim_blocks && is_contiguous(scale) &&
-        (g.B * fsize == 64 || g.B * fsize == 32) && g.n / g.B < (1ll << 31)) {
-        Transposed tr;
-        const long long ntiles = fill_transposed_tiles(tr, input, ld, fsize, g.B);
-        count_launch();
-        return cuda_status(launch_scales_transposed(input_dtype, (int)(g.B * fsize), input->ptr, scale->ptr, tr, ntiles, range,
-                                                    1.0f / range, cfg, stream));
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(input, &ld) && g.last_dim_blocks && is_contiguous(scale)) {
+        for (int ub = 64; ub >= 32; ub >>= 1) {
+            const long long U = ub / fsize;
+            const int lgb = (g.B % U == 0) ? log2_exact(g.B / U) : -1;
+            if (lgb < 0 || lgb > 3 || g.n / U >= (1ll << 31)) continue;
+            Transposed tr;
+            const long long ntiles = fill_transposed_tiles(tr, input, ld, fsize, U);
+            count_launch();
+            return cuda_status(launch_scales_transposed(input_dtype, ub, lgb, input->ptr, scale->ptr, tr, ntiles, range,
+                                                        1.0f / range, cfg, stream));
+        }
     }
     GeneralScalesArgs a;
     fill_layout(a.layout, g, scale, nullptr, input);
@@ -1117,7 +1121,13 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         for (int ub = 64; ub >= 32; ub >>= 1) {
             if (ub < min_unit_bytes(input_dtype, g.kind)) break;
             const long long U = ub / fsize;
-            if (g.shape[1] % U != 0 || (!g.per_tensor && g.B != U)) continue;
+            // a block is 1, 2, 4 or 8 units: the warps of one tile row of the kernel
+            int lgb = -1;
+            if (!g.per_tensor) {
+                lgb = (g.B % U == 0) ? log2_exact(g.B / U) : -1;
+                if (lgb < 0 || lgb > 3) continue;
+            }
+            if (g.shape[1] % U != 0) continue;
             const int out_words = (int)(U / kind_elems_per_u32(g.kind));
             if (!aligned(output->ptr, out_words >= 4 ? 16 : 4 * out_words)) continue;
             if (g.n / U >= (1ll << 31) || g.shape[0] >= (1ll << 31)) continue;
@@ -1125,7 +1135,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             one.a.ntensors = 1;
             one.a.nunits = g.n / U;
             one.a.absmax = absmax;
-            one.a.lg_units_per_block = g.per_tensor ? -1 : 0;
+            one.a.lg_units_per_block = lgb;
             one.a.param = scheme->param;
             one.a.lo = lo;
             one.a.hi = hi;
@@ -1258,14 +1268,19 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
         for (int ob = 64; ob >= 32; ob >>= 1) {
             if (ob < min_dequant_bytes(output_dtype, g.kind)) break;
             const long long E = ob / fsize;
-            if (g.shape[1] % E != 0 || (!g.per_tensor && g.B != E)) continue;
+            int lgb = -1;
+            if (!g.per_tensor) {
+                lgb = (g.B % E == 0) ? log2_exact(g.B / E) : -1;
+                if (lgb < 0 || lgb > 3) continue;
+            }
+            if (g.shape[1] % E != 0) continue;
             const int in_words = (int)(E / kind_elems_per_u32(g.kind));
             if (!aligned(values->ptr, 4 * (in_words >= 4 ? 4 : in_words))) continue;
             if (g.n / E >= (1ll << 31) || g.shape[0] >= (1ll << 31)) continue;
             DequantBatch one;
             one.a.ntensors = 1;
             one.a.nunits = g.n / E;
-            one.a.lg_units_per_block = g.per_tensor ? -1 : 0;
+            one.a.lg_units_per_block = lgb;
             one.a.param = scheme->param;
             one.a.aligned32 = 0;
             const bool pairs = fsize == 2 && g.shape[0] % 2 == 0 && ld % 2 == 0 && aligned(output->ptr, 4);

@@ -974,10 +974,11 @@ __global__ void __launch_bounds__(256) block_scales_2d_kernel(const void *in_, v
 // Host-side launchers, one translation unit per float type.
 cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream);
-// Transposed matrix views (transposed_kernels.cu): one tensor, unit = block (lg 0) or per tensor (lg -1).
+// Transposed matrix views (transposed_kernels.cu): one tensor; blocks of 1, 2, 4 or 8 units (lg 0..3) or per tensor (lg -1).
 cudaError_t launch_quantize_transposed(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
                                        const LaunchCfg &cfg, cudaStream_t stream);
-cudaError_t launch_scales_transposed(int fdt, int unit_bytes, const void *in, void *scale_out, const Transposed &tr,
+// `lgb`: a block is 2^lgb units (0..3).
+cudaError_t launch_scales_transposed(int fdt, int unit_bytes, int lgb, const void *in, void *scale_out, const Transposed &tr,
                                      long long ntiles, float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream);
 // Device flag the staged kernels set when a bounded wait gives up (address of the current device).
 int *stage_error_flag();

@@ -93,9 +93,11 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
     using F = typename ElemOf<FDT>::type;
     __shared__ uint32_t codes_s[RT][ROW_WORDS + 1];   // +1: lanes write one column of this array
     __shared__ float scales_s[RT][CT + 1];
+    __shared__ float amax_s[RT][CT + 1];
     const QuantTensor &T = a.t[0];
     const char *in = static_cast<const char *>(T.in);
-    const int lg = a.lg_units_per_block;      // 0 (a unit is a block) or -1 (per tensor)
+    const int lg = a.lg_units_per_block;      // -1 per tensor; else a block is 2^lg units (1, 2, 4 or 8 warps of the tile)
+    const int lgb = lg < 0 ? 0 : lg;
     const unsigned R = a.tr.nrows, upr = a.tr.units_per_row;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_entry();
@@ -110,15 +112,25 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
         const bool active = cu < upr && r0 < R;
         uint32_t raw[NR][RAW];
         gather_units<FDT, UB, PAIR>(in, a.tr.ld, cu, r0, active, raw);
+        if constexpr (DYN) {
+            // absmax of a block: the unit's own, then (blocks of several units) the other warps' through shared memory
+#pragma unroll
+            for (int k = 0; k < NR; ++k) amax_s[lane * NR + k][warp] = unit_absmax<FDT, RAW>(raw[k]);
+            if (lgb > 0) __syncthreads();
+        }
 #pragma unroll
         for (int k = 0; k < NR; ++k) {
             float scale_f;
             if constexpr (DYN) {
-                scale_f = fused_unit_scale<FDT, RAW>(raw[k], 0, a.range, a.inv_range);
+                float amax = amax_s[lane * NR + k][warp];
+                const int first = warp & ~((1 << lgb) - 1);
+                for (int j = 0; j < (1 << lgb); ++j) amax = fmaxf(amax, amax_s[lane * NR + k][first + j]);
+                scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
             } else if (lg < 0) {
                 scale_f = tensor_scale;
             } else {
-                scale_f = active ? static_cast<float>(static_cast<const F *>(T.scale_in)[(long long)(r0 + k) * upr + cu]) : 1.0f;
+                scale_f = active ? static_cast<float>(static_cast<const F *>(T.scale_in)[(long long)(r0 + k) * (upr >> lgb) + (cu >> lgb)])
+                                 : 1.0f;
             }
             // write_scale (crates/cubek-quant/src/quantize.rs:83-98): cast to the param type, divide by that value
             const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
@@ -128,7 +140,7 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
             else quantize_unit_exact<FDT, KIND, UB>(raw[k], sc, a.lo, a.hi, w);
 #pragma unroll
             for (int j = 0; j < OW; ++j) codes_s[lane * NR + k][warp * OW + j] = w[j];
-            scales_s[lane * NR + k][warp] = s_fs;
+            if ((warp & ((1 << lgb) - 1)) == 0) scales_s[lane * NR + k][warp >> lgb] = s_fs;
             if (lg < 0 && tile == 0 && threadIdx.x == 0 && k == 0) store_dyn(T.out_scale, a.param, 0, s_fs);
         }
         __syncthreads();
@@ -140,10 +152,12 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
             if (grow < R && gcu < upr) out[((long long)grow * upr + ct * CT) * OW + col] = codes_s[row][col];
         }
         if (lg >= 0) {
-            for (int j = threadIdx.x; j < RT * CT; j += 256) {
-                const int row = j / CT, c = j % CT;
-                const unsigned grow = rt * RT + row, gcu = ct * CT + c;
-                if (grow < R && gcu < upr) store_dyn(T.out_scale, a.param, (long long)grow * upr + gcu, scales_s[row][c]);
+            const int per_row = CT >> lgb;      // blocks of one tile row
+            for (int j = threadIdx.x; j < RT * per_row; j += 256) {
+                const int row = j / per_row, c = j % per_row;
+                const unsigned grow = rt * RT + row, gcu = ct * CT + (c << lgb);
+                if (grow < R && gcu < upr)
+                    store_dyn(T.out_scale, a.param, (long long)grow * (upr >> lgb) + (gcu >> lgb), scales_s[row][c]);
             }
         }
         __syncthreads();   // the tile buffers are reused
@@ -154,7 +168,7 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
 // F-typed scales leave as runs of 8 per logical row.
 template <int FDT, int UB, bool PAIR>
 __global__ void __launch_bounds__(256) scales_transposed_kernel(const void *in_, void *scale_out, const Transposed tr,
-                                                                long long ntiles, float range, float inv_range)
+                                                                long long ntiles, float range, float inv_range, int lgb)
 {
     constexpr int RAW = UB / 4;
     constexpr int NR = PAIR ? 2 : 1;
@@ -174,12 +188,18 @@ __global__ void __launch_bounds__(256) scales_transposed_kernel(const void *in_,
         uint32_t raw[NR][RAW];
         gather_units<FDT, UB, PAIR>(in, tr.ld, cu, r0, cu < upr && r0 < R, raw);
 #pragma unroll
-        for (int k = 0; k < NR; ++k) scales_s[lane * NR + k][warp] = fused_unit_scale<FDT, RAW>(raw[k], 0, range, inv_range);
+        for (int k = 0; k < NR; ++k) scales_s[lane * NR + k][warp] = unit_absmax<FDT, RAW>(raw[k]);   // absmax per unit
         __syncthreads();
-        for (int j = threadIdx.x; j < RT * CT; j += 256) {
-            const int row = j / CT, c = j % CT;
-            const unsigned grow = rt * RT + row, gcu = ct * CT + c;
-            if (grow < R && gcu < upr) static_cast<F *>(scale_out)[(long long)grow * upr + gcu] = static_cast<F>(scales_s[row][c]);
+        const int per_row = CT >> lgb;      // blocks of 2^lgb units
+        for (int j = threadIdx.x; j < RT * per_row; j += 256) {
+            const int row = j / per_row, c = j % per_row;
+            const unsigned grow = rt * RT + row, gcu = ct * CT + (c << lgb);
+            if (grow < R && gcu < upr) {
+                float amax = 0.0f;
+                for (int u = 0; u < (1 << lgb); ++u) amax = fmaxf(amax, scales_s[row][(c << lgb) + u]);
+                static_cast<F *>(scale_out)[(long long)grow * (upr >> lgb) + (gcu >> lgb)] =
+                    static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
+            }
         }
         __syncthreads();
     }
@@ -203,7 +223,7 @@ __global__ void __launch_bounds__(256) dequantize_transposed_kernel(const Dequan
         uint32_t words[IW];
 #pragma unroll
         for (int j = 0; j < IW; ++j) words[j] = __ldg(vals + j);
-        const long long si = (lg < 0) ? 0 : ix.li;
+        const long long si = (lg < 0) ? 0 : (long long)ix.r * (a.tr.units_per_row >> lg) + (ix.cu >> lg);
         const float s = round_to<FDT>(load_dyn(T.params, a.param, si));
         uint32_t s2 = 0;
         if constexpr (FDT != QK_F32) s2 = h2_pack<FDT>(s, s);
@@ -246,7 +266,8 @@ __global__ void __launch_bounds__(256) dequantize_transposed_pair_kernel(const D
         for (int k = 0; k < 2; ++k) {
             const long long li = (long long)(r + k) * a.tr.units_per_row + cu;
             const uint32_t *vals = static_cast<const uint32_t *>(T.values) + li * IW;
-            const float s = round_to<FDT>(load_dyn(T.params, a.param, (lg < 0) ? 0 : li));
+            const long long si = (lg < 0) ? 0 : (long long)(r + k) * (a.tr.units_per_row >> lg) + (cu >> lg);
+            const float s = round_to<FDT>(load_dyn(T.params, a.param, si));
             const uint32_t s2 = h2_pack<FDT>(s, s);
 #pragma unroll
             for (int j = 0; j < IW; ++j) dequant_word<FDT, KIND>(__ldg(vals + j), s, s2, o[k] + j * OREG_PER_WORD);
@@ -382,7 +403,7 @@ static cudaError_t dequantize_kind(int kind, int out_bytes, const DequantArgs &a
 
 template <int FDT, int UB>
 static cudaError_t scales_pairing(const void *in, void *scale_out, const Transposed &tr, long long ntiles, float range,
-                                  float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
+                                  float inv_range, int lgb, const LaunchCfg &cfg, cudaStream_t stream)
 {
     long long need = ntiles;
     if constexpr (FDT != QK_F32) {
@@ -390,29 +411,29 @@ static cudaError_t scales_pairing(const void *in, void *scale_out, const Transpo
             const long long cap = (long long)cfg.sm_count * resident(scales_transposed_kernel<FDT, UB, true>) * 4;
             if (need > cap) need = cap;
             return launch_kernel(scales_transposed_kernel<FDT, UB, true>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, tr,
-                                 ntiles, range, inv_range);
+                                 ntiles, range, inv_range, lgb);
         }
     }
     const long long cap = (long long)cfg.sm_count * resident(scales_transposed_kernel<FDT, UB, false>) * 4;
     if (need > cap) need = cap;
     return launch_kernel(scales_transposed_kernel<FDT, UB, false>, (int)need, 256, stream, cfg.pdl != 0, in, scale_out, tr,
-                         ntiles, range, inv_range);
+                         ntiles, range, inv_range, lgb);
 }
 
-cudaError_t launch_scales_transposed(int fdt, int unit_bytes, const void *in, void *scale_out, const Transposed &tr,
+cudaError_t launch_scales_transposed(int fdt, int unit_bytes, int lgb, const void *in, void *scale_out, const Transposed &tr,
                                      long long ntiles, float range, float inv_range, const LaunchCfg &cfg, cudaStream_t stream)
 {
-    if (ntiles < 1 || (unit_bytes != 64 && unit_bytes != 32)) return cudaErrorInvalidValue;
+    if (ntiles < 1 || (unit_bytes != 64 && unit_bytes != 32) || lgb < 0 || lgb > 3) return cudaErrorInvalidValue;
     switch (fdt) {
     case QK_F32:
-        return unit_bytes == 64 ? scales_pairing<QK_F32, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
-                                : scales_pairing<QK_F32, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
+        return unit_bytes == 64 ? scales_pairing<QK_F32, 64>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream)
+                                : scales_pairing<QK_F32, 32>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream);
     case QK_F16:
-        return unit_bytes == 64 ? scales_pairing<QK_F16, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
-                                : scales_pairing<QK_F16, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
+        return unit_bytes == 64 ? scales_pairing<QK_F16, 64>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream)
+                                : scales_pairing<QK_F16, 32>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream);
     case QK_BF16:
-        return unit_bytes == 64 ? scales_pairing<QK_BF16, 64>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream)
-                                : scales_pairing<QK_BF16, 32>(in, scale_out, tr, ntiles, range, inv_range, cfg, stream);
+        return unit_bytes == 64 ? scales_pairing<QK_BF16, 64>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream)
+                                : scales_pairing<QK_BF16, 32>(in, scale_out, tr, ntiles, range, inv_range, lgb, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -419,7 +419,11 @@ def test_column_slices_of_wider_tensors(fname, scheme):
     ("f32", QuantScheme(value=QuantValue.Q8S)),
     ("bf16", QuantScheme(value=QuantValue.Q8S)),
     ("f16", QuantScheme(value=QuantValue.E4M3, store=QuantStore.Native)),
-    ("bf16", QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([64]))),     # blocks of two units: general kernels
+    ("bf16", QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([64]))),     # blocks of two units
+    ("bf16", QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([128]))),    # four units
+    ("f32", QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([128]))),     # eight units
+    ("f16", QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native, level=QuantLevel.block([64]), param=QuantParam.F16)),
+    ("f32", QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([24]))),      # not a power of two: general kernels
 ])
 def test_transposed_matrix_views(fname, scheme):
     """`w.t()` of a row-major matrix (also of a column slice of it, ld > rows): blocks and packed words run
@@ -427,13 +431,14 @@ def test_transposed_matrix_views(fname, scheme):
     the dequantize writes nothing outside the view."""
     import torch
     from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
-    from tests._util import code_dtype, elem_of, empty_device, to_device, to_numpy
+    from tests._util import NP_FLOAT, code_dtype, elem_of, empty_device, to_device, to_numpy
 
     F = FLOATS[fname]
     elem = elem_of(F)
     H = TensorHandleRef.from_torch
     client = ComputeClient.current()
-    for (rows, cols), pad in (((300, 1024), 0), ((1000, 128), 24), ((33, 64), 7)):
+    pdt = NP_FLOAT[ElemType(int(scheme.param))]
+    for (rows, cols), pad in (((300, 1536), 0), ((1000, 384), 24), ((33, 384), 7)):
         x = random_tensor((rows, cols), F, 2468)
         store = to_device(random_tensor((cols, rows + pad), F, 1))       # memory: [cols, ld]
         view = store[:, :rows].t()                                      # logical [rows, cols], strides (1, ld)
@@ -441,13 +446,13 @@ def test_transposed_matrix_views(fname, scheme):
         assert tuple(view.shape) == (rows, cols) and view.stride(0) == 1
         want_codes, want_scale = O.quantize_dynamic(x, scheme)
         dq = empty_device(scheme.packed_shape((rows, cols)), code_dtype(scheme))
-        ds = empty_device(scheme.scales_shape((rows, cols)), np.float32)
+        ds = empty_device(scheme.scales_shape((rows, cols)), pdt)
         ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
         quantize.launch_dynamic(client, H(view), H(dq), H(ds), scheme, elem, H(ws))
         dscale = empty_device(scheme.scales_shape((rows, cols)), F)
         quantize.compute_scales(client, H(view), H(dscale), scheme, elem, H(ws))
         dq2 = empty_device(scheme.packed_shape((rows, cols)), code_dtype(scheme))
-        ds2 = empty_device(scheme.scales_shape((rows, cols)), np.float32)
+        ds2 = empty_device(scheme.scales_shape((rows, cols)), pdt)
         quantize.launch_ref(client, H(view), H(dq2), H(dscale), H(ds2), scheme, elem)
         out_store = to_device(random_tensor((cols, rows + pad), F, 2))
         before = out_store.clone()
@@ -455,10 +460,10 @@ def test_transposed_matrix_views(fname, scheme):
         dequantize.launch_ref(client, H(dq), H(out_view), H(ds), scheme, elem)
         torch.cuda.synchronize()
         assert_bits_equal(to_numpy(dq, code_dtype(scheme)), want_codes, "codes")
-        assert_bits_equal(to_numpy(ds, np.float32), want_scale, "scales")
+        assert_bits_equal(to_numpy(ds, pdt), want_scale, "scales")
         assert_bits_equal(to_numpy(dscale, F), O.compute_scales(x, scheme), "compute_scales")
         assert_bits_equal(to_numpy(dq2, code_dtype(scheme)), want_codes, "codes (two calls)")
-        assert_bits_equal(to_numpy(ds2, np.float32), want_scale, "scales (two calls)")
+        assert_bits_equal(to_numpy(ds2, pdt), want_scale, "scales (two calls)")
         assert_bits_equal(to_numpy(out_view.contiguous(), F), O.dequantize(want_codes, want_scale, scheme, F), "restored")
         out_store[:, :rows] = before[:, :rows]
         assert torch.equal(out_store.view(torch.uint8), before.view(torch.uint8)), "bytes outside the view changed"
