@@ -112,20 +112,26 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
         const bool active = cu < upr && r0 < R;
         uint32_t raw[NR][RAW];
         gather_units<FDT, UB, PAIR>(in, a.tr.ld, cu, r0, active, raw);
+        float amax[NR];
         if constexpr (DYN) {
-            // absmax of a block: the unit's own, then (blocks of several units) the other warps' through shared memory
+            // absmax of a block: the unit's own; blocks of several units add the other warps' through shared memory
 #pragma unroll
-            for (int k = 0; k < NR; ++k) amax_s[lane * NR + k][warp] = unit_absmax<FDT, RAW>(raw[k]);
-            if (lgb > 0) __syncthreads();
+            for (int k = 0; k < NR; ++k) amax[k] = unit_absmax<FDT, RAW>(raw[k]);
+            if (lgb > 0) {
+#pragma unroll
+                for (int k = 0; k < NR; ++k) amax_s[lane * NR + k][warp] = amax[k];
+                __syncthreads();
+                const int first = warp & ~((1 << lgb) - 1);
+#pragma unroll
+                for (int k = 0; k < NR; ++k)
+                    for (int j = 0; j < (1 << lgb); ++j) amax[k] = fmaxf(amax[k], amax_s[lane * NR + k][first + j]);
+            }
         }
 #pragma unroll
         for (int k = 0; k < NR; ++k) {
             float scale_f;
             if constexpr (DYN) {
-                float amax = amax_s[lane * NR + k][warp];
-                const int first = warp & ~((1 << lgb) - 1);
-                for (int j = 0; j < (1 << lgb); ++j) amax = fmaxf(amax, amax_s[lane * NR + k][first + j]);
-                scale_f = round_to<FDT>(div_by_range(2.0f * amax, a.range, a.inv_range));
+                scale_f = round_to<FDT>(div_by_range(2.0f * amax[k], a.range, a.inv_range));
             } else if (lg < 0) {
                 scale_f = tensor_scale;
             } else {
