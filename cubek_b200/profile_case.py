@@ -1,7 +1,10 @@
 """Runs a few fused-quantize + dequantize launches of one benchmark workload, optionally on a
 reduced number of rows, so that a profiler can capture single launches on a small case.
 
-    python -m cubek_b200.profile_case WORKLOAD [ROWS [ITERATIONS]]
+    python -m cubek_b200.profile_case WORKLOAD [ROWS [ITERATIONS [LAYOUT]]]
+
+LAYOUT is ``contiguous`` (default), ``transposed`` (the float tensors are `.t()` views of [cols, rows] matrices)
+or ``slice`` (column slices of matrices 256 columns wider).
 
 e.g.  ncu --set full --clock-control none -k regex:^quantize_kernel -s 1 -c 1 -o report \
           python -m cubek_b200.profile_case q4_block32_bf16_14336x4096 32768 3
@@ -20,12 +23,25 @@ def main(argv) -> None:
     w = WORKLOADS[argv[1]]
     rows = int(argv[2]) if len(argv) > 2 else w.shape[0]
     iters = int(argv[3]) if len(argv) > 3 else 3
+    layout = argv[4] if len(argv) > 4 else "contiguous"
     s, cols = w.scheme, w.shape[1]
     x = generate(w, "cuda", rows=rows)
+
+    def like(t):
+        if layout == "transposed":
+            return torch.empty((cols, rows), dtype=t.dtype, device="cuda").t()
+        if layout == "slice":
+            return torch.empty((rows, cols + 256), dtype=t.dtype, device="cuda")[:, 128:128 + cols]
+        return torch.empty_like(t)
+
+    if layout != "contiguous":
+        view = like(x)
+        view.copy_(x)
+        x = view
     code_dtype = torch.int32 if s.store.name == "U32" else torch.uint8
     codes = torch.empty(s.packed_shape((rows, cols)), dtype=code_dtype, device="cuda")
     scales = torch.empty(s.scales_shape((rows, cols)), dtype=torch.float32, device="cuda")
-    out = torch.empty_like(x)
+    out = like(x)
     ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     H, client = TensorHandleRef.from_torch, ComputeClient.current()
     for _ in range(iters):
