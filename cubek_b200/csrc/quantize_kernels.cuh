@@ -107,13 +107,6 @@ template <int FDT> __device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32
     else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
-// a * b + c, fused, per half (bf16 only: used by the packed division below).
-__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c)
-{
-    uint32_t r;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
 template <int FDT> __device__ __forceinline__ uint32_t h2_min(uint32_t a, uint32_t b)
 {
     uint32_t r;
@@ -273,52 +266,13 @@ __device__ void quantize_unit_exact(const uint32_t *raw, float s, float lo, floa
     pack_from_f32<KIND, UT::U>(c, outw);
 }
 
-// Elements e0 and e1 of a unit of 16-bit values as one packed register (e0 in the low half).
-__device__ __forceinline__ uint32_t raw_pair(const uint32_t *raw, int e0, int e1)
-{
-    if (e1 == e0 + 1 && (e0 & 1) == 0) return raw[e0 >> 1];
-    const uint32_t sel = ((e0 & 1) ? 0x0032u : 0x0010u) | ((e1 & 1) ? 0x7600u : 0x5400u);
-    return __byte_perm(raw[e0 >> 1], raw[e1 >> 1], sel);
-}
-
-// Quotients of two bf16 elements by the bf16 scale s, correctly rounded to bf16, in packed bf16 arithmetic:
-//   y = RN_bf16(RN_f32(1/s)), q0 = x*y, e = fma(-s, q0, x), q = fma(e, y, q0)
-// (three operations on the FMA pipe per pair instead of two widenings, two multiplies and a narrowing).
-// Checked on the host against RN_bf16(x/s) for every bf16 s in [2^-100, 2^100] and every bf16 x with
-// x/s in [1/8, 2^18]: identical.  With a caller-supplied scale the first guess is clamped so that a huge
-// quotient ends as a huge value or infinity of the right sign, never NaN.
-struct Bf16Divider {
-    uint32_t y2, neg_s2, q_lo2, q_hi2;
-};
-__device__ __forceinline__ Bf16Divider make_bf16_divider(float s, float r, float lo, float hi)
-{
-    Bf16Divider d;
-    d.y2 = pack_bf16x2(r, r);
-    d.neg_s2 = pack_bf16x2(-s, -s);
-    d.q_lo2 = pack_bf16x2(lo - 2.0f, lo - 2.0f);
-    d.q_hi2 = pack_bf16x2(hi + 2.0f, hi + 2.0f);
-    return d;
-}
-// SIGNED_ZERO: the codes distinguish -0 from +0 (fp4, fp8).  The correction step turns a quotient of -0 into
-// +0 (e = +0, then +0 + -0), so the sign of x (the scale is positive here) is put back.
-template <bool BOUNDED, bool SIGNED_ZERO> __device__ __forceinline__ uint32_t bf16_quotients(uint32_t x2, const Bf16Divider &d)
-{
-    uint32_t q0 = h2_mul<QK_BF16>(x2, d.y2);
-    if constexpr (!BOUNDED) q0 = h2_min<QK_BF16>(h2_max<QK_BF16>(q0, d.q_lo2), d.q_hi2);
-    const uint32_t e = bf2_fma(d.neg_s2, q0, x2);
-    const uint32_t q = bf2_fma(e, d.y2, q0);
-    if constexpr (SIGNED_ZERO) return (q & 0x7fff7fffu) | (x2 & 0x80008000u);
-    else return q;
-}
-
 // ---- fast route ---------------------------------------------------------------------------------
 // Valid for scale_is_safe(s) and finite inputs.  CLAMP = false is used by the fused form when
 // |x/s| cannot reach hi + 0.5 (see need_clamp()).
 //   f32 quotient: q0 = x*r, q = fma(fma(-s, q0, x), r, q0) with r = RN(1/s) is the correctly
 //     rounded quotient.  With a caller-supplied scale (BOUNDED = false) the first guess is
 //     clamped so that a huge quotient ends as +-inf or a huge value of the right sign (never NaN).
-//   bf16 quotient: packed bf16 arithmetic, see bf16_quotients().
-//   f16 quotient (and the bound used by the bf16 check): x and s carry 11 / 8 significant bits, so x/s is never closer than
+//   f16 / bf16 quotient: x and s carry 11 / 8 significant bits, so x/s is never closer than
 //     2^-23 / 2^-17 (relative) to a rounding boundary of F; the f32 product x*r rounds to the
 //     same F value as the exact quotient for every |x/s| in [1/8, 2^18] (checked exhaustively on
 //     the host for all pairs; the property depends on the two significands only); outside that
@@ -345,13 +299,9 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
         pack_from_f32<KIND, U>(c, outw);
     } else if constexpr (KIND == KIND_E4M3 || KIND == KIND_E5M2) {
         float c[U];
-        Bf16Divider div16;
-        if constexpr (FDT == QK_BF16) div16 = make_bf16_divider(s, r, lo, hi);
 #pragma unroll
         for (int i = 0; i < U; i += 2) {
-            uint32_t p;
-            if constexpr (FDT == QK_BF16) p = bf16_quotients<BOUNDED, true>(raw[i >> 1], div16);
-            else p = h2_pack<FDT>(raw_elem<FDT>(raw, i) * r, raw_elem<FDT>(raw, i + 1) * r);
+            const uint32_t p = h2_pack<FDT>(raw_elem<FDT>(raw, i) * r, raw_elem<FDT>(raw, i + 1) * r);
             c[i] = fminf(fmaxf(h_lo_to_f32<FDT>(p), lo), hi);
             c[i + 1] = fminf(fmaxf(h_hi_to_f32<FDT>(p), lo), hi);
         }
@@ -362,12 +312,6 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
         // only: element j and element j + EPW/2 of a word for the integer packs, neighbours
         // (2j, 2j+1) for fp4 bytes and for bf16 8-bit codes.
         const uint32_t lo2 = h2_const<FDT>(lo), hi2 = h2_const<FDT>(hi);
-        // bf16: packed division, except for 4-bit packs - there it needs a byte permute per pair to bring the
-        // elements together and the kernel is HBM bound anyway (measured: 6420 vs 6530 GB/s on bf16 q4 block 32,
-        // against 6560 vs 6320 on q8 and 6030 vs 5380 on fp8, where neighbours pair up).
-        constexpr bool PACKED_DIV = FDT == QK_BF16 && KIND != KIND_PACK4;
-        Bf16Divider div16;
-        if constexpr (PACKED_DIV) div16 = make_bf16_divider(s, r, lo, hi);
         constexpr bool SPLIT_PAIRS = (KIND == KIND_PACK4 || KIND == KIND_PACK2 ||
                                       ((KIND == KIND_PACK8 || KIND == KIND_I8) && FDT == QK_F16));
 #pragma unroll
@@ -377,9 +321,7 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
             for (int j = 0; j < EPW / 2; ++j) {
                 const int e0 = w * EPW + (SPLIT_PAIRS ? j : 2 * j);
                 const int e1 = w * EPW + (SPLIT_PAIRS ? j + EPW / 2 : 2 * j + 1);
-                uint32_t q;
-                if constexpr (PACKED_DIV) q = bf16_quotients<BOUNDED, KIND == KIND_E2M1>(raw_pair(raw, e0, e1), div16);
-                else q = h2_pack<FDT>(raw_elem<FDT>(raw, e0) * r, raw_elem<FDT>(raw, e1) * r);
+                uint32_t q = h2_pack<FDT>(raw_elem<FDT>(raw, e0) * r, raw_elem<FDT>(raw, e1) * r);
                 if constexpr (CLAMP) q = h2_min<FDT>(h2_max<FDT>(q, lo2), hi2);
                 p[j] = q;
             }
