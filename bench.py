@@ -224,7 +224,7 @@ def run_reference(args, workload):
     value = round((q + d) / secs / 1e9, 3)
     sample = (f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor per step "
               f"(one of the {args.batch} tensors of a step of the GPU arm)")
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.elem.name.lower(),
@@ -233,7 +233,7 @@ def run_reference(args, workload):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU port of the reference arithmetic (the oracle); the reference's own CubeCL CPU runtime "
                 "cannot be built here (no Rust toolchain, un-vendored JIT dependency)",
-    }))
+    })
 
 
 def config_of(workload, args):
@@ -406,7 +406,7 @@ def run_gpu(args, workload):
     }
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(workload)
-    print(json.dumps(out))
+    emit(out)
     if world > 1:
         dist.destroy_process_group()
 
@@ -494,7 +494,7 @@ def run_weight_set(args, per_tensor: bool, row_sharded: bool = False):
         ms = float(t.item()) / args.steps
         value = (q_bytes + d_bytes) / ms / 1e6
         peak, kind = measured_peak()
-        print(json.dumps({
+        emit({
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -504,7 +504,7 @@ def run_weight_set(args, per_tensor: bool, row_sharded: bool = False):
                                      if row_sharded else "whole tensors, largest first onto the least loaded rank"),
                        "api": "qk_quantize_dynamic_batch + qk_dequantize_batch", "distribution": "normal(0,0.02)"},
             "pct_of_measured_peak": round(100 * value / world / peak, 1), "peak_source": f"{kind} copy bandwidth",
-            "gpu_launches": int(launches)}))
+            "gpu_launches": int(launches)})
     if world > 1:
         dist.destroy_process_group()
 
@@ -568,7 +568,30 @@ def run_e2e(args, workload, dev, local_rank, rank, world, xs):
             "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies)"}
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Library chatter on stdout (NCCL prints its version there when NCCL_DEBUG asks for it) would sit next to
+    the result line: from here on file descriptor 1 goes to stderr, and the one JSON line is written to the
+    original stdout by emit()."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(result) -> None:
+    line = (json.dumps(result) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, line)
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
