@@ -3,8 +3,9 @@ reduced number of rows, so that a profiler can capture single launches on a smal
 
     python -m cubek_b200.profile_case WORKLOAD [ROWS [ITERATIONS [LAYOUT]]]
 
-LAYOUT is ``contiguous`` (default), ``transposed`` (the float tensors are `.t()` views of [cols, rows] matrices)
-or ``slice`` (column slices of matrices 256 columns wider).
+LAYOUT is ``contiguous`` (default), ``transposed`` (the float tensors are `.t()` views of [cols, rows] matrices),
+``slice`` (column slices of matrices 256 columns wider) or ``twocall`` (contiguous tensors through the reference-shaped
+flow: compute_scales, quantize with given scales, dequantize).
 
 e.g.  ncu --set full --clock-control none -k regex:^quantize_kernel -s 1 -c 1 -o report \
           python -m cubek_b200.profile_case q4_block32_bf16_14336x4096 32768 3
@@ -34,7 +35,7 @@ def main(argv) -> None:
             return torch.empty((rows, cols + 256), dtype=t.dtype, device="cuda")[:, 128:128 + cols]
         return torch.empty_like(t)
 
-    if layout != "contiguous":
+    if layout in ("transposed", "slice"):
         view = like(x)
         view.copy_(x)
         x = view
@@ -44,8 +45,13 @@ def main(argv) -> None:
     out = like(x)
     ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     H, client = TensorHandleRef.from_torch, ComputeClient.current()
+    given = torch.empty(s.scales_shape((rows, cols)), dtype=x.dtype, device="cuda")
     for _ in range(iters):
-        quantize.launch_dynamic(client, H(x), H(codes), H(scales), s, w.elem, H(ws))
+        if layout == "twocall":
+            quantize.compute_scales(client, H(x), H(given), s, w.elem, H(ws))
+            quantize.launch_ref(client, H(x), H(codes), H(given), H(scales), s, w.elem)
+        else:
+            quantize.launch_dynamic(client, H(x), H(codes), H(scales), s, w.elem, H(ws))
         dequantize.launch_ref(client, H(codes), H(out), H(scales), s, w.elem)
     torch.cuda.synchronize()
     print("ok", w.name, rows, float(out.float().abs().max()))
