@@ -1,22 +1,31 @@
 """Benchmark of the quantize + dequantize hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--batch B] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-One step = fused dynamic quantize followed by dequantize of a batch of B distinct synthetic
-tensors of the workload (B x inputs > L2, so every step streams from HBM).  Prints ONE JSON line.
-Under torchrun every rank processes its own batch (weak scaling, no data-path collective for
-per-block schemes); time is the max over ranks, measured with CUDA events.
+Default workload ``llama3_8b_q8``: the 225 bf16 matrices of a Llama-3-8B-shaped model (7.5 G elements, 15 GB).
+One step quantizes and dequantizes the whole set twice: with q8 codes and one scale per block of 128
+(``block128``: no communication) and with q8 codes and one scale per tensor (``tensor``: absmax of the local
+shards, ONE all-reduce(MAX) of 225 floats, quantize with the scales every rank derives from the reduced
+values).  Under torchrun every tensor is split into contiguous row ranges, one per rank (strong scaling: the
+set is fixed); the time of a run is the maximum over the ranks, measured with CUDA events.
 
-``--impl reference`` times the CPU oracle (a port of the reference's arithmetic; the reference
-itself needs a Rust toolchain and a JIT dependency that are not available) on the host cores.
+The line also carries, under ``configs``, a record for each of the single-tensor configurations (f32 q8 per
+tensor, bf16 q4 block 32, f16 fp4 block 16 / 32, f32 q2 block 64), timed the same way on tensors that are
+row-sharded over the ranks, as one batched launch per phase and as one call per tensor.
+
+``--workload NAME`` with a name from ``cubek_b200.synthetic.WORKLOADS`` makes that configuration the headline
+instead.  ``--case NAME --rows R --iters I [--layout L]`` runs a few launches of one configuration on R rows and
+exits: the small case a profiler captures.  ``--impl reference`` times the CPU oracle (a port of the
+reference's arithmetic; the reference itself needs a Rust toolchain and a JIT dependency that are not
+available) on the host cores.  Prints ONE JSON line on stdout.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -26,21 +35,24 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-DEFAULT_WORKLOAD = "q4_block32_bf16_14336x4096"
+DEFAULT_WORKLOAD = "llama3_8b_q8"
 METRIC = "quantize+dequantize HBM GB/s"
 SPEC_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
+L2_BYTES = 126 << 20
+SUB_CONFIGS = ("q8_tensor_f32_4096x4096", "q4_block32_bf16_14336x4096", "e2m1_block16_f16_8192x4096",
+               "e2m1_block32_f16_8192x4096", "q2_block64_f32_65536x4096")
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch and per tensor from one ncu capture of each kernel
-# on a reduced number of rows (still larger than L2), scaled by rows to the bench tensor; summaries of those
-# captures are kept under profiles/.  Reads equal the algorithmic reads; writes come out lower than the
-# algorithmic writes because part of the output is still dirty in L2 when the kernel ends.
-NCU_TRAFFIC_BYTES = {
-    "q4_block32_bf16_14336x4096": {"quantize_dynamic": 145.2e6, "dequantize": 130.4e6},
-    "e2m1_block16_f16_8192x4096": {"quantize_dynamic": 84.6e6, "dequantize": 78.3e6},
-    "q2_block64_f32_65536x4096": {"quantize_dynamic": 1145.0e6, "dequantize": 941.9e6},
-    "q8_block128_bf16_14336x4096": {"quantize_dynamic": 164.9e6, "dequantize": 154.5e6},
-    "q8_tensor_bf16_14336x4096": {"quantize_dynamic": 281.3e6},        # absmax pass + quantize pass
+# DRAM traffic of one launch, modelled from one ncu capture of each kernel on a reduced number of rows (still larger
+# than L2; summaries in the files named here): dram__bytes_read.sum was 1.000 x the algorithmic reads in every
+# capture, and dram__bytes_write.sum fell short of the algorithmic writes by what was still dirty in L2 when the
+# kernel ended - an amount bounded by the L2, not proportional to the launch.  traffic(launch) = algorithmic reads
+# + max(0, algorithmic writes - residue).
+NCU_WRITE_RESIDUE_BYTES = {
+    ("dequantize", "q8_block128_bf16"): (268.4e6 - 214.6e6, "profiles/dequantize_kernel_q8_block128_bf16.md"),
+    ("quantize_dynamic", "q8_block128_bf16"): (138.4e6 - 108.3e6, "profiles/quantize_kernel_q8_block128_bf16.md"),
+    ("dequantize", "q4_block32_bf16"): (154.1e6 - 130.4e6, "profiles/dequantize_kernel_q4_block32_bf16.md"),
+    ("quantize_dynamic", "q4_block32_bf16"): (154.1e6 - 145.2e6, "profiles/quantize_kernel_q4_block32_bf16.md"),
 }
 
 
@@ -54,19 +66,21 @@ def measured_peak():
     return FALLBACK_PEAK_GBS, "fallback"
 
 
-def algorithmic_bytes(workload, rows=None):
-    """Bytes one quantize and one dequantize must move for a tensor of this workload."""
-    r, c = workload.shape
-    if rows is not None:
-        r = rows
-    n = r * c
-    s = workload.scheme
-    nscales = 1 if s.level.is_tensor else n // s.level.block_size.as_slice()[-1]
-    code_bytes = n * s.value.size_bits() // 8
-    in_bytes = n * workload.elem.size
-    quant = in_bytes * (2 if s.level.is_tensor else 1) + code_bytes + nscales * s.param.size
-    dequant = code_bytes + nscales * s.param.size + in_bytes
+def tensor_bytes(n, esize, scheme):
+    """Algorithmic bytes (quantize, dequantize) of one tensor of ``n`` elements: the fused quantize reads the
+    input once per block scheme and twice per tensor scheme (absmax pass, quantize pass), writes codes and
+    scales; the dequantize reads codes and scales and writes the floats."""
+    per_tensor = scheme.level.is_tensor
+    nscales = 1 if per_tensor else n // math.prod(scheme.level.block_size.as_slice())
+    code_bytes = n * scheme.value.size_bits() // 8
+    quant = n * esize * (2 if per_tensor else 1) + code_bytes + nscales * scheme.param.size
+    dequant = code_bytes + nscales * scheme.param.size + n * esize
     return quant, dequant
+
+
+def algorithmic_bytes(workload, rows=None):
+    r, c = workload.shape
+    return tensor_bytes((rows if rows is not None else r) * c, workload.elem.size, workload.scheme)
 
 
 class ClockSampler:
@@ -124,51 +138,42 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-# ------------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the oracle on the host cores
-# ------------------------------------------------------------------------------------------------
-def cpu_sample_rows(workload, seconds_target=12.0):
-    """Rows of the workload tensor the oracle processes in about ``seconds_target`` seconds."""
+def torch_to_numpy(t):
+    """Host NumPy view of a torch tensor, bf16 included (as ml_dtypes.bfloat16)."""
+    import ml_dtypes
     import numpy as np
-    from oracle import oracle as O
-
-    probe_rows = min(256, workload.shape[0])
-    x = cpu_input(workload, probe_rows)
-    t0 = time.perf_counter()
-    codes, scale = O.quantize_dynamic(x, workload.scheme)
-    O.dequantize(codes, scale, workload.scheme, x.dtype)
-    dt = max(time.perf_counter() - t0, 1e-6)
-    rows = int(probe_rows * seconds_target / dt / 6)   # ~6 passes: warm-up + best of 5
-    rows = max(probe_rows, min(rows, workload.shape[0]))
-    return rows - rows % 8 if rows >= 8 else rows
-
-
-def cpu_input(workload, rows):
-    import numpy as np
-    from cubek_b200.synthetic import generate
-    from tests._util import NP_FLOAT, bfloat16
     import torch
 
-    t = generate(workload, "cpu", rows=rows)
+    t = t.detach().cpu().contiguous()
     if t.dtype == torch.bfloat16:
-        return t.view(torch.int16).numpy().view(bfloat16)
+        return t.view(torch.int16).numpy().view(ml_dtypes.bfloat16)
+    if t.dtype == torch.int32:
+        return t.numpy().view(np.uint32)
     return t.numpy()
 
 
-def time_cpu(workload, rows, repeats=5):
-    """Best-of-``repeats`` seconds of oracle quantize_dynamic + dequantize on ``rows`` rows."""
-    from oracle import oracle as O
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_workloads(name):
+    """The single-tensor configurations whose round trips make one CPU step of workload ``name``: for the
+    weight set, the largest layer matrix (gate / up projection, 14336 x 4096 bf16) under both of its schemes."""
+    from cubek_b200.synthetic import WORKLOADS
 
-    x = cpu_input(workload, rows)
-    step = cpu_step(workload, x)
-    best = float("inf")
-    for i in range(repeats + 1):
-        t0 = time.perf_counter()
-        step()
-        dt = time.perf_counter() - t0
-        if i > 0:
-            best = min(best, dt)
-    return best
+    if name.startswith("llama3_8b_q8"):
+        parts = []
+        if not name.endswith("_tensor"):
+            parts.append(WORKLOADS["q8_block128_bf16_14336x4096"])
+        if not name.endswith("_block128"):
+            parts.append(WORKLOADS["q8_tensor_bf16_14336x4096"])
+        return parts
+    return [WORKLOADS[name]]
+
+
+def cpu_input(workload, rows):
+    from cubek_b200.synthetic import generate
+
+    return torch_to_numpy(generate(workload, "cpu", rows=rows))
 
 
 def cpu_step(workload, x):
@@ -189,19 +194,46 @@ def cpu_step(workload, x):
     return step
 
 
-def cpu_baseline(workload):
+def cpu_plan(name, seconds_per_step):
+    """(steps, bytes): the oracle round trips of one CPU step, on as many rows of each tensor as fit the time."""
+    parts = cpu_workloads(name)
+    steps, total, sample = [], 0, []
+    for w in parts:
+        probe_rows = min(256, w.shape[0])
+        x = cpu_input(w, probe_rows)
+        probe = cpu_step(w, x)
+        probe()
+        t0 = time.perf_counter()
+        probe()
+        dt = max(time.perf_counter() - t0, 1e-6)
+        rows = int(probe_rows * seconds_per_step / len(parts) / dt)
+        rows = max(probe_rows, min(rows, w.shape[0]))
+        rows -= rows % 8
+        steps.append(cpu_step(w, cpu_input(w, rows)))
+        q, d = algorithmic_bytes(w, rows)
+        total += q + d
+        sample.append(f"{rows} of {w.shape[0]} rows of one {w.name} tensor")
+    return steps, total, " + ".join(sample)
+
+
+def cpu_baseline(name):
     from oracle import oracle as O
 
     O.set_threads(len(os.sched_getaffinity(0)))
-    rows = cpu_sample_rows(workload)
-    secs = time_cpu(workload, rows)
-    q, d = algorithmic_bytes(workload, rows)
-    return {"value": round((q + d) / secs / 1e9, 3), "unit": "GB/s", "cores": O.max_threads(), "kind": "port",
-            "sample": f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor, best of 5, "
-                      f"OpenMP over {O.max_threads()} threads"}
+    steps, total, sample = cpu_plan(name, seconds_per_step=2.5)
+    best = float("inf")
+    for i in range(6):
+        t0 = time.perf_counter()
+        for s in steps:
+            s()
+        dt = time.perf_counter() - t0
+        if i > 0:
+            best = min(best, dt)
+    return {"value": round(total / best / 1e9, 3), "unit": "GB/s", "cores": O.max_threads(), "kind": "port",
+            "sample": f"{sample}; best of 5; OpenMP over {O.max_threads()} threads"}
 
 
-def run_reference(args, workload):
+def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -210,362 +242,644 @@ def run_reference(args, workload):
     # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm is the only CPU work of the job and takes
     # every core the process may run on.
     O.set_threads(len(os.sched_getaffinity(0)))
-    rows = cpu_sample_rows(workload, seconds_target=max(2.0, 60.0 / max(args.steps + args.warmup, 1)))
-    x = cpu_input(workload, rows)
-    q, d = algorithmic_bytes(workload, rows)
-    step = cpu_step(workload, x)
+    steps, total, sample = cpu_plan(args.workload, seconds_per_step=max(0.5, 60.0 / max(args.steps + args.warmup, 1)))
     times = []
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
-        step()
+        for s in steps:
+            s()
         if i >= args.warmup:
             times.append(time.perf_counter() - t0)
     secs = sum(times) / len(times)
-    value = round((q + d) / secs / 1e9, 3)
-    sample = (f"{rows} of {workload.shape[0]} rows of one {workload.name} tensor per step "
-              f"(one of the {args.batch} tensors of a step of the GPU arm)")
+    value = round(total / secs / 1e9, 3)
     emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.elem.name.lower(),
-        "data": "synthetic", "config": config_of(workload, args),
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": O.max_threads(), "kind": "port", "sample": sample},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": reference_dtype(args.workload),
+        "data": "synthetic", "config": config_of(args.workload, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": O.max_threads(), "kind": "port",
+                         "sample": sample + " per step"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU port of the reference arithmetic (the oracle); the reference's own CubeCL CPU runtime "
                 "cannot be built here (no Rust toolchain, un-vendored JIT dependency)",
     })
 
 
-def config_of(workload, args):
-    s = workload.scheme
-    return {"workload": workload.name, "shape": list(workload.shape),
-            "batch_tensors_per_step": args.batch,
-            "value": s.value.name, "store": s.store.name, "param": s.param.name,
-            "level": "tensor" if s.level.is_tensor else f"block{list(s.level.block_size.as_slice())}",
-            "distribution": workload.distribution,
-            "api": "qk_quantize_dynamic_batch + qk_dequantize_batch (one launch per batch each)",
-            "l2": "batch of distinct tensors larger than L2; no flush needed"}
+def reference_dtype(name):
+    return cpu_workloads(name)[0].elem.name.lower()
+
+
+def config_of(name, world):
+    from cubek_b200.synthetic import WORKLOADS
+    from cubek_b200.weights import llama3_8b_shapes
+
+    if name.startswith("llama3_8b_q8"):
+        shapes = llama3_8b_shapes()
+        schemes = [k for k in ("block128", "tensor") if name in ("llama3_8b_q8", "llama3_8b_q8_" + k)]
+        return {"workload": name, "tensors": len(shapes), "elements": sum(r * c for _, r, c in shapes),
+                "value": "Q8S", "store": "U32", "param": "F32", "schemes_per_step": schemes,
+                "distribution": "normal(0,0.02)",
+                "placement": (f"every tensor split into contiguous row ranges over {world} ranks" if world > 1
+                              else "one GPU holds the whole set"),
+                "collective": ("tensor: one all-reduce(MAX) of 225 f32 per step (NCCL); block128: none" if world > 1
+                               else "none (one rank)") if "tensor" in schemes else "none",
+                "api": "qk_quantize_dynamic_batch, qk_absmax_batch + qk_quantize_from_absmax_batch, qk_dequantize_batch "
+                       "(up to 64 tensors per launch)",
+                "l2": "per-rank inputs of a step are far larger than L2; no flush needed"}
+    w = WORKLOADS[name]
+    s = w.scheme
+    return {"workload": w.name, "shape": list(w.shape), "value": s.value.name, "store": s.store.name,
+            "param": s.param.name, "level": "tensor" if s.level.is_tensor else f"block{list(s.level.block_size.as_slice())}",
+            "distribution": w.distribution,
+            "placement": f"rows split over {world} ranks" if world > 1 else "one GPU",
+            "api": "qk_quantize_dynamic_batch + qk_dequantize_batch (one launch per batch each)"}
 
 
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-def run_gpu(args, workload):
-    import torch
-    import torch.distributed as dist
+class Ctx:
+    """Process-wide state of the GPU arm: rank, device, library, stream helpers."""
 
-    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
-    from cubek_b200 import _ffi
-    from cubek_b200.synthetic import TORCH_DTYPE, generate
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        from cubek_b200 import ComputeClient, _ffi
 
-    lib = _ffi.lib()      # raises if the CUDA library is missing: there is no fallback
-    if args.no_pdl:
-        lib.qk_set_tuning(_ffi.TUNE_PDL, 0)
-    for kv in filter(None, args.tune.split(",")):
-        key, value = kv.split("=")
-        lib.qk_set_tuning(int(key), int(value))
-    scheme, elem = workload.scheme, workload.elem
-    r, c = workload.shape
-    B = args.batch
-    tdt = TORCH_DTYPE[elem]
-    code_torch = torch.int32 if scheme.store.name == "U32" else torch.uint8
-    pdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[int(scheme.param)]
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.lib = _ffi.lib()      # raises if the CUDA library is missing: there is no fallback
+        if args.no_pdl:
+            self.lib.qk_set_tuning(_ffi.TUNE_PDL, 0)
+        for kv in filter(None, args.tune.split(",")):
+            key, value = kv.split("=")
+            self.lib.qk_set_tuning(int(key), int(value))
+        self.client = ComputeClient.current()
+        self.flush_buf = None
 
-    xs = [generate(workload, dev, seed_offset=rank * 1000 + i) for i in range(B)]
-    codes = [torch.empty(scheme.packed_shape((r, c)), dtype=code_torch, device=dev) for _ in range(B)]
-    scales = [torch.empty(scheme.scales_shape((r, c)), dtype=pdt, device=dev) for _ in range(B)]
-    outs = [torch.empty((r, c), dtype=tdt, device=dev) for _ in range(B)]
-    ws = torch.zeros(4096, dtype=torch.uint8, device=dev)
-    H = TensorHandleRef.from_torch
-    hx, hc, hs, ho, hws = [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], [H(t) for t in outs], H(ws)
-    client = ComputeClient.current()
-    # Argument marshalling is done once.  A step is two calls into the C ABI: the fused quantize
-    # of the whole batch and the dequantize of the whole batch (one launch each for up to 64
-    # tensors).  The same work as one call per tensor is timed afterwards for comparison.
-    quant_batch = quantize.PreparedDynamicBatch(client, hx, hc, hs, scheme, elem, hws)
-    dequant_batch = dequantize.PreparedBatch(client, hc, ho, hs, scheme, elem)
-    quant_calls = [quantize.PreparedDynamic(client, hx[i], hc[i], hs[i], scheme, elem, hws) for i in range(B)]
-    dequant_calls = [dequantize.Prepared(client, hc[i], ho[i], hs[i], scheme, elem) for i in range(B)]
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
 
-    def step():
-        quant_batch()
-        dequant_batch()
+    def max_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return float(value)
+        t = self.torch.tensor([value], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    def step_single():
-        for i in range(B):
-            quant_calls[i]()
-            dequant_calls[i]()
+    def flush_l2(self):
+        """Evicts the step's tensors from L2 with a read-only pass over a 512 MB buffer (reads leave no dirty
+        lines behind that the next step would have to write back)."""
+        from cubek_b200 import ElemType, TensorHandleRef, quantize
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+        torch = self.torch
+        if self.flush_buf is None:
+            self.flush_buf = torch.ones(128 << 20, dtype=torch.float32, device=self.dev)
+            self.flush_cell = torch.zeros(1, dtype=torch.float32, device=self.dev)
+            self.flush_handle = TensorHandleRef.from_torch(self.flush_buf)
+        quantize.absmax(self.client, self.flush_handle, ElemType.F32, self.flush_cell.data_ptr())
 
-    def timed(fn, reps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        fn()
-        torch.cuda.synchronize()
-        a.record()
-        for _ in range(reps):
+    def time_steps(self, fn, steps, flush=False):
+        """Milliseconds per call of ``fn`` over ``steps`` calls (device time, this rank).  Without a flush the
+        calls run back to back between two events; with one, every call has its own event pair and the
+        flush runs between the pairs."""
+        torch = self.torch
+        if not flush:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / steps
+        pairs = []
+        for _ in range(steps):
+            self.flush_l2()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
             fn()
-        b.record()
+            b.record()
+            pairs.append((a, b))
         torch.cuda.synchronize()
-        return a.elapsed_time(b) / reps
+        return sum(a.elapsed_time(b) for a, b in pairs) / steps
 
+
+class ShardedSet:
+    """A set of 2-D tensors of one float type under one scheme, every tensor row-sharded over the ranks; this
+    rank's shards with their code, scale and restored buffers, and the prepared calls on them."""
+
+    def __init__(self, ctx: Ctx, shapes, elem, scheme, make_input, seed, codes=None, outs=None):
+        from cubek_b200 import TensorHandleRef, dequantize, quantize
+        from cubek_b200.shard import ShardedPerTensorSet, plan_rows
+        from cubek_b200.synthetic import TORCH_DTYPE
+
+        torch = ctx.torch
+        self.ctx, self.scheme, self.elem, self.global_shapes = ctx, scheme, elem, list(shapes)
+        self.per_tensor = scheme.level.is_tensor
+        self.shards = [plan_rows(r, c, ctx.world, elem, scheme)[ctx.rank] for r, c in shapes]
+        self.index = [i for i, sh in enumerate(self.shards) if sh.rows > 0]   # tensors this rank holds rows of
+        local = [(self.shards[i].rows, shapes[i][1]) for i in self.index]
+        tdt = TORCH_DTYPE[elem]
+        code_torch = torch.int32 if scheme.store.name == "U32" else torch.uint8
+        pdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[int(scheme.param)]
+        self.xs = [make_input(i, sh, seed) for i, sh in zip(self.index, local)]
+        self.codes = codes if codes is not None else [torch.empty(scheme.packed_shape(sh), dtype=code_torch, device=ctx.dev)
+                                                      for sh in local]
+        self.scales = [torch.empty(scheme.scales_shape(sh), dtype=pdt, device=ctx.dev) for sh in local]
+        self.outs = outs if outs is not None else [torch.empty(sh, dtype=tdt, device=ctx.dev) for sh in local]
+        self.ws = torch.zeros(1 << 16, dtype=torch.uint8, device=ctx.dev)
+        H = TensorHandleRef.from_torch
+        hx, hc, hs, ho = ([H(t) for t in ts] for ts in (self.xs, self.codes, self.scales, self.outs))
+        self.handles = (hx, hc, hs, ho)
+        if self.per_tensor:
+            # One cell per tensor of the SET, reduced over the ranks in one all-reduce.  A rank that holds rows of
+            # every tensor reduces straight into that vector; otherwise its cells are scattered into it first.
+            self.absmax = torch.zeros(len(shapes), dtype=torch.float32, device=ctx.dev)
+            self.holds_all = self.index == list(range(len(shapes)))
+            self.cells = self.absmax if self.holds_all else torch.zeros(len(self.index), dtype=torch.float32, device=ctx.dev)
+            self.index_t = torch.tensor(self.index, dtype=torch.int64, device=ctx.dev)
+            self.quant_set = ShardedPerTensorSet(ctx.client, hx, hc, hs, self.cells, scheme, elem)
+            self.quant = self._quant_per_tensor
+        else:
+            self.quant = quantize.PreparedDynamicBatch(ctx.client, hx, hc, hs, scheme, elem, H(self.ws))
+        self.dequant = dequantize.PreparedBatch(ctx.client, hc, ho, hs, scheme, elem)
+        q = d = 0
+        for r, c in shapes:
+            tq, td = tensor_bytes(r * c, elem.size, scheme)
+            q, d = q + tq, d + td
+        self.quant_bytes, self.dequant_bytes = q, d          # whole set, all ranks
+        self.local_input_bytes = sum(t.numel() * t.element_size() for t in self.xs)
+
+    def _quant_per_tensor(self):
+        from cubek_b200.shard import allreduce_absmax
+
+        self.quant_set.absmax()
+        if not self.holds_all:
+            self.absmax.zero_()
+            self.absmax.index_copy_(0, self.index_t, self.cells)
+        allreduce_absmax(self.absmax)
+        if not self.holds_all:
+            self.cells.copy_(self.absmax.index_select(0, self.index_t))
+        self.quant_set.quantize()
+
+    def step(self):
+        self.quant()
+        self.dequant()
+
+    def phases(self):
+        """(name, callable, whole-set algorithmic bytes) of the kernels of one step, in order."""
+        if not self.per_tensor:
+            return [("quantize_dynamic", self.quant, self.quant_bytes), ("dequantize", self.dequant, self.dequant_bytes)]
+        n_in = sum(r * c for r, c in self.global_shapes) * self.elem.size
+        return [("absmax", self.quant_set.absmax, n_in),
+                ("quantize_from_absmax", self.quant_set.quantize, self.quant_bytes - n_in),
+                ("dequantize", self.dequant, self.dequant_bytes)]
+
+    def per_call(self):
+        """The same work as one call per tensor (the reference's calling pattern)."""
+        from cubek_b200 import TensorHandleRef, dequantize, quantize
+        from cubek_b200.shard import quantize_per_tensor_sharded
+
+        ctx, H = self.ctx, TensorHandleRef.from_torch
+        hx, hc, hs, ho = self.handles
+        n = len(hx)
+        deq = [dequantize.Prepared(ctx.client, hc[i], ho[i], hs[i], self.scheme, self.elem) for i in range(n)]
+        if self.per_tensor and ctx.world > 1:
+            cells = [self.absmax[j: j + 1] for j in self.index]
+
+            def quant_one(i):
+                quantize_per_tensor_sharded(ctx.client, hx[i], hc[i], hs[i], cells[i], self.scheme, self.elem)
+        else:
+            calls = [quantize.PreparedDynamic(ctx.client, hx[i], hc[i], hs[i], self.scheme, self.elem, H(self.ws))
+                     for i in range(n)]
+
+            def quant_one(i):
+                calls[i]()
+
+        def run():
+            for i in range(n):
+                quant_one(i)
+                deq[i]()
+
+        return run
+
+
+def check_against_oracle(ctx: Ctx, sset: ShardedSet, rows_per_tensor=4, max_tensors=None):
+    """Outside the timed region: whole rows of this rank's shards (first, last and random ones of every tensor)
+    are compared bit for bit with the oracle - codes, scales and restored values.  Per tensor, the oracle is
+    given the scale that follows from the all-reduced torch absmax, and the ranks compare their scale bits."""
+    import numpy as np
+    from oracle import oracle as O
+
+    torch = ctx.torch
+    s = sset.scheme
+    F = O.np_dtype(int(sset.elem))
+    lo, hi = s.value.range()
+    gen = torch.Generator().manual_seed(1234 + ctx.rank)
+    checked_rows = mismatches = 0
+    picked = list(range(len(sset.xs)))
+    if max_tensors is not None and len(picked) > max_tensors:
+        picked = picked[:: max(1, len(picked) // max_tensors)][:max_tensors]
+    if sset.per_tensor:
+        want_amax = torch.zeros(len(sset.global_shapes), dtype=torch.float32, device=ctx.dev)
+        for j, x in zip(sset.index, sset.xs):
+            want_amax[j] = x.float().abs().max()
+        if ctx.world > 1:
+            ctx.dist.all_reduce(want_amax, op=ctx.dist.ReduceOp.MAX)
+        want_amax = want_amax.cpu().numpy()
+    for k in picked:
+        x, codes, scales, out = sset.xs[k], sset.codes[k], sset.scales[k], sset.outs[k]
+        rows = x.shape[0]
+        extra = torch.randint(0, rows, (max(rows_per_tensor - 2, 0),), generator=gen).tolist()
+        pick = torch.tensor(sorted(set([0, rows - 1] + extra)), device=ctx.dev)
+        xs = torch_to_numpy(x[pick])
+        if sset.per_tensor:
+            amax = np.float32(want_amax[sset.index[k]])
+            want_scale = np.array([np.float32(2) * amax / np.float32(hi - lo)], dtype=np.float32).astype(F)
+            o_codes, o_scale = O.quantize(xs, want_scale, s)
+            got_scale = torch_to_numpy(scales).reshape(-1)
+        else:
+            o_codes, o_scale = O.quantize_dynamic(xs, s)
+            got_scale = torch_to_numpy(scales[pick])
+        o_restored = O.dequantize(o_codes, o_scale, s, F)
+        ok = (got_scale.tobytes() == o_scale.reshape(got_scale.shape).tobytes()
+              and torch_to_numpy(codes[pick]).tobytes() == o_codes.tobytes()
+              and torch_to_numpy(out[pick]).tobytes() == o_restored.tobytes())
+        mismatches += 0 if ok else 1
+        checked_rows += int(pick.numel())
+    scales_agree = True
+    if sset.per_tensor and ctx.world > 1:
+        # every rank that holds rows of a tensor must have written the same scale bits
+        mine = torch.full((len(sset.global_shapes),), -1, dtype=torch.int64, device=ctx.dev)
+        for j, sc in zip(sset.index, sset.scales):
+            mine[j] = sc.view(torch.int32).reshape(-1)[0].to(torch.int64)
+        gathered = [torch.empty_like(mine) for _ in range(ctx.world)]
+        ctx.dist.all_gather(gathered, mine)
+        g = torch.stack(gathered)
+        held = g >= 0
+        ref = torch.where(held, g, torch.full_like(g, -1)).max(dim=0).values
+        scales_agree = bool((~held | (g == ref.unsqueeze(0))).all().item())
+    t = torch.tensor([mismatches, checked_rows, 0 if scales_agree else 1], dtype=torch.int64, device=ctx.dev)
+    if ctx.world > 1:
+        ctx.dist.all_reduce(t)
+    return {"ok": int(t[0]) == 0 and int(t[2]) == 0, "rows_compared": int(t[1]), "tensors_with_mismatch": int(t[0]),
+            "scale_bits_agree_across_ranks": int(t[2]) == 0}
+
+
+def llama_input(ctx):
+    torch = ctx.torch
+
+    def make(i, shape, seed):
+        g = torch.Generator(device=ctx.dev)
+        g.manual_seed(0x5EED0004 + 1000003 * (seed + i) + 7919 * ctx.rank)
+        return (torch.randn(shape, generator=g, device=ctx.dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+    return make
+
+
+def workload_input(ctx, workload):
+    from dataclasses import replace
+
+    from cubek_b200.synthetic import generate
+
+    def make(i, shape, seed):
+        return generate(replace(workload, shape=tuple(shape)), ctx.dev, seed_offset=seed + i + 100 * ctx.rank)
+
+    return make
+
+
+def timed_region(ctx, step, args):
+    """Warm-up, barrier, K timed steps between two events, barrier; returns (ms per step as the maximum over the
+    ranks, kernel launches of this rank inside the region, clocks sampled on rank 0)."""
+    torch = ctx.torch
     for _ in range(args.warmup):
         step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    ctx.barrier()
+    sampler = ClockSampler(ctx.local_rank)
+    if ctx.rank == 0:
         sampler.start()
-    launches_before = lib.qk_launch_count()
+    before = ctx.lib.qk_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
         step()
     stop.record()
-    barrier()
-    launches = lib.qk_launch_count() - launches_before
-    elapsed_ms = start.elapsed_time(stop)
-
-    # Per-kernel durations for the roofline: the same launches, one kind at a time, again
-    # bracketed by events on the launch stream (an event between every pair of kernels would
-    # serialise launch and execution and time the gap, not the kernel).
-    q_avg = timed(quant_batch, args.steps)
-    d_avg = timed(dequant_batch, args.steps)
-    # Distribution over single steps (an event pair per step; the gaps they add are part of these figures).
-    per_step = []
-    for _ in range(min(args.steps, 50)):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        step()
-        b.record()
-        per_step.append((a, b))
-    torch.cuda.synchronize()
-    per_step = sorted(a.elapsed_time(b) for a, b in per_step)
-    single_ms = timed(step_single, max(args.steps // 2, 1))
-    single_q = timed(lambda: [c() for c in quant_calls], max(args.steps // 2, 1)) / B
-    single_d = timed(lambda: [c() for c in dequant_calls], max(args.steps // 2, 1)) / B
-    clocks = sampler.stop() if rank == 0 else None
-
-    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-
-    # sanity: the last round trip must be within half a quantization step (cheap, outside timing)
-    err_ok = bool(torch.isfinite(outs[-1].float()).all().item())
-
-    # ---- end to end through host buffers (pinned), copies inside the timed region ---------------
-    e2e = run_e2e(args, workload, dev, local_rank, rank, world, xs)
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    q_bytes, d_bytes = algorithmic_bytes(workload)
-    total_bytes = (q_bytes + d_bytes) * B * args.steps * world
-    value = total_bytes / (elapsed_ms * 1e-3) / 1e9
-    peak, peak_kind = measured_peak()
-    kernels = {
-        "quantize_dynamic": {"avg_ms": round(q_avg, 5), "bytes": q_bytes * B, "gbs": round(q_bytes * B / q_avg / 1e6, 1),
-                             "tensors_per_launch": B},
-        "dequantize": {"avg_ms": round(d_avg, 5), "bytes": d_bytes * B, "gbs": round(d_bytes * B / d_avg / 1e6, 1),
-                       "tensors_per_launch": B},
-    }
-    dom = "quantize_dynamic" if q_avg >= d_avg else "dequantize"
-    achieved = kernels[dom]["gbs"]
-    traffic = NCU_TRAFFIC_BYTES.get(workload.name, {}).get(dom)
-    out = {
-        "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": elem.name.lower(), "data": "synthetic",
-        "config": config_of(workload, args),
-        "pct_of_spec_peak": round(100 * value / world / SPEC_PEAK_GBS, 1),
-        "pct_of_measured_peak": round(100 * value / world / peak, 1),
-        "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": traffic * B if traffic else None,
-                     "peak_source": f"{peak_kind} copy bandwidth", "kernels": kernels},
-        "single_tensor_calls": {
-            "value": round((q_bytes + d_bytes) * B / single_ms / 1e6, 1), "unit": "GB/s (this rank)",
-            "ms_per_step": round(single_ms, 4),
-            "quantize_dynamic": {"avg_ms": round(single_q, 5), "gbs": round(q_bytes / single_q / 1e6, 1)},
-            "dequantize": {"avg_ms": round(single_d, 5), "gbs": round(d_bytes / single_d / 1e6, 1)}},
-        "step_ms": {"median": round(per_step[len(per_step) // 2], 4), "best": round(per_step[0], 4),
-                    "worst": round(per_step[-1], 4), "samples": len(per_step)},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "finite_output": err_ok,
-    }
-    if world == 1:
-        out["cpu_baseline"] = cpu_baseline(workload)
-    emit(out)
-    if world > 1:
-        dist.destroy_process_group()
+    ctx.barrier()
+    launches = ctx.lib.qk_launch_count() - before
+    clocks = sampler.stop() if ctx.rank == 0 else None
+    ms = ctx.max_over_ranks(start.elapsed_time(stop)) / args.steps
+    return ms, int(launches), clocks
 
 
-def run_weight_set(args, per_tensor: bool, row_sharded: bool = False):
-    """BASELINE config 5: the 225 bf16 matrices of a Llama-3-8B-shaped model (15 GB), q8 with
-    block-128 scales or per-tensor scales, whole tensors placed round-robin over the ranks (strong
-    scaling: the set is fixed).  One step = fused quantize + dequantize of every tensor a rank owns."""
-    import torch
-    import torch.distributed as dist
+def phase_table(ctx, sets, steps):
+    """Per kernel kind: launches per call, average launch duration (this rank's events, maximum over the ranks)
+    and algorithmic GB/s over all ranks.  One kind at a time between two events (an event between every pair
+    of kernels would time the launch gap, not the kernel)."""
+    table = {}
+    for label, sset in sets:
+        for name, fn, nbytes in sset.phases():
+            fn()
+            ctx.torch.cuda.synchronize()
+            before = ctx.lib.qk_launch_count()
+            fn()
+            launches = int(ctx.lib.qk_launch_count() - before)
+            ctx.barrier()
+            ms = ctx.max_over_ranks(ctx.time_steps(fn, steps))
+            kernels = launches - (1 if name == "absmax" else 0)    # the absmax call counts its memset as a launch
+            table[f"{label}.{name}"] = {
+                "kernel_launches_per_step": kernels, "avg_launch_ms": round(ms / max(kernels, 1), 5),
+                "ms_per_step": round(ms, 5), "bytes_per_step": int(nbytes),
+                "bytes_per_launch": int(nbytes / ctx.world / max(kernels, 1)),
+                "gbs": round(nbytes / ms / 1e6, 1), "gbs_per_gpu": round(nbytes / ms / 1e6 / ctx.world, 1)}
+    return table
 
-    from cubek_b200 import (ComputeClient, ElemType, QuantLevel, QuantScheme, QuantStore, QuantValue, TensorHandleRef,
-                            dequantize, quantize)
-    from cubek_b200 import _ffi
-    from cubek_b200.shard import assign_round_robin
+
+def run_weight_set(ctx: Ctx, args):
+    from cubek_b200 import ElemType, QuantLevel, QuantScheme, QuantStore, QuantValue
     from cubek_b200.weights import llama3_8b_shapes
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    lib = _ffi.lib()
-    level = QuantLevel.Tensor if per_tensor else QuantLevel.block([128])
-    scheme = QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32, level=level)
-    shapes = llama3_8b_shapes()
-    g = torch.Generator(device=dev)
-    g.manual_seed(0x5EED0004 + rank)
-    if row_sharded:
-        # every tensor is split by rows over the ranks; the per-tensor absmax needs one all-reduce(MAX)
-        from cubek_b200.shard import ShardedPerTensorSet, plan_rows
-
-        my_shapes = [(plan_rows(r, c, world, ElemType.BF16, scheme)[rank].rows, c) for _, r, c in shapes]
-        my_shapes = [sh for sh in my_shapes if sh[0] > 0]
-    else:
-        owned = assign_round_robin([r * c for _, r, c in shapes], world)[rank]
-        my_shapes = [(shapes[i][1], shapes[i][2]) for i in owned]
-    xs = [(torch.randn(sh, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16) for sh in my_shapes]
-    codes = [torch.empty(scheme.packed_shape(x.shape), dtype=torch.int32, device=dev) for x in xs]
-    scales = [torch.empty(scheme.scales_shape(x.shape), dtype=torch.float32, device=dev) for x in xs]
-    outs = [torch.empty_like(x) for x in xs]
-    ws = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
-    H = TensorHandleRef.from_torch
-    client = ComputeClient.current()
-    if row_sharded:
-        absmax = torch.zeros(len(xs), dtype=torch.float32, device=dev)
-        qb = ShardedPerTensorSet(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], absmax, scheme,
-                                 ElemType.BF16)
-    else:
-        qb = quantize.PreparedDynamicBatch(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales],
-                                           scheme, ElemType.BF16, H(ws))
-    db = dequantize.PreparedBatch(client, [H(t) for t in codes], [H(t) for t in outs], [H(t) for t in scales], scheme,
-                                  ElemType.BF16)
+    shapes = [(r, c) for _, r, c in llama3_8b_shapes()]
+    make = llama_input(ctx)
+    sets = []
+    block = tensor = None
+    if not args.workload.endswith("_tensor"):
+        block = ShardedSet(ctx, shapes, ElemType.BF16,
+                           QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32, level=QuantLevel.block([128])), make, 0)
+        sets.append(("block128", block))
+    if not args.workload.endswith("_block128"):
+        # the two schemes share inputs, codes and restored buffers (same sizes); only the scales differ
+        shared = block
+        tensor = ShardedSet(ctx, shapes, ElemType.BF16, QuantScheme(value=QuantValue.Q8S, store=QuantStore.U32),
+                            (lambda i, sh, seed, xs=shared.xs: xs[shared.index.index(i)]) if shared else make, 0,
+                            codes=shared.codes if shared else None, outs=shared.outs if shared else None)
+        sets.append(("tensor", tensor))
 
     def step():
-        qb()
-        db()
+        for _, s in sets:
+            s.step()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    before = lib.qk_launch_count()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(args.steps):
-        step()
-    b.record()
-    barrier()
-    launches = lib.qk_launch_count() - before
-    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        n = sum(r * c for _, r, c in shapes)
-        nscales = len(shapes) if per_tensor else n // 128
-        q_bytes = n * 2 * (2 if per_tensor else 1) + n + nscales * 4
-        d_bytes = n + nscales * 4 + n * 2
-        ms = float(t.item()) / args.steps
-        value = (q_bytes + d_bytes) / ms / 1e6
-        peak, kind = measured_peak()
-        emit({
-            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "tensors": len(shapes), "elements": n,
-                       "level": "tensor" if per_tensor else "block[128]", "value": "Q8S", "store": "U32",
-                       "placement": ("every tensor split by rows over the ranks; one all-reduce(MAX) of 225 floats per step"
-                                     if row_sharded else "whole tensors, largest first onto the least loaded rank"),
-                       "api": "qk_quantize_dynamic_batch + qk_dequantize_batch", "distribution": "normal(0,0.02)"},
-            "pct_of_measured_peak": round(100 * value / world / peak, 1), "peak_source": f"{kind} copy bandwidth",
-            "gpu_launches": int(launches)})
-    if world > 1:
-        dist.destroy_process_group()
+    ms, launches, clocks = timed_region(ctx, step, args)
+    total_bytes = sum(s.quant_bytes + s.dequant_bytes for _, s in sets)
+    # parity right after the timed region: the buffers hold the last step's results of the LAST scheme run on them
+    parity = {}
+    for label, s in sets:
+        s.step()
+        ctx.torch.cuda.synchronize()
+        parity[label] = check_against_oracle(ctx, s, rows_per_tensor=4)
+    table = phase_table(ctx, sets, max(args.steps // 2, 2))
+    per_scheme = {}
+    for label, s in sets:
+        t = ctx.max_over_ranks(ctx.time_steps(s.step, max(args.steps // 2, 2)))
+        per_scheme[label] = {"ms_per_step": round(t, 4), "gbs": round((s.quant_bytes + s.dequant_bytes) / t / 1e6, 1)}
+    return {"ms": ms, "launches": launches, "clocks": clocks, "bytes": total_bytes, "parity": parity, "kernels": table,
+            "per_scheme": per_scheme, "sets": sets, "dtype": "bf16",
+            "traffic_key": "q8_block128_bf16"}
 
 
-def run_e2e(args, workload, dev, local_rank, rank, world, xs):
-    """Same metric through ``qk_roundtrip_host``: inputs in pinned host memory, codes + scales +
-    restored tensor read back to pinned host memory, every step."""
-    import torch
-    import torch.distributed as dist
+def run_single_config(ctx: Ctx, args, workload, batch, headline):
+    """One of the single-tensor configurations: ``batch`` distinct tensors, each row-sharded over the ranks."""
+    sset = ShardedSet(ctx, [workload.shape] * batch, workload.elem, workload.scheme, workload_input(ctx, workload),
+                      seed=workload.index * 17)
+    flush = sset.local_input_bytes < 2 * L2_BYTES
+    total = sset.quant_bytes + sset.dequant_bytes
+    rec = {}
+    if headline:
+        ms, launches, clocks = timed_region(ctx, sset.step, args)
+        rec.update(ms=ms, launches=launches, clocks=clocks, bytes=total, dtype=workload.elem.name.lower(),
+                   traffic_key=workload.name.rsplit("_", 1)[0])
+    steps = args.steps if headline else max(args.steps // 2, 3)
+    for _ in range(3):
+        sset.step()
+    ctx.barrier()
+    batch_ms = ctx.max_over_ranks(ctx.time_steps(sset.step, steps, flush))
+    sset.step()
+    ctx.torch.cuda.synchronize()
+    parity = check_against_oracle(ctx, sset, rows_per_tensor=6, max_tensors=2)
+    table = phase_table(ctx, [("batch", sset)], steps) if not flush else {}
+    if flush:
+        for name, fn, nbytes in sset.phases():
+            t = ctx.max_over_ranks(ctx.time_steps(fn, steps, True))
+            table[f"batch.{name}"] = {"ms_per_step": round(t, 5), "bytes_per_step": int(nbytes), "gbs": round(nbytes / t / 1e6, 1),
+                                      "gbs_per_gpu": round(nbytes / t / 1e6 / ctx.world, 1)}
+    per_call = sset.per_call()
+    per_call()
+    ctx.barrier()
+    call_ms = ctx.max_over_ranks(ctx.time_steps(per_call, steps, flush))
+    peak, _ = measured_peak()
+    summary = {
+        "tensors_per_step": batch, "shape": list(workload.shape),
+        "batch": {"gbs": round(total / batch_ms / 1e6, 1), "ms_per_step": round(batch_ms, 4),
+                  "frac_of_measured_per_gpu": round(total / batch_ms / 1e6 / ctx.world / peak, 4),
+                  "frac_of_spec_per_gpu": round(total / batch_ms / 1e6 / ctx.world / SPEC_PEAK_GBS, 4)},
+        "per_call": {"gbs": round(total / call_ms / 1e6, 1), "ms_per_step": round(call_ms, 4),
+                     "frac_of_measured_per_gpu": round(total / call_ms / 1e6 / ctx.world / peak, 4),
+                     "frac_of_spec_per_gpu": round(total / call_ms / 1e6 / ctx.world / SPEC_PEAK_GBS, 4)},
+        "kernels": {k.split(".", 1)[1]: {"gbs_per_gpu": v["gbs_per_gpu"], "ms_per_step": v["ms_per_step"]} for k, v in table.items()},
+        "l2": "flushed between steps (read-only pass over 512 MB, outside the event pairs)" if flush
+              else "per-rank inputs of a step exceed twice the L2",
+        "parity_checked": parity["ok"],
+    }
+    rec.update(summary=summary, kernels=table, parity={"batch": parity}, sets=[("batch", sset)])
+    return rec
 
-    from cubek_b200 import TensorHandleRef
-    from cubek_b200 import _ffi
-    from cubek_b200.synthetic import TORCH_DTYPE
 
-    lib = _ffi.lib()
-    scheme, elem = workload.scheme, workload.elem
-    r, c = workload.shape
-    nb = min(args.batch, args.e2e_batch)
+def run_e2e(ctx: Ctx, args, sset: ShardedSet, what: str):
+    """Same metric through ``qk_roundtrip_host``: this rank's shards in pinned host memory; codes, scales and the
+    restored tensor read back to pinned host memory, every step.  Also times the same copies alone (both
+    directions at once on two streams, no kernels): the ceiling the host link and host memory set."""
+    import ctypes as C
+
+    from cubek_b200 import TensorHandleRef, _ffi
+
+    torch, lib = ctx.torch, ctx.lib
+    scheme, elem = sset.scheme, sset.elem
+    take = list(range(min(len(sset.xs), args.e2e_tensors)))
     steps = max(1, min(args.steps, args.e2e_steps))
-    tdt = TORCH_DTYPE[elem]
-    code_torch = torch.int32 if scheme.store.name == "U32" else torch.uint8
-    pdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[int(scheme.param)]
-    h_in = [xs[i].cpu().pin_memory() for i in range(nb)]
-    h_codes = [torch.empty(scheme.packed_shape((r, c)), dtype=code_torch).pin_memory() for _ in range(nb)]
-    h_scales = [torch.empty(scheme.scales_shape((r, c)), dtype=pdt).pin_memory() for _ in range(nb)]
-    h_out = [torch.empty((r, c), dtype=tdt).pin_memory() for _ in range(nb)]
+    h_in = [sset.xs[i].cpu().pin_memory() for i in take]
+    h_codes = [torch.empty_like(sset.codes[i], device="cpu").pin_memory() for i in take]
+    h_scales = [torch.empty_like(sset.scales[i], device="cpu").pin_memory() for i in take]
+    h_out = [torch.empty_like(sset.outs[i], device="cpu").pin_memory() for i in take]
     H = TensorHandleRef.from_torch
-    cin = [_ffi.CTensor(H(t)) for t in h_in]
-    ccodes = [_ffi.CTensor(H(t)) for t in h_codes]
-    cscales = [_ffi.CTensor(H(t)) for t in h_scales]
-    cout = [_ffi.CTensor(H(t)) for t in h_out]
+    cin, ccodes, cscales, cout = ([_ffi.CTensor(H(t)) for t in ts] for ts in (h_in, h_codes, h_scales, h_out))
     sch = _ffi.c_scheme(scheme)
-    need = lib.qk_host_roundtrip_staging_bytes(cin[0].ref(), sch, int(elem))
-    staging = torch.empty(int(need), dtype=torch.uint8, device=dev)
+    need = max(int(lib.qk_host_roundtrip_staging_bytes(c.ref(), sch, int(elem))) for c in cin)
+    staging = torch.empty(need, dtype=torch.uint8, device=ctx.dev)
 
     def step():
-        for i in range(nb):
+        for i in range(len(take)):
             _ffi.check(lib.qk_roundtrip_host(cin[i].ref(), ccodes[i].ref(), cscales[i].ref(), cout[i].ref(), sch,
-                                             int(elem), staging.data_ptr(), int(need), local_rank))
+                                             int(elem), staging.data_ptr(), need, ctx.local_rank))
 
-    step()   # warm-up (creates the internal streams)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    torch.cuda.synchronize()
-    secs = time.perf_counter() - t0
-    t = torch.tensor([secs], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    secs = float(t.item())
-    q_bytes, d_bytes = algorithmic_bytes(workload)
+    def wall(fn, reps):
+        fn()
+        ctx.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return ctx.max_over_ranks(time.perf_counter() - t0) / reps
+
+    secs = wall(step, steps)
+    # copies alone
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    d_in = [sset.xs[i] for i in take]
+
+    def copies():
+        with torch.cuda.stream(up):
+            for h, d in zip(h_in, d_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(down):
+            for i, k in enumerate(take):
+                h_codes[i].copy_(sset.codes[k], non_blocking=True)
+                h_scales[i].copy_(sset.scales[k], non_blocking=True)
+                h_out[i].copy_(sset.outs[k], non_blocking=True)
+        up.synchronize()
+        down.synchronize()
+
+    copy_secs = wall(copies, steps)
     h2d = sum(t.numel() * t.element_size() for t in h_in)
     d2h = sum(t.numel() * t.element_size() for ts in (h_codes, h_scales, h_out) for t in ts)
-    # the restored tensor must be what the device path produced
-    return {"value": round((q_bytes + d_bytes) * nb * steps * world / secs / 1e9, 2), "unit": "GB/s",
-            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
-            "tensors_per_step": nb, "ms_per_step": round(secs / steps * 1e3, 3),
-            "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies)"}
+    # bytes of the metric for the tensors taken, all ranks
+    nbytes = 0
+    for i in take:
+        r, c = sset.global_shapes[sset.index[i]]
+        q, d = tensor_bytes(r * c, elem.size, scheme)
+        nbytes += q + d
+    return {"value": round(nbytes / secs / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "steps": steps, "ms_per_step": round(secs * 1e3, 3), "sample": what,
+            "copies_only": {"ms_per_step": round(copy_secs * 1e3, 3), "h2d_gbs_per_rank": round(h2d / copy_secs / 1e9, 1),
+                            "d2h_gbs_per_rank": round(d2h / copy_secs / 1e9, 1),
+                            "note": "the same host<->device copies with no kernels, both directions at once: the "
+                                    "ceiling set by the host link and, with several ranks, by host memory"},
+            "fraction_of_copy_ceiling": round(copy_secs / secs, 3),
+            "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies); bytes per step are this rank's"}
+
+
+def run_gpu(args):
+    from cubek_b200.synthetic import WORKLOADS
+
+    ctx = Ctx(args)
+    torch = ctx.torch
+    peak, peak_kind = measured_peak()
+    is_set = args.workload.startswith("llama3_8b_q8")
+    if is_set:
+        main = run_weight_set(ctx, args)
+        e2e_set, e2e_what = main["sets"][0][1], (f"the first {args.e2e_tensors} tensors of the set (one layer: q, k, v, o, gate, up, down = "
+                                                 "218 M of the 7505 M elements), scheme " + main["sets"][0][0])
+    else:
+        w = WORKLOADS[args.workload]
+        main = run_single_config(ctx, args, w, args.batch, headline=True)
+        e2e_set, e2e_what = main["sets"][0][1], f"{min(args.e2e_tensors, args.batch)} of the {args.batch} tensors of a step"
+    e2e = run_e2e(ctx, args, e2e_set, e2e_what)
+
+    configs = {}
+    if is_set and not args.no_configs:
+        del main["sets"]
+        e2e_set = None
+        torch.cuda.empty_cache()
+        for name in SUB_CONFIGS:
+            w = WORKLOADS[name]
+            rec = run_single_config(ctx, args, w, 2 if w.shape[0] * w.shape[1] >= 1 << 28 else 8, headline=False)
+            configs[name] = rec["summary"]
+            del rec
+            torch.cuda.empty_cache()
+
+    if ctx.rank == 0:
+        value = main["bytes"] / main["ms"] / 1e6
+        kernels = main["kernels"]
+        dom = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
+        d = kernels[dom]
+        achieved = d["gbs_per_gpu"]
+        traffic = None
+        tk = NCU_WRITE_RESIDUE_BYTES.get((dom.split(".", 1)[1], main.get("traffic_key", "")))
+        if tk and "bytes_per_launch" in d:
+            traffic = int(max(d["bytes_per_launch"] - tk[0], 0))
+        parity_ok = all(p["ok"] for p in main["parity"].values())
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": ctx.world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(main["ms"], 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": main["dtype"], "data": "synthetic",
+            "config": config_of(args.workload, ctx.world),
+            "pct_of_spec_peak_per_gpu": round(100 * value / ctx.world / SPEC_PEAK_GBS, 1),
+            "pct_of_measured_peak_per_gpu": round(100 * value / ctx.world / peak, 1),
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "frac_of_spec": round(achieved / SPEC_PEAK_GBS, 4),
+                         "traffic": traffic, "traffic_source": tk[1] if tk else None,
+                         "avg_launch_ms": d.get("avg_launch_ms"), "bytes_per_launch": d.get("bytes_per_launch"),
+                         "peak_source": f"{peak_kind} copy bandwidth (a plain copy: a lower bound of the peak, so a "
+                                        "fraction may read slightly above 1)",
+                         "kernels": kernels},
+            "parity_checked": parity_ok, "parity": main["parity"],
+            "e2e": e2e, "gpu_launches": main["launches"], "clocks": main["clocks"],
+        }
+        if "per_scheme" in main:
+            out["per_scheme"] = main["per_scheme"]
+        if "summary" in main:
+            out["headline_config"] = main["summary"]
+        if configs:
+            out["configs"] = configs
+        if ctx.world == 1:
+            out["cpu_baseline"] = cpu_baseline(args.workload)
+        if ctx.world > 1 and is_set:
+            out["limits"] = ("per-rank shards shrink with N while launches per step stay (5 batched launches per scheme "
+                             "of up to 64 tensors) and the tensor scheme adds one all-reduce of 225 floats")
+        emit(out)
+    if ctx.world > 1:
+        ctx.dist.destroy_process_group()
+
+
+def run_case(args):
+    """A few fused quantize + dequantize launches of one configuration on a reduced number of rows: the small
+    case a profiler captures.  Layouts: contiguous, transposed (`.t()` views of [cols, rows] matrices), slice
+    (column slices of matrices 256 columns wider), twocall (compute_scales, quantize with given scales,
+    dequantize on contiguous tensors)."""
+    import torch
+
+    from cubek_b200 import ComputeClient, TensorHandleRef, dequantize, quantize
+    from cubek_b200.synthetic import WORKLOADS, generate
+
+    w = WORKLOADS[args.case]
+    rows = args.rows or w.shape[0]
+    layout = args.layout
+    s, cols = w.scheme, w.shape[1]
+    x = generate(w, "cuda", rows=rows)
+
+    def like(t):
+        if layout == "transposed":
+            return torch.empty((cols, rows), dtype=t.dtype, device="cuda").t()
+        if layout == "slice":
+            return torch.empty((rows, cols + 256), dtype=t.dtype, device="cuda")[:, 128:128 + cols]
+        return torch.empty_like(t)
+
+    if layout in ("transposed", "slice"):
+        view = like(x)
+        view.copy_(x)
+        x = view
+    code_dtype = torch.int32 if s.store.name == "U32" else torch.uint8
+    codes = torch.empty(s.packed_shape((rows, cols)), dtype=code_dtype, device="cuda")
+    scales = torch.empty(s.scales_shape((rows, cols)), dtype=torch.float32, device="cuda")
+    out = like(x)
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    H, client = TensorHandleRef.from_torch, ComputeClient.current()
+    given = torch.empty(s.scales_shape((rows, cols)), dtype=x.dtype, device="cuda")
+    for _ in range(args.iters):
+        if layout == "twocall":
+            quantize.compute_scales(client, H(x), H(given), s, w.elem, H(ws))
+            quantize.launch_ref(client, H(x), H(codes), H(given), H(scales), s, w.elem)
+        else:
+            quantize.launch_dynamic(client, H(x), H(codes), H(scales), s, w.elem, H(ws))
+        dequantize.launch_ref(client, H(codes), H(out), H(scales), s, w.elem)
+    torch.cuda.synchronize()
+    emit({"case": w.name, "rows": rows, "iters": args.iters, "layout": layout, "max_abs_restored": float(out.float().abs().max())})
 
 
 _RESULT_FD = None
@@ -594,28 +908,29 @@ def main():
     keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
-    ap.add_argument("--batch", type=int, default=8, help="distinct tensors per step")
-    ap.add_argument("--e2e-batch", type=int, default=2)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD,
+                    help="llama3_8b_q8 (both schemes), llama3_8b_q8_block128, llama3_8b_q8_tensor, or a single-tensor configuration")
+    ap.add_argument("--batch", type=int, default=8, help="distinct tensors per step of a single-tensor configuration")
+    ap.add_argument("--e2e-tensors", type=int, default=7)
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-configs", action="store_true", help="skip the records of the single-tensor configurations")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B runs)")
-    ap.add_argument("--tune", default="", help="library tuning keys for A/B runs, e.g. 11=2,8=1 (see qk_set_tuning)")
+    ap.add_argument("--tune", default="", help="library tuning keys for A/B runs, e.g. 11=2,8=1")
+    ap.add_argument("--case", default="", help="run a few launches of this configuration and exit (profiler case)")
+    ap.add_argument("--rows", type=int, default=0, help="rows of the --case tensor (default: the configuration's)")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--layout", default="contiguous", choices=["contiguous", "transposed", "slice", "twocall"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-
-    from cubek_b200.synthetic import WORKLOADS
-
-    if args.workload.startswith("llama3_8b_q8_") and args.impl != "reference":
-        run_weight_set(args, per_tensor="tensor" in args.workload, row_sharded=args.workload.endswith("_sharded"))
-        return
-    workload = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        run_reference(args, workload)
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
     else:
-        run_gpu(args, workload)
+        run_gpu(args)
 
 
 if __name__ == "__main__":

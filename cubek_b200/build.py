@@ -70,26 +70,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    build_device_api_probe()
     return LIB
-
-
-PROBE_SRC = PKG.parent / "tests" / "device_api" / "probe.cu"
-PROBE_LIB = PKG.parent / "tests" / "device_api" / "libdevice_api_probe.so"
-
-
-def build_device_api_probe() -> Path | None:
-    """The test kernel that exercises the public device header (include/cubek_quant_b200_device.cuh);
-    a shared object of its own, loaded only by the GPU test of that header."""
-    if not PROBE_SRC.exists():
-        return None
-    if _stale(PROBE_LIB, [PROBE_SRC, *_headers()]):
-        cmd = [NVCC, *NVCC_FLAGS, "-shared", str(PROBE_SRC), "-o", str(PROBE_LIB), "-lcudart_static", "-ldl",
-               "-lpthread", "-lrt"]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"nvcc failed for {PROBE_SRC.name}:\n{res.stdout}\n{res.stderr}")
-    return PROBE_LIB
 
 
 if __name__ == "__main__":

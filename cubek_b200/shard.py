@@ -115,9 +115,22 @@ class ShardedPerTensorSet:
         self._absmax, self._group, self._scheme = absmax, group, _ffi.c_scheme(scheme)
         self._elem, self._stream, self._lib, self._ffi = int(elem), client.stream, _ffi.lib(), _ffi
 
-    def __call__(self) -> None:
-        f = self._ffi
-        f.check(self._lib.qk_absmax_batch(self._in.count, self._in.array, self._elem, self._absmax.data_ptr(), self._stream))
+    def absmax(self) -> None:
+        """Phase 1: one absmax per shard into the cells (``qk_absmax_batch``: a memset and one launch per 128 tensors)."""
+        self._ffi.check(self._lib.qk_absmax_batch(self._in.count, self._in.array, self._elem, self._absmax.data_ptr(),
+                                                  self._stream))
+
+    def exchange(self) -> None:
+        """Phase 2: the only collective of the path, MAX over the ranks of one f32 per tensor."""
         allreduce_absmax(self._absmax, self._group)
-        f.check(self._lib.qk_quantize_from_absmax_batch(self._in.count, self._in.array, self._out.array, self._sc.array,
-                                                        self._absmax.data_ptr(), self._scheme, self._elem, self._stream))
+
+    def quantize(self) -> None:
+        """Phase 3: quantize every shard with the scale derived on the device from its (global) absmax cell."""
+        self._ffi.check(self._lib.qk_quantize_from_absmax_batch(self._in.count, self._in.array, self._out.array,
+                                                                self._sc.array, self._absmax.data_ptr(), self._scheme,
+                                                                self._elem, self._stream))
+
+    def __call__(self) -> None:
+        self.absmax()
+        self.exchange()
+        self.quantize()

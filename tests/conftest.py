@@ -43,4 +43,7 @@ def _built_libraries():
     from oracle import oracle
 
     oracle.build()
+    from tests.device_api.build_probe import build_probe
+
+    build_probe()
     yield

@@ -22,7 +22,7 @@ PROBE = Path(__file__).resolve().parent / "device_api" / "libdevice_api_probe.so
 @pytest.fixture(scope="module")
 def probe():
     if not PROBE.exists():
-        pytest.fail(f"{PROBE} is missing: run `python -m cubek_b200.build`")
+        pytest.fail(f"{PROBE} is missing: tests/device_api/build_probe.py builds it")
     lib = C.CDLL(str(PROBE))
     lib.probe_dequantize.restype = C.c_int
     lib.probe_dequantize.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.POINTER(_ffi.QkScheme),

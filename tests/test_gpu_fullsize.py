@@ -1,8 +1,8 @@
-"""The benchmark configurations at their full sizes.  The oracle is too slow for whole tensors of
-this size, so parity is established through (1) bit-exact comparison with the oracle on a random
-sample of whole rows, (2) size-independent properties: the fused one-pass result equals the
-two-call result, the round-trip error is within half a quantization step of every element, and
-re-quantizing the restored tensor with the same scales reproduces the codes (idempotence)."""
+"""The benchmark configurations at their full sizes: every element of every configuration is compared bit for
+bit with the oracle (codes, scales, restored values), and so are the eight tensors of one batched benchmark
+step.  Size-independent properties are checked besides: the fused one-pass result equals the two-call result,
+the round-trip error is within half a quantization step of every element, and re-quantizing the restored
+tensor with the same scales reproduces the codes (idempotence)."""
 import numpy as np
 import pytest
 import torch
@@ -78,24 +78,35 @@ def test_full_size_configuration(name):
         if elem == ElemType.F32:
             assert torch.equal(codes, codes3)
 
-    # (d) bit-exact against the oracle on 48 whole rows (per block) / on the whole tensor's scale
-    g = torch.Generator().manual_seed(7)
-    pick = torch.sort(torch.randperm(rows, generator=g)[:48]).values
-    if s.level.is_tensor:
-        # the oracle needs the global scale: take it from the device result after checking it
-        xs = to_numpy(x[pick.cuda()].contiguous(), F)
-        amax = float(x.float().abs().max())
-        lo, hi = s.value.range()
-        want_scale = np.array([np.float32(2) * np.float32(amax) / np.float32(hi - lo)], dtype=np.float32).astype(F)
-        o_codes, o_scale = O.quantize(xs, want_scale, s)
-        assert_bits_equal(to_numpy(out_scale, np.float32), o_scale, "scale")
-    else:
-        xs = to_numpy(x[pick.cuda()].contiguous(), F)
-        o_codes, o_scale = O.quantize_dynamic(xs, s)
-        assert_bits_equal(to_numpy(out_scale[pick.cuda()].contiguous(), np.float32), o_scale, "scales")
-    assert_bits_equal(to_numpy(codes[pick.cuda()].contiguous(), o_codes.dtype), o_codes, "codes")
+    # (d) bit-exact against the oracle on the whole tensor
+    o_codes, o_scale = O.quantize_dynamic(to_numpy(x, F), s)
+    assert_bits_equal(to_numpy(out_scale, np.float32), o_scale, "scales")
+    assert_bits_equal(to_numpy(codes, o_codes.dtype), o_codes, "codes")
     o_restored = O.dequantize(o_codes, o_scale, s, F)
-    assert_bits_equal(to_numpy(restored[pick.cuda()].contiguous(), F), o_restored, "restored")
+    assert_bits_equal(to_numpy(restored, F), o_restored, "restored")
+
+
+@pytest.mark.parametrize("name", ["q4_block32_bf16_14336x4096", "q8_tensor_bf16_14336x4096"])
+def test_batched_benchmark_step_matches_the_oracle_on_every_tensor(name):
+    """The call the benchmark times: eight distinct 14336 x 4096 tensors through qk_quantize_dynamic_batch and
+    qk_dequantize_batch (one launch each for the block scheme); all eight compared with the oracle in full."""
+    w = WORKLOADS[name]
+    s, elem = w.scheme, w.elem
+    F = NP_FLOAT[elem]
+    client = ComputeClient.current()
+    xs = [generate(w, "cuda", seed_offset=i) for i in range(8)]
+    codes = [torch.empty(s.packed_shape(x.shape), dtype=torch.int32, device="cuda") for x in xs]
+    scales = [torch.empty(s.scales_shape(x.shape), dtype=torch.float32, device="cuda") for x in xs]
+    outs = [torch.empty_like(x) for x in xs]
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    quantize.PreparedDynamicBatch(client, [H(t) for t in xs], [H(t) for t in codes], [H(t) for t in scales], s, elem, H(ws))()
+    dequantize.PreparedBatch(client, [H(t) for t in codes], [H(t) for t in outs], [H(t) for t in scales], s, elem)()
+    torch.cuda.synchronize()
+    for i in range(8):
+        o_codes, o_scale = O.quantize_dynamic(to_numpy(xs[i], F), s)
+        assert_bits_equal(to_numpy(scales[i], np.float32), o_scale, f"scales of tensor {i}")
+        assert_bits_equal(to_numpy(codes[i], np.uint32), o_codes, f"codes of tensor {i}")
+        assert_bits_equal(to_numpy(outs[i], F), O.dequantize(o_codes, o_scale, s, F), f"restored tensor {i}")
 
 
 def test_embedding_sized_tensor_q8_block128():

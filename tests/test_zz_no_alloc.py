@@ -1,8 +1,8 @@
 """`qk_quantize_dynamic_noalloc`, the entry point for callers that cannot allocate device memory
 (its scratch is a fixed array inside the library instead of a caller-provided workspace).
 
-Checked through the C ABI against `qk_quantize_dynamic` on the same inputs: the bits must be
-identical, on two calls in a row with different data (the second call finds the first call's
+Checked through the C ABI against `qk_quantize_dynamic` and against the CPU oracle on the same inputs: the
+bits must be identical, on two calls in a row with different data (the second call finds the first call's
 leftovers in the shared array and must not be affected by them).  Collected last on purpose, so a
 run that stops at the first failure has already exercised everything else.
 """
@@ -11,6 +11,7 @@ import pytest
 
 from cubek_b200 import ElemType, QuantLevel, QuantScheme, QuantStore, QuantValue, TensorHandleRef
 from cubek_b200 import _ffi
+from oracle import oracle as O
 from tests._cases import FLOATS, random_tensor
 from tests._util import NP_FLOAT, assert_bits_equal, code_dtype, elem_of, empty_device, to_device, to_numpy, workspace
 
@@ -61,6 +62,10 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(fname, scheme, sha
         assert want_status == 0 and status == 0, _ffi.strerror(status)
         assert_bits_equal(codes, want_codes, "codes")
         assert_bits_equal(scale, want_scale, "out_scale")
+        # and against the CPU oracle, so that the check does not rest on another CUDA path alone
+        o_codes, o_scale = O.quantize_dynamic(x, scheme)
+        assert_bits_equal(codes, o_codes, "codes vs oracle")
+        assert_bits_equal(scale, o_scale, "out_scale vs oracle")
 
 
 def test_noalloc_rejects_layouts_whose_staged_scales_do_not_fit():
