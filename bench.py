@@ -472,6 +472,28 @@ class ShardedSet:
 
         return run
 
+    def two_call(self):
+        """The reference-shaped flow, one tensor per call: ``compute_scales`` (the caller's half: absmax and the
+        scale formula, scales typed like the input) then ``launch_ref`` with those scales.  Returns the two
+        phases as callables over all local tensors, with their algorithmic bytes over all ranks.  One rank only
+        (a sharded per-tensor scale needs the exchange, which ``quantize_per_tensor_sharded`` does)."""
+        from cubek_b200 import TensorHandleRef, quantize
+        from cubek_b200.synthetic import TORCH_DTYPE
+
+        ctx, H = self.ctx, TensorHandleRef.from_torch
+        hx, hc, hs, _ = self.handles
+        given = [ctx.torch.empty(self.scheme.scales_shape(x.shape), dtype=TORCH_DTYPE[self.elem], device=ctx.dev) for x in self.xs]
+        hg = [H(t) for t in given]
+        self._given = given
+        scales = [quantize.PreparedScales(ctx.client, hx[i], hg[i], self.scheme, self.elem, H(self.ws)) for i in range(len(hx))]
+        quant = [quantize.PreparedRef(ctx.client, hx[i], hc[i], hg[i], hs[i], self.scheme, self.elem) for i in range(len(hx))]
+        n_in = sum(r * c for r, c in self.global_shapes) * self.elem.size
+        nscales = sum(t.numel() for t in given) * ctx.world
+        code_bytes = sum(r * c for r, c in self.global_shapes) * self.scheme.value.size_bits() // 8
+        return [("compute_scales", lambda: [c() for c in scales], n_in + nscales * self.elem.size),
+                ("quantize_given_scales", lambda: [c() for c in quant],
+                 n_in + nscales * self.elem.size + code_bytes + nscales * self.scheme.param.size)]
+
 
 def check_against_oracle(ctx: Ctx, sset: ShardedSet, rows_per_tensor=4, max_tensors=None):
     """Outside the timed region: whole rows of this rank's shards (first, last and random ones of every tensor)
@@ -674,6 +696,12 @@ def run_single_config(ctx: Ctx, args, workload, batch, headline):
     per_call()
     ctx.barrier()
     call_ms = ctx.max_over_ranks(ctx.time_steps(per_call, steps, flush))
+    two_call = {}
+    if ctx.world == 1:
+        for name, fn, nbytes in sset.two_call():
+            fn()
+            t = ctx.time_steps(fn, steps, flush)
+            two_call[name] = {"gbs_per_gpu": round(nbytes / t / 1e6, 1), "ms_per_step": round(t, 5)}
     peak, _ = measured_peak()
     summary = {
         "tensors_per_step": batch, "shape": list(workload.shape),
@@ -684,6 +712,7 @@ def run_single_config(ctx: Ctx, args, workload, batch, headline):
                      "frac_of_measured_per_gpu": round(total / call_ms / 1e6 / ctx.world / peak, 4),
                      "frac_of_spec_per_gpu": round(total / call_ms / 1e6 / ctx.world / SPEC_PEAK_GBS, 4)},
         "kernels": {k.split(".", 1)[1]: {"gbs_per_gpu": v["gbs_per_gpu"], "ms_per_step": v["ms_per_step"]} for k, v in table.items()},
+        "two_call_flow_per_tensor": two_call,
         "l2": "flushed between steps (read-only pass over 512 MB, outside the event pairs)" if flush
               else "per-rank inputs of a step exceed twice the L2",
         "parity_checked": parity["ok"],

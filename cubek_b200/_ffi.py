@@ -24,6 +24,8 @@ QK_ERR_NULL = 7
 QK_ERR_WORKSPACE = 8
 QK_ERR_TOO_LARGE = 9
 QK_ERR_NCCL = 10
+QK_ERR_TIMEOUT = 11
+QK_ERR_DEVICE = 12
 QK_ERR_CUDA = 1000
 
 # Status codes that stand for a `panic!` / `assert!` in the reference.
@@ -84,6 +86,7 @@ _SIGNATURES = {
     "qk_quantize_from_absmax_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.c_void_p, C.POINTER(QkScheme), C.c_int,
                                                         C.c_void_p]),
     "qk_allreduce_max_f32": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "qk_allreduce_max_f32_deadline": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int]),
     "qk_workspace_bytes": (C.c_size_t, []),
     "qk_workspace_bytes_for": (C.c_size_t, [C.POINTER(QkTensor), C.POINTER(QkScheme), C.c_int]),
     "qk_roundtrip_host": (C.c_int, [C.POINTER(QkTensor)] * 4 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
@@ -93,11 +96,20 @@ _SIGNATURES = {
     "qk_version": (C.c_char_p, []),
     "qk_launch_count": (C.c_uint64, []),
     "qk_device_error": (C.c_int, [C.POINTER(C.c_int)]),
+}
+
+# include/cubek_quant_b200_testing.h: hooks for tests and measurements, not part of the drop-in interface
+ALLREDUCE_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p, C.c_void_p)
+ASYNC_ERROR_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_int))
+STREAM_QUERY_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p)
+_TESTING_SIGNATURES = {
     "qk_set_tuning": (None, [C.c_int, C.c_int]),
     "qk_get_tuning": (C.c_int, [C.c_int]),
+    "qk_testing_set_collective_hooks": (None, [C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+TESTING_SYMBOLS = tuple(_TESTING_SIGNATURES)
 
 
 def lib() -> C.CDLL:
@@ -108,7 +120,7 @@ def lib() -> C.CDLL:
             raise OSError(f"{LIB_PATH} not found: build it with `python -m cubek_b200.build` "
                           "(there is no CPU fallback)")
         handle = C.CDLL(str(LIB_PATH))
-        for name, (res, args) in _SIGNATURES.items():
+        for name, (res, args) in {**_SIGNATURES, **_TESTING_SIGNATURES}.items():
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args

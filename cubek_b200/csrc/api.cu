@@ -9,15 +9,19 @@
 #include <cstring>
 #include <dlfcn.h>
 
+#include <chrono>
+#include <thread>
+
+#include "../../include/cubek_quant_b200_testing.h"
 #include "dequantize_kernels.cuh"
 #include "misc_kernels.cuh"
 #include "quantize_kernels.cuh"
 
 namespace qk {
 
-cudaError_t launch_quantize_f32(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_quantize_f16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
-cudaError_t launch_quantize_bf16(int, int, bool, bool, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_f32(int, int, bool, bool, int, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_f16(int, int, bool, bool, int, const QuantArgs &, const LaunchCfg &, cudaStream_t);
+cudaError_t launch_quantize_bf16(int, int, bool, bool, int, const QuantArgs &, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_f32(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_f16(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
 cudaError_t launch_block_scales_bf16(const void *, void *, long long, int, int, float, float, const RowStride &, const LaunchCfg &, cudaStream_t);
@@ -53,13 +57,13 @@ cudaError_t launch_quantize_tensor(int fdt, int kind, QuantTensorArgs &args, int
     }
 }
 
-cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, int sub, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_quantize_f32(kind, unit_bytes, dyn, clamp, args, cfg, stream);
-    case QK_F16: return launch_quantize_f16(kind, unit_bytes, dyn, clamp, args, cfg, stream);
-    case QK_BF16: return launch_quantize_bf16(kind, unit_bytes, dyn, clamp, args, cfg, stream);
+    case QK_F32: return launch_quantize_f32(kind, unit_bytes, dyn, clamp, sub, args, cfg, stream);
+    case QK_F16: return launch_quantize_f16(kind, unit_bytes, dyn, clamp, sub, args, cfg, stream);
+    case QK_BF16: return launch_quantize_bf16(kind, unit_bytes, dyn, clamp, sub, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -381,9 +385,13 @@ static bool aligned(const void *p, unsigned a) { return (reinterpret_cast<uintpt
 // last dim, contiguous scales and vector-aligned bases.  Picks the unit (64 bytes when blocks
 // and the tensor allow, else the smallest unit of the kind); returns log2(units per block), -1
 // for per tensor, or -2 when the call has to take the layout-general kernels.
+// `*sub` (optional) is set to the blocks per unit: 2 when the fused form may run 16-bit blocks of 32 bytes as halves
+// of 64-byte units (f32 params, scales 8-byte aligned), else 1.
 static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, const QkTensor *out,
-                            const QkTensor *scale, const QkTensor *out_scale, int *unit_bytes)
+                            const QkTensor *scale, const QkTensor *out_scale, int *unit_bytes, int *sub = nullptr,
+                            bool fused = false, int param = QK_F32)
 {
+    if (sub) *sub = 1;
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     const int esz = dtype_size(fdt);
     if (!aligned(in->ptr, 16)) return -2;
@@ -410,6 +418,11 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
         if (!aligned(out->ptr, out_align)) continue;
         *unit_bytes = ub;
         if (g.per_tensor) return -1;
+        if (sub && fused && ub == 64 && esz == 2 && U == 2 * g.B && !g.blocks_2d && !strided_rows && param == QK_F32 &&
+            32 >= min_unit_bytes(fdt, g.kind) && out_scale && aligned(out_scale->ptr, 8)) {
+            *sub = 2;
+            return 0;
+        }
         if (g.B % U != 0) continue;
         const int lg = log2_exact(g.B / U);
         if (lg < 0 || (lg > 5 && !g.blocks_2d)) continue;
@@ -557,7 +570,7 @@ static int absmax_into_cells(int count, const QkTensor *inputs, const bool *skip
 // specialisation and geometry go out as one launch (up to QK_MAX_BATCH tensors).
 struct QuantBatch {
     QuantArgs a;
-    int fdt = -1, kind = -1, unit_bytes = 0;
+    int fdt = -1, kind = -1, unit_bytes = 0, sub = 1;
     bool dyn = false, clamp = false;
     QuantBatch() { a.ntensors = 0; a.nunits = 0; a.absmax = nullptr; a.b2.enabled = 0; a.rs.enabled = 0; a.tr.enabled = 0; }
 };
@@ -571,7 +584,7 @@ static int flush_quant(QuantBatch &b, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (b.a.ntensors == 0) return QK_OK;
     count_launch();
-    const cudaError_t e = launch_quantize(b.fdt, b.kind, b.unit_bytes, b.dyn, b.clamp, b.a, cfg, stream);
+    const cudaError_t e = launch_quantize(b.fdt, b.kind, b.unit_bytes, b.dyn, b.clamp, b.sub, b.a, cfg, stream);
     b.a.ntensors = 0;
     b.a.nunits = 0;
     b.a.absmax = nullptr;
@@ -947,25 +960,100 @@ int qk_quantize_from_absmax(const QkTensor *input, const QkTensor *output, const
 }
 
 // ---- NCCL, resolved at run time so that the library has no link-time NCCL dependency -----------
+}  // extern "C"
+
+namespace {
+
+typedef int (*allreduce_fn)(const void *, void *, size_t, int, int, void *, void *);
+typedef int (*async_error_fn)(void *, int *);
+typedef int (*stream_query_fn)(void *);
+
+std::atomic<allreduce_fn> g_allreduce{nullptr};
+std::atomic<async_error_fn> g_async_error{nullptr};
+std::atomic<stream_query_fn> g_stream_query{nullptr};
+std::atomic<bool> g_hooks_set{false};
+
+int real_stream_query(void *stream) { return (int)cudaStreamQuery(static_cast<cudaStream_t>(stream)); }
+
+void *nccl_symbol(const char *name)
+{
+    void *sym = dlsym(RTLD_DEFAULT, name);
+    if (!sym) {
+        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h) sym = dlsym(h, name);
+    }
+    return sym;
+}
+
+bool resolve_collectives()
+{
+    if (g_allreduce.load() && g_async_error.load() && g_stream_query.load()) return true;
+    if (g_hooks_set.load()) return false;   // hooks are installed as a complete set
+    void *ar = nccl_symbol("ncclAllReduce");
+    void *ae = nccl_symbol("ncclCommGetAsyncError");
+    if (!ar || !ae) return false;
+    g_allreduce.store(reinterpret_cast<allreduce_fn>(ar));
+    g_async_error.store(reinterpret_cast<async_error_fn>(ae));
+    g_stream_query.store(real_stream_query);
+    return true;
+}
+
+constexpr int kNcclSuccess = 0, kNcclInProgress = 7;   // nccl.h: ncclResult_t
+constexpr int kCudaNotReady = 600;                     // cudaErrorNotReady
+
+// Enqueue, then (wait_done) poll until the stream has drained.  `timeout_ms` bounds every wait.
+int allreduce_max(float *buf, size_t count, void *comm, void *stream, int timeout_ms, bool wait_done)
+{
+    if (!buf || !comm) return QK_ERR_NULL;
+    if (!resolve_collectives()) return QK_ERR_NCCL;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+    const auto expired = [&] { return std::chrono::steady_clock::now() >= deadline; };
+    // ncclFloat32 = 7, ncclMax = 2 (nccl.h: ncclDataType_t, ncclRedOp_t)
+    int rc = g_allreduce.load()(buf, buf, count, 7, 2, comm, stream);
+    while (rc == kNcclInProgress) {   // non-blocking communicator: the enqueue itself is still pending
+        int state = kNcclSuccess;
+        if (g_async_error.load()(comm, &state) != kNcclSuccess) return QK_ERR_NCCL;
+        if (state == kNcclSuccess) { rc = kNcclSuccess; break; }
+        if (state != kNcclInProgress) return QK_ERR_NCCL;
+        if (expired()) return QK_ERR_TIMEOUT;
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (rc != kNcclSuccess) return QK_ERR_NCCL;
+    if (!wait_done) return QK_OK;
+    for (;;) {
+        int state = kNcclSuccess;
+        if (g_async_error.load()(comm, &state) != kNcclSuccess) return QK_ERR_NCCL;
+        if (state != kNcclSuccess && state != kNcclInProgress) return QK_ERR_NCCL;
+        const int q = g_stream_query.load()(stream);
+        if (q == 0) return QK_OK;
+        if (q != kCudaNotReady) return QK_ERR_CUDA + q;
+        if (expired()) return QK_ERR_TIMEOUT;
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
 int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream)
 {
-    typedef int (*allreduce_fn)(const void *, void *, size_t, int, int, void *, cudaStream_t);
-    static std::atomic<allreduce_fn> cached{nullptr};
-    allreduce_fn fn = cached.load();
-    if (!fn) {
-        void *sym = dlsym(RTLD_DEFAULT, "ncclAllReduce");
-        if (!sym) {
-            void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-            if (h) sym = dlsym(h, "ncclAllReduce");
-        }
-        if (!sym) return QK_ERR_NCCL;
-        fn = reinterpret_cast<allreduce_fn>(sym);
-        cached.store(fn);
-    }
-    if (!buf || !comm) return QK_ERR_NULL;
-    // ncclFloat32 = 7, ncclMax = 2 (nccl.h: ncclDataType_t, ncclRedOp_t)
-    const int rc = fn(buf, buf, count, 7, 2, comm, static_cast<cudaStream_t>(stream));
-    return rc == 0 ? QK_OK : QK_ERR_NCCL;
+    return allreduce_max(buf, count, comm, stream, 10000, false);
+}
+
+int qk_allreduce_max_f32_deadline(float *buf, size_t count, void *comm, void *stream, int timeout_ms)
+{
+    return allreduce_max(buf, count, comm, stream, timeout_ms, true);
+}
+
+void qk_testing_set_collective_hooks(int (*allreduce)(const void *, void *, size_t, int, int, void *, void *),
+                                     int (*async_error)(void *, int *), int (*stream_query)(void *))
+{
+    const bool set = allreduce && async_error && stream_query;
+    g_hooks_set.store(set);
+    g_allreduce.store(set ? allreduce : nullptr);
+    g_async_error.store(set ? async_error : nullptr);
+    g_stream_query.store(set ? stream_query : nullptr);
 }
 
 const char *qk_strerror(int status)
@@ -981,7 +1069,9 @@ const char *qk_strerror(int status)
     case QK_ERR_NULL: return "null argument";
     case QK_ERR_WORKSPACE: return "workspace missing or too small";
     case QK_ERR_TOO_LARGE: return "size beyond what this entry point supports";
-    case QK_ERR_NCCL: return "NCCL call failed or NCCL not found";
+    case QK_ERR_NCCL: return "NCCL call failed, communicator in error, or NCCL not found";
+    case QK_ERR_TIMEOUT: return "deadline passed before the collective completed";
+    case QK_ERR_DEVICE: return "a kernel gave up on a bounded wait and left its output unwritten";
     default:
         if (status >= QK_ERR_CUDA) return cudaGetErrorString((cudaError_t)(status - QK_ERR_CUDA));
         return "unknown status";
@@ -997,7 +1087,9 @@ int qk_device_error(int *flag_out)
     if (!flag_out) return QK_ERR_NULL;
     int *p = stage_error_flag();
     if (!p) return QK_ERR_CUDA;
-    const cudaError_t e = cudaMemcpy(flag_out, p, sizeof(int), cudaMemcpyDeviceToHost);   // synchronises
+    cudaError_t e = cudaMemcpy(flag_out, p, sizeof(int), cudaMemcpyDeviceToHost);   // synchronises
+    if (e != cudaSuccess) return cuda_status(e);
+    if (*flag_out != 0) e = cudaMemset(p, 0, sizeof(int));                          // read and clear
     return cuda_status(e);
 }
 
@@ -1039,8 +1131,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     float lo, hi;
     qk_value_range(scheme->value, &lo, &hi);
     const LaunchCfg cfg = current_cfg();
-    int unit_bytes = 0;
-    const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale, &unit_bytes);
+    int unit_bytes = 0, sub = 1;
+    const int lg = fast_quantize_lg(g, input_dtype, input, output, scale, out_scale, &unit_bytes, &sub, dynamic,
+                                    scheme->param);
     // Tiles over two dims cannot be reduced inside one thread group: the fused form first writes the
     // tile scales (one warp per tile) into the workspace, then runs the given-scale kernel.
     const void *tile_scales = nullptr;
@@ -1072,7 +1165,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         const bool joins = !g.blocks_2d && !b.a.b2.enabled &&   // tile geometry is per launch
                            !strided_rows && !b.a.rs.enabled &&  // and so is a row stride
                            b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == input_dtype &&
-                           b.kind == g.kind && b.unit_bytes == unit_bytes && b.dyn == dynamic && b.clamp == clamp &&
+                           b.kind == g.kind && b.unit_bytes == unit_bytes && b.sub == sub && b.dyn == dynamic && b.clamp == clamp &&
                            b.a.lg_units_per_block == lg && b.a.param == scheme->param && b.a.lo == lo && b.a.hi == hi &&
                            b.a.force_exact == cfg.force_exact &&
                            ((absmax == nullptr && b.a.absmax == nullptr) ||
@@ -1082,6 +1175,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             b.fdt = input_dtype;
             b.kind = g.kind;
             b.unit_bytes = unit_bytes;
+            b.sub = sub;
             b.dyn = dynamic;
             b.clamp = clamp;
             b.a.absmax = absmax;
@@ -1150,8 +1244,8 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
             one.a.t[0].out_scale = out_scale->ptr;
             one.a.t[0].unit_end = one.a.nunits;
             one.a.t[0].tile_end = 0;
-            const bool symmetric = (lo == -hi);
-            const bool clamp = need_clamp(input_dtype, g.kind, dynamic, symmetric, scheme->param);
+            // always clamped here: the clamp also keeps a NaN element inside its own code
+            const bool clamp = true;
             count_launch();
             return cuda_status(launch_quantize_transposed(input_dtype, g.kind, ub, dynamic, clamp, one.a, cfg, stream));
         }

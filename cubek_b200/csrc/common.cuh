@@ -167,6 +167,14 @@ template <int FDT> __device__ __forceinline__ void widen16(const Vec16 &v, float
     }
 }
 
+// Maximum of three f32 in one instruction (sm_100); a NaN operand is ignored, like fmaxf.
+__device__ __forceinline__ float fmax3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // ---- scale arithmetic -----------------------------------------------------------------
 
 // clamp(round(t)) with round-half-to-even; a NaN quotient (0/0) gives code 0.
@@ -244,6 +252,7 @@ __device__ __forceinline__ void pdl_entry()
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), int grid, int threads, cudaStream_t stream, bool pdl,
                                         Args... args)
@@ -319,6 +328,44 @@ struct Transposed {
     long long ld;
     unsigned units_per_row;
 };
+
+// ---- work split ---------------------------------------------------------------------------------
+// The persistent streaming kernels (one wave of CTAs, many passes each) walk their units in passes of
+// gridDim.x * 256 * UNR consecutive units: CTA b takes the b-th run of 256 * UNR units of a pass, so that at any
+// moment the grid reads one contiguous window of memory.  The passes that are full for EVERY CTA run in a loop
+// without bounds checks; what is left (less than one pass) is dealt out in rows of 32 units, one row per warp and
+// round, over all warps of the grid.
+struct PassSplit {
+    long long full_passes;   // passes in which every thread of the grid has UNR valid units
+};
+static inline PassSplit make_pass_split(long long nunits, long long grid, int threads, int unr)
+{
+    PassSplit s;
+    s.full_passes = nunits / (grid * threads * unr);
+    return s;
+}
+// Calls `pass(idx, true)` once per full pass with this thread's UNR unit indices, then `pass(idx, false)` once with
+// its units of the remainder (units past `nunits` included) unless its whole row of the first round of the
+// remainder lies past the end.  The two call sites give two inlined copies of the body: with the literal `true`
+// the one in the loop keeps no bounds checks at all.
+#define QK_WALK_PASSES(FULL_PASSES, NUNITS, UNR, PASS)                                                              \
+    do {                                                                                                            \
+        const long long qk_per_cta = (long long)blockDim.x * (UNR);                                                 \
+        const long long qk_per_pass = qk_per_cta * gridDim.x;                                                       \
+        long long qk_base = (long long)blockIdx.x * qk_per_cta + threadIdx.x;                                       \
+        for (long long qk_p = 0; qk_p < (FULL_PASSES); ++qk_p, qk_base += qk_per_pass) {                            \
+            long long qk_idx[UNR];                                                                                  \
+            _Pragma("unroll") for (int qk_k = 0; qk_k < (UNR); ++qk_k) qk_idx[qk_k] = qk_base + qk_k * blockDim.x;  \
+            PASS(qk_idx, true);                                                                                     \
+        }                                                                                                           \
+        const long long qk_rest = (FULL_PASSES) * qk_per_pass + (long long)blockIdx.x * blockDim.x + threadIdx.x;   \
+        if (qk_rest - (threadIdx.x & 31) < (NUNITS)) {                                                              \
+            long long qk_idx[UNR];                                                                                  \
+            _Pragma("unroll") for (int qk_k = 0; qk_k < (UNR); ++qk_k)                                              \
+                qk_idx[qk_k] = qk_rest + (long long)qk_k * gridDim.x * blockDim.x;                                  \
+            PASS(qk_idx, false);                                                                                    \
+        }                                                                                                           \
+    } while (0)
 
 // ---- launch bookkeeping -----------------------------------------------------------------
 

@@ -6,8 +6,13 @@
 // crates/cubek-quant/tests/suite/symmetric.rs:32-127), as one entry point.
 #include <mutex>
 
+#include "../../include/cubek_quant_b200_testing.h"
 #include "common.cuh"
 #include "misc_kernels.cuh"
+
+namespace qk {
+int *stage_error_flag();   // device address of the flag the staged kernels raise (api.cu)
+}
 
 namespace {
 
@@ -225,6 +230,18 @@ int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTens
     for (int i = 0; i < slots; ++i) {
         e = cudaStreamSynchronize(streams[i]);
         if (e != cudaSuccess && status == QK_OK) status = QK_ERR_CUDA + (int)e;
+    }
+    // The results are claimed to be in host memory: a kernel that gave up on a bounded wait must not pass silently.
+    // (Read on one of the internal streams: a copy on the default stream would wait for other threads' work.)
+    if (status == QK_OK) {
+        int flag = 0;
+        int *dev_flag = qk::stage_error_flag();
+        if (dev_flag) {
+            e = cudaMemcpyAsync(&flag, dev_flag, sizeof(int), cudaMemcpyDeviceToHost, streams[0]);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(streams[0]);
+            if (e != cudaSuccess) status = QK_ERR_CUDA + (int)e;
+            else if (flag != 0) status = QK_ERR_DEVICE;
+        }
     }
     return status;
 }

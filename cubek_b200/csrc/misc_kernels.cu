@@ -27,7 +27,8 @@ template <typename Kernel> static int resident_ctas(Kernel kernel)
 // absmax
 // ---------------------------------------------------------------------------------------
 template <int FDT>
-__global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long n, unsigned int *cell, const RowStride rs)
+__global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long n, unsigned int *cell, const RowStride rs,
+                                                     const PassSplit split)
 {
     constexpr int PER = FInfo<FDT>::PER16;
     constexpr int UNR = 4;
@@ -36,28 +37,26 @@ __global__ void __launch_bounds__(256) absmax_kernel(const void *in_, long long 
     float amax = 0.0f;
     pdl_entry();
 
-    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
-    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nchunks;
-         base += stride) {
+    auto pass = [&](const long long (&idx)[UNR], const bool full) {
         Vec16 raw[UNR];
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            long long offset = idx * 16;
+            long long offset = idx[k] * 16;
             if (rs.enabled) {   // rows of whole 16-byte chunks, `row_bytes` apart
-                const unsigned row = fastdiv((unsigned)idx, rs.units_per_row);
-                offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx - row * rs.units_per_row.div) * 16;
+                const unsigned row = fastdiv((unsigned)idx[k], rs.units_per_row);
+                offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx[k] - row * rs.units_per_row.div) * 16;
             }
-            raw[k] = (idx < nchunks) ? ldg128_stream(in + offset) : Vec16{{0u, 0u, 0u, 0u}};
+            raw[k] = (full || idx[k] < nchunks) ? ldg128_stream(in + offset) : Vec16{{0u, 0u, 0u, 0u}};
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
             float x[PER];
             widen16<FDT>(raw[k], x);
 #pragma unroll
-            for (int i = 0; i < PER; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            for (int i = 0; i < PER; i += 2) amax = fmax3(amax, fabsf(x[i]), fabsf(x[i + 1]));
         }
-    }
+    };
+    QK_WALK_PASSES(split.full_passes, nchunks, UNR, pass);
     // ragged tail (fewer than PER elements)
     if (blockIdx.x == 0 && threadIdx.x == 0)
         for (long long i = nchunks * PER; i < n; ++i) amax = fmaxf(amax, fabsf(load_dyn(in_, FDT, i)));
@@ -234,10 +233,11 @@ cudaError_t launch_absmax(int fdt, const void *in, long long n, unsigned int *ce
     if (wave.ctas_per_sm <= 0) wave.ctas_per_sm = occ[fdt == QK_F32 ? 0 : fdt == QK_F16 ? 1 : 2];
     const int grid = grid_for(n / per + 1, threads * 4, wave);
     const bool pdl = cfg.pdl != 0;
+    const PassSplit split = make_pass_split(n / per, grid, threads, 4);
     switch (fdt) {
-    case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell, rs);
-    case QK_F16: return launch_kernel(absmax_kernel<QK_F16>, grid, threads, stream, pdl, in, n, cell, rs);
-    default: return launch_kernel(absmax_kernel<QK_BF16>, grid, threads, stream, pdl, in, n, cell, rs);
+    case QK_F32: return launch_kernel(absmax_kernel<QK_F32>, grid, threads, stream, pdl, in, n, cell, rs, split);
+    case QK_F16: return launch_kernel(absmax_kernel<QK_F16>, grid, threads, stream, pdl, in, n, cell, rs, split);
+    default: return launch_kernel(absmax_kernel<QK_BF16>, grid, threads, stream, pdl, in, n, cell, rs, split);
     }
 }
 

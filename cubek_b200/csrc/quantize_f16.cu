@@ -2,10 +2,10 @@
 #include "quantize_inst.cuh"
 
 namespace qk {
-cudaError_t launch_quantize_f16(int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+cudaError_t launch_quantize_f16(int kind, int unit_bytes, bool dyn, bool clamp, int sub, const QuantArgs &args,
                                const LaunchCfg &cfg, cudaStream_t stream)
 {
-    return launch_quantize_t<QK_F16>(kind, unit_bytes, dyn, clamp, args, cfg, stream);
+    return launch_quantize_t<QK_F16>(kind, unit_bytes, dyn, clamp, sub, args, cfg, stream);
 }
 cudaError_t launch_block_scales_f16(const void *in, void *scale_out, long long nunits, int unit_bytes, int lg,
                                      float range, float inv_range, const RowStride &rs, const LaunchCfg &cfg,

@@ -55,6 +55,7 @@ struct QuantArgs {
     float inv_range;         // RN(1 / range), computed on the host
     int force_exact;         // 1: reference arithmetic for every unit
     int aligned32;           // every input and output base is 32-byte aligned (256-bit accesses allowed)
+    PassSplit split;         // full passes of the grid (filled by the launcher once the grid is known)
 };
 
 // A unit: UB bytes of input handled by one thread.
@@ -130,6 +131,20 @@ template <int FDT> __device__ __forceinline__ uint32_t h2_pack(float lo, float h
 // A small integer-valued constant as packed F x2 (both halves).
 template <int FDT> __device__ __forceinline__ uint32_t h2_const(float v) { return h2_pack<FDT>(v, v); }
 
+// Two f32 products with one packed instruction (mul.rn.f32x2: one issue slot for both lanes' pair).
+__device__ __forceinline__ void mul2(float a0, float a1, float b, float &o0, float &o1)
+{
+#ifdef QK_NO_F32X2
+    o0 = a0 * b;
+    o1 = a1 * b;
+#else
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmul.rn.f32x2 rc, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(o0), "=f"(o1)
+        : "f"(a0), "f"(a1), "f"(b));
+#endif
+}
+
 template <int FDT> __device__ __forceinline__ float h_lo_to_f32(uint32_t p)
 {
     if constexpr (FDT == QK_BF16) return bf16_lo_to_f32(p);
@@ -154,7 +169,7 @@ template <int FDT, int RAW> __device__ __forceinline__ float unit_absmax(const u
     if constexpr (FDT == QK_F32) {
         float m = 0.0f;
 #pragma unroll
-        for (int i = 0; i < RAW; ++i) m = fmaxf(m, fabsf(__uint_as_float(raw[i])));
+        for (int i = 0; i < RAW; i += 2) m = fmax3(m, fabsf(__uint_as_float(raw[i])), fabsf(__uint_as_float(raw[i + 1])));
         return m;
     } else {
         uint32_t m = raw[0];
@@ -294,14 +309,19 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
             float q0 = x * r;
             if constexpr (!BOUNDED) q0 = fminf(fmaxf(q0, lo - 2.0f), hi + 2.0f);
             const float t = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
-            c[i] = CLAMP ? fminf(fmaxf(t, lo), hi) : t;
+            // The 4- and 2-bit packs add shifted bit patterns: a NaN would carry into the fields of its neighbours, so
+            // the unclamped form still takes the minimum with the upper bound (which a NaN does not survive).
+            constexpr bool ADDS = (KIND == KIND_PACK4 || KIND == KIND_PACK2);
+            c[i] = CLAMP ? fminf(fmaxf(t, lo), hi) : (ADDS ? fminf(t, hi) : t);
         }
         pack_from_f32<KIND, U>(c, outw);
     } else if constexpr (KIND == KIND_E4M3 || KIND == KIND_E5M2) {
         float c[U];
 #pragma unroll
         for (int i = 0; i < U; i += 2) {
-            const uint32_t p = h2_pack<FDT>(raw_elem<FDT>(raw, i) * r, raw_elem<FDT>(raw, i + 1) * r);
+            float q0, q1;
+            mul2(raw_elem<FDT>(raw, i), raw_elem<FDT>(raw, i + 1), r, q0, q1);
+            const uint32_t p = h2_pack<FDT>(q0, q1);
             c[i] = fminf(fmaxf(h_lo_to_f32<FDT>(p), lo), hi);
             c[i + 1] = fminf(fmaxf(h_hi_to_f32<FDT>(p), lo), hi);
         }
@@ -321,8 +341,11 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
             for (int j = 0; j < EPW / 2; ++j) {
                 const int e0 = w * EPW + (SPLIT_PAIRS ? j : 2 * j);
                 const int e1 = w * EPW + (SPLIT_PAIRS ? j + EPW / 2 : 2 * j + 1);
-                uint32_t q = h2_pack<FDT>(raw_elem<FDT>(raw, e0) * r, raw_elem<FDT>(raw, e1) * r);
+                float q0, q1;
+                mul2(raw_elem<FDT>(raw, e0), raw_elem<FDT>(raw, e1), r, q0, q1);
+                uint32_t q = h2_pack<FDT>(q0, q1);
                 if constexpr (CLAMP) q = h2_min<FDT>(h2_max<FDT>(q, lo2), hi2);
+                else if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2) q = h2_min<FDT>(q, hi2);   // NaN -> hi, see above
                 p[j] = q;
             }
             if constexpr (KIND == KIND_PACK4 || KIND == KIND_PACK2) {
@@ -440,13 +463,18 @@ template <int OW> __device__ __forceinline__ void store_words(uint32_t *dst, con
 
 // Scale of a fused unit: absmax of its block (the unit's own registers, then the lanes that share the
 // block: aligned runs of 2^lg lanes; every lane of the warp takes part), then the scale formula.
-template <int FDT, int RAW>
+// LG0: the block is the unit (lg == 0 known at compile time): no shuffle rounds, no tests for them.
+// NaN elements do not take part (maxima return the other operand), as in the reference's MaxAbs
+// (crates/cubek-reduce/src/instructions/maxabs.rs:62-63).
+template <int FDT, int RAW, bool LG0 = false>
 __device__ __forceinline__ float fused_unit_scale(const uint32_t *raw, int lg, float range, float inv_range)
 {
     float amax = unit_absmax<FDT, RAW>(raw);
+    if constexpr (!LG0) {
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1)
-        if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        for (int m = 1; m < 32; m <<= 1)
+            if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    }
     return round_to<FDT>(div_by_range(2.0f * amax, range, inv_range));
 }
 
@@ -461,20 +489,34 @@ __device__ __forceinline__ float tensor_unit_scale(const QuantArgs &a, const Qua
 
 // write_scale, quantize, store: the scale is cast to the param type, stored by the unit that starts
 // the block (unit 0 for per tensor), and that value cast back to F is the divisor
-// (crates/cubek-quant/src/quantize.rs:83-98).
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
-__device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTensor &T, const uint32_t *raw, float scale_f,
-                                            long long sidx, bool starts, long long li, bool valid, bool aligned32)
+// (crates/cubek-quant/src/quantize.rs:83-98).  SUB = 2: the unit holds two blocks (halves of the unit), each
+// with its own scale; `sidx` is then the index of the first of the two (f32 params, 8-byte aligned scales).
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1>
+__device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTensor &T, const uint32_t *raw,
+                                            const float *scale_f, long long sidx, bool starts, long long li, bool valid,
+                                            bool aligned32)
 {
     constexpr int OW = UnitT<FDT, KIND, UB>::OW;
-    const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
-    const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
-    if (valid && starts) store_dyn(T.out_scale, a.param, sidx, s_fs);
+    constexpr int RAW = UnitT<FDT, KIND, UB>::RAW;
+    static_assert(SUB == 1 || (SUB == 2 && OW % 2 == 0), "a half unit must fill whole output words");
+    float s_fs[SUB], s[SUB];
+#pragma unroll
+    for (int j = 0; j < SUB; ++j) {
+        s_fs[j] = (a.param == QK_F32) ? scale_f[j] : round_to_dyn(a.param, scale_f[j]);
+        s[j] = (a.param == QK_F32) ? scale_f[j] : round_to<FDT>(s_fs[j]);
+    }
+    if (valid && starts) {
+        if constexpr (SUB == 1) store_dyn(T.out_scale, a.param, sidx, s_fs[0]);
+        else *reinterpret_cast<float2 *>(static_cast<float *>(T.out_scale) + sidx) = make_float2(s_fs[0], s_fs[1]);
+    }
     uint32_t w[OW];
-    if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s))
-        quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw, s, a.lo, a.hi, w);
-    else
-        quantize_unit_exact<FDT, KIND, UB>(raw, s, a.lo, a.hi, w);
+#pragma unroll
+    for (int j = 0; j < SUB; ++j) {
+        if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s[j]))
+            quantize_unit_fast<FDT, KIND, UB / SUB, CLAMP, DYN>(raw + j * (RAW / SUB), s[j], a.lo, a.hi, w + j * (OW / SUB));
+        else
+            quantize_unit_exact<FDT, KIND, UB / SUB>(raw + j * (RAW / SUB), s[j], a.lo, a.hi, w + j * (OW / SUB));
+    }
     if (valid) store_words<OW>(static_cast<uint32_t *>(T.out) + li * OW, w, aligned32);
 }
 
@@ -482,26 +524,38 @@ __device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTenso
 // The kernel.  DYN = true: scale from the block's own absmax (one pass, fused).
 // DYN = false: scale given (tensor of F, one per block) or derived from a device absmax.
 // -------------------------------------------------------------------------------------
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP>
-__global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
+// Resident CTAs per SM the register allocation must allow: 3 (at most 85 registers), 4 for the two-blocks-per-unit
+// form, which fits 64 registers without spilling.
+#ifndef QK_GIVEN_MIN_CTAS
+#define QK_GIVEN_MIN_CTAS 3
+#endif
+#ifndef QK_SUB2_MIN_CTAS
+#define QK_SUB2_MIN_CTAS 4
+#endif
+#define QK_MIN_CTAS(DYN, SUB) ((SUB) == 2 ? QK_SUB2_MIN_CTAS : ((DYN) ? 3 : QK_GIVEN_MIN_CTAS))
+// SUB = 2 (fused form only): two blocks per unit.  LG0: one block per unit, known at compile time.
+// Units are walked in grid-wide passes (see PassSplit).
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false>
+__global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(const QuantArgs a)
 {
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
-    constexpr int OW = UT::OW;
     constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread (128 bytes; 64 for 16-byte units)
     using F = typename ElemOf<FDT>::type;
+    static_assert(SUB == 1 || DYN, "two blocks per unit: fused form only");
 
     const bool aligned32 = a.aligned32 != 0;
-    const int lg = a.lg_units_per_block;
+    const int lg = (LG0 || SUB == 2) ? 0 : a.lg_units_per_block;
     pdl_entry();
 
     int ti = 0;                 // tensor of the batch this thread is in (only ever moves forward)
     int scale_ti = -1;          // tensor `tensor_scale` belongs to
     float tensor_scale = 0.0f;  // per tensor: one scale for the whole tensor
 
-    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
-    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < a.nunits;
-         base += stride) {
+    // One pass over UNR units of this thread.  `full`: all of them exist.  Otherwise a unit may lie past the end
+    // (it is loaded as zeros and stores nothing), and rows of 32 units that lie past the end entirely are skipped
+    // by their whole warp.
+    auto pass = [&](const long long (&idx)[UNR], const bool full) {
         uint32_t raw[UNR][RAW];
         int tk[UNR];
         long long lidx[UNR];
@@ -511,17 +565,15 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
         long long given_idx[UNR];
         bool given_starts[UNR];
         const bool block_scales_given = !DYN && (lg >= 0 || a.b2.enabled);
-        const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
             given[k] = 1.0f;
             given_idx[k] = 0;
             given_starts[k] = false;
-            if (full || idx < a.nunits) {
-                while (ti + 1 < a.ntensors && idx >= a.t[ti].unit_end) ++ti;
+            if (full || idx[k] < a.nunits) {
+                while (ti + 1 < a.ntensors && idx[k] >= a.t[ti].unit_end) ++ti;
                 tk[k] = ti;
-                lidx[k] = idx - (ti ? a.t[ti - 1].unit_end : 0);
+                lidx[k] = idx[k] - (ti ? a.t[ti - 1].unit_end : 0);
                 long long offset = lidx[k] * UB;
                 if (a.rs.enabled) {
                     const unsigned row = fastdiv((unsigned)lidx[k], a.rs.units_per_row);
@@ -549,33 +601,40 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantArgs a)
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            const bool valid = full || idx < a.nunits;
+            if (!full && idx[k] - (threadIdx.x & 31) >= a.nunits) continue;   // the whole row lies past the end
+            const bool valid = full || idx[k] < a.nunits;
             const QuantTensor &T = a.t[tk[k]];
             const long long li = lidx[k];
 
-            float scale_f;
+            float scale_f[SUB];
             long long sidx = 0;      // index of the unit's scale
             bool starts = false;     // the unit is the first of its block
-            if constexpr (DYN) {
-                sidx = li >> lg;
-                starts = (li & ((1ll << lg) - 1)) == 0;
-                scale_f = fused_unit_scale<FDT, RAW>(raw[k], lg, a.range, a.inv_range);
+            if constexpr (DYN && SUB == 2) {
+                sidx = 2 * li;
+                starts = true;
+                scale_f[0] = fused_unit_scale<FDT, RAW / 2, true>(raw[k], 0, a.range, a.inv_range);
+                scale_f[1] = fused_unit_scale<FDT, RAW / 2, true>(raw[k] + RAW / 2, 0, a.range, a.inv_range);
+            } else if constexpr (DYN) {
+                sidx = LG0 ? li : (li >> lg);
+                starts = LG0 ? true : ((li & ((1ll << lg) - 1)) == 0);
+                scale_f[0] = fused_unit_scale<FDT, RAW, LG0>(raw[k], lg, a.range, a.inv_range);
             } else if (lg < 0 && !a.b2.enabled) {
                 if (scale_ti != tk[k]) {
                     scale_ti = tk[k];
                     tensor_scale = tensor_unit_scale<FDT>(a, T, scale_ti);
                 }
-                scale_f = tensor_scale;
+                scale_f[0] = tensor_scale;
                 starts = (li == 0);
             } else {
                 sidx = given_idx[k];
                 starts = given_starts[k];
-                scale_f = given[k];
+                scale_f[0] = given[k];
             }
-            finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
+            finish_unit<FDT, KIND, UB, DYN, CLAMP, SUB>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
         }
-    }
+    };
+
+    QK_WALK_PASSES(a.split.full_passes, a.nunits, UNR, pass);
 }
 
 // -------------------------------------------------------------------------------------
@@ -633,7 +692,6 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
 {
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
-    constexpr int OW = UT::OW;
     constexpr int UPT = QK_TILE_BYTES / (256 * UB);   // units per thread per tile: 1, 2 or 4
     constexpr int TILE_UNITS = 256 * UPT;
     using F = typename ElemOf<FDT>::type;
@@ -714,19 +772,19 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
         for (int k = 0; k < UPT; ++k) {
             const long long li = u0 + k * 256 + threadIdx.x;
             const bool valid = li < nunits_t;
-            float scale_f;
+            float scale_f[1];
             long long sidx = 0;
             bool starts = false;
             if constexpr (DYN) {
                 sidx = li >> lg;
                 starts = (li & ((1ll << lg) - 1)) == 0;
-                scale_f = fused_unit_scale<FDT, RAW>(raw[k], lg, a.range, a.inv_range);
+                scale_f[0] = fused_unit_scale<FDT, RAW>(raw[k], lg, a.range, a.inv_range);
             } else if (lg < 0 && !a.b2.enabled) {
                 if (scale_ti != ti) {
                     scale_ti = ti;
                     tensor_scale = tensor_unit_scale<FDT>(a, T, ti);
                 }
-                scale_f = tensor_scale;
+                scale_f[0] = tensor_scale;
                 starts = (li == 0);
             } else {
                 if (a.b2.enabled) {
@@ -735,7 +793,7 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
                     sidx = li >> lg;
                     starts = (li & ((1ll << lg) - 1)) == 0;
                 }
-                scale_f = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
+                scale_f[0] = valid ? static_cast<float>(static_cast<const F *>(T.scale_in)[sidx]) : 1.0f;
             }
             finish_unit<FDT, KIND, UB, DYN, CLAMP>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
         }
@@ -852,7 +910,7 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
         for (int k = 0; k < UNR; ++k) {
             const long long idx = base + (long long)k * blockDim.x;
             uint32_t w[OW];
-            if (fast) quantize_unit_fast<FDT, KIND, UB, true, false>(last[k], s, a.lo, a.hi, w);
+            if (fast) quantize_unit_fast<FDT, KIND, UB, true, true>(last[k], s, a.lo, a.hi, w);   // clamped: a NaN stays in its own code
             else quantize_unit_exact<FDT, KIND, UB>(last[k], s, a.lo, a.hi, w);
             if (idx < a.nunits) store_words<OW>(out + idx * OW, w, aligned32);
         }
@@ -869,7 +927,7 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
 template <int FDT, int UB>
 __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void *scale_out, long long nunits,
                                                            int lg_units_per_block, float range, float inv_range,
-                                                           int aligned32, const RowStride rs)
+                                                           int aligned32, const RowStride rs, const PassSplit split)
 {
     using F = typename ElemOf<FDT>::type;
     constexpr int RAW = UB / 4;
@@ -877,18 +935,15 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
     const char *in = static_cast<const char *>(in_);
     const int lg = lg_units_per_block;
     pdl_entry();
-    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
-    for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < nunits;
-         base += stride) {
+    auto pass = [&](const long long (&idx)[UNR], const bool full) {
         uint32_t raw[UNR][RAW];
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            if (idx < nunits) {
-                long long offset = idx * UB;
+            if (full || idx[k] < nunits) {
+                long long offset = idx[k] * UB;
                 if (rs.enabled) {
-                    const unsigned row = fastdiv((unsigned)idx, rs.units_per_row);
-                    offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx - row * rs.units_per_row.div) * UB;
+                    const unsigned row = fastdiv((unsigned)idx[k], rs.units_per_row);
+                    offset = (long long)row * rs.row_bytes + (long long)((unsigned)idx[k] - row * rs.units_per_row.div) * UB;
                 }
                 load_unit<UB>(raw[k], in + offset, aligned32 != 0);
             } else {
@@ -898,16 +953,17 @@ __global__ void __launch_bounds__(256) block_scales_kernel(const void *in_, void
         }
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
+            if (!full && idx[k] - (threadIdx.x & 31) >= nunits) continue;   // the whole row lies past the end
             float amax = unit_absmax<FDT, RAW>(raw[k]);
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1)
                 if (m < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-            if (idx < nunits && (idx & ((1ll << lg) - 1)) == 0)
-                static_cast<F *>(scale_out)[idx >> lg] =
+            if ((full || idx[k] < nunits) && (idx[k] & ((1ll << lg) - 1)) == 0)
+                static_cast<F *>(scale_out)[idx[k] >> lg] =
                     static_cast<F>(round_to<FDT>(div_by_range(2.0f * amax, range, inv_range)));
         }
-    }
+    };
+    QK_WALK_PASSES(split.full_passes, nunits, UNR, pass);
 }
 
 // -------------------------------------------------------------------------------------
@@ -972,7 +1028,8 @@ __global__ void __launch_bounds__(256) block_scales_2d_kernel(const void *in_, v
 }
 
 // Host-side launchers, one translation unit per float type.
-cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,
+// `sub`: blocks per unit, 1 or 2 (2: fused form of 16-bit types with 64-byte units and blocks of 32 bytes).
+cudaError_t launch_quantize(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, int sub, const QuantArgs &args,
                             const LaunchCfg &cfg, cudaStream_t stream);
 // Transposed matrix views (transposed_kernels.cu): one tensor; blocks of 1, 2, 4 or 8 units (lg 0..3) or per tensor (lg -1).
 cudaError_t launch_quantize_transposed(int fdt, int kind, int unit_bytes, bool dyn, bool clamp, const QuantArgs &args,

@@ -85,6 +85,39 @@ class PreparedDynamic:
             _ffi.check(status)
 
 
+class PreparedScales:
+    """``compute_scales`` with the argument marshalling done once."""
+
+    def __init__(self, client: ComputeClient, input: TensorHandleRef, scale: TensorHandleRef, scheme: QuantScheme,
+                 input_elem: ElemType, workspace: TensorHandleRef | None = None):
+        self._keep = _ffi.c_tensors(input, scale)
+        self._scheme = _ffi.c_scheme(scheme)
+        ws_ptr, ws_bytes = (workspace.handle, workspace.shape[0] * workspace.elem_size) if workspace else (None, 0)
+        self._args = (self._keep[0].ref(), self._keep[1].ref(), self._scheme, int(input_elem), ws_ptr, ws_bytes, client.stream)
+        self._fn = _ffi.lib().qk_compute_scales
+
+    def __call__(self) -> None:
+        status = self._fn(*self._args)
+        if status:
+            _ffi.check(status)
+
+
+class PreparedRef:
+    """``launch_ref`` (quantize with given scales) with the argument marshalling done once."""
+
+    def __init__(self, client: ComputeClient, input: TensorHandleRef, output: TensorHandleRef, scale: TensorHandleRef,
+                 out_scale: TensorHandleRef, scheme: QuantScheme, input_elem: ElemType):
+        self._keep = _ffi.c_tensors(input, output, scale, out_scale)
+        self._scheme = _ffi.c_scheme(scheme)
+        self._args = tuple(k.ref() for k in self._keep) + (self._scheme, int(input_elem), client.stream)
+        self._fn = _ffi.lib().qk_quantize
+
+    def __call__(self) -> None:
+        status = self._fn(*self._args)
+        if status:
+            _ffi.check(status)
+
+
 class PreparedDynamicBatch:
     """Fused quantize of a set of tensors with one launch per group of up to 64 compatible tensors
     (``qk_quantize_dynamic_batch``); same results as ``launch_dynamic`` per tensor."""

@@ -81,7 +81,9 @@ enum {
     QK_ERR_NULL = 7,
     QK_ERR_WORKSPACE = 8,          /* workspace missing or too small */
     QK_ERR_TOO_LARGE = 9,          /* more elements than the entry point supports */
-    QK_ERR_NCCL = 10,
+    QK_ERR_NCCL = 10,              /* an NCCL call failed, the communicator reports an asynchronous error, or NCCL is absent */
+    QK_ERR_TIMEOUT = 11,           /* a host-side deadline ran out (qk_allreduce_max_f32_deadline) */
+    QK_ERR_DEVICE = 12,            /* a kernel gave up on a bounded wait: see qk_device_error */
     QK_ERR_CUDA = 1000             /* QK_ERR_CUDA + cudaError_t */
 };
 
@@ -177,8 +179,18 @@ int qk_quantize_from_absmax_batch(int count, const QkTensor *inputs, const QkTen
                                   int input_dtype, void *stream);
 
 /* ncclAllReduce(buf, buf, count, ncclFloat32, ncclMax, comm, stream) on a library-resolved
- * NCCL (libnccl.so.2 already loaded in the process, else dlopen).  `comm` is an ncclComm_t. */
+ * NCCL (libnccl.so.2 already loaded in the process, else dlopen).  `comm` is an ncclComm_t.
+ * Enqueues and returns; on a non-blocking communicator it waits (at most 10 s) for the enqueue itself to leave
+ * ncclInProgress. */
 int qk_allreduce_max_f32(float *buf, size_t count, void *comm, void *stream);
+
+/* The same exchange with a host-side deadline, for callers that must find out when a rank never joins: after the
+ * enqueue the call polls `ncclCommGetAsyncError(comm)` and the stream until the collective has completed, the
+ * communicator reports an error (QK_ERR_NCCL) or `timeout_ms` has passed (QK_ERR_TIMEOUT).  It blocks the calling
+ * thread, never the device; after QK_ERR_TIMEOUT or QK_ERR_NCCL the communicator is the caller's to abort
+ * (ncclCommAbort) - the library does not own it.  With a non-blocking communicator (ncclConfig_t.blocking = 0) the
+ * enqueue itself is covered by the deadline too. */
+int qk_allreduce_max_f32_deadline(float *buf, size_t count, void *comm, void *stream, int timeout_ms);
 
 /*
  * qk_quantize_dynamic for callers that cannot allocate.  (No counterpart in the reference, whose
@@ -235,22 +247,16 @@ size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *sc
 const char *qk_strerror(int status);
 const char *qk_version(void);
 
-/* Reads (synchronously) the device-side error flag of the current device: non-zero if a kernel gave up
- * on a bounded wait (only the shared-memory staged quantize variant, tuning key 8, has such waits). */
+/* Reads AND CLEARS (synchronously: the call waits for the device) the error flag of the current device: `*flag_out`
+ * is non-zero if, since the last call, a kernel gave up on a bounded wait and left its output unwritten.  Only the
+ * quantize variant that stages its input through shared memory with bulk copies has such waits.  Entry points
+ * are asynchronous and cannot report this themselves: callers that need the guarantee call this after
+ * synchronising the stream.  qk_roundtrip_host, which synchronises anyway, checks the flag itself and returns
+ * QK_ERR_DEVICE. */
 int qk_device_error(int *flag_out);
 
 /* Number of kernels this library has launched in the calling process (for accounting). */
 uint64_t qk_launch_count(void);
-
-/* Process-wide launch knobs, for measurements and tests only (keys: 0 threads per CTA, 1 CTAs per SM,
- * 2 force the reference-arithmetic route, 3 force the layout-general kernels, 4 programmatic dependent
- * launch on/off, 5 / 6 grid size of the quantize / dequantize kernels in waves, 7 cooperative per-tensor
- * kernel on/off, 8 staging of the quantize input through shared
- * memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never, 9 / 10 input KiB per slice and staging
- * slots (1..8) of qk_roundtrip_host; change them only between calls, and size the staging area after, 11 ring
- * depth (2..4 tiles of 16 KB) of the staged quantize variant). */
-void qk_set_tuning(int key, int value);
-int qk_get_tuning(int key);
 
 #ifdef __cplusplus
 }

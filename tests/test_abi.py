@@ -12,12 +12,14 @@ from cubek_b200 import (ComputeClient, ElemType, LaunchError, QuantLevel, QuantP
                         QuantStore, QuantValue, TensorHandleRef, dequantize, quantize)
 from cubek_b200 import _ffi
 
-HEADER = Path(__file__).resolve().parent.parent / "include" / "cubek_quant_b200.h"
+INCLUDE = Path(__file__).resolve().parent.parent / "include"
+HEADER = INCLUDE / "cubek_quant_b200.h"
+TESTING_HEADER = INCLUDE / "cubek_quant_b200_testing.h"
 CLIENT = ComputeClient(0, 0)
 
 
-def declared_symbols():
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+def declared_symbols(header=HEADER):
+    text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
     return sorted(set(re.findall(r"\b(qk_[a-z0-9_]+)\s*\(", text)))
 
 
@@ -25,12 +27,15 @@ def test_library_exports_every_declared_symbol():
     lib = C.CDLL(str(_ffi.LIB_PATH))
     names = declared_symbols()
     assert len(names) >= 15
-    for name in names:
-        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    for name in names + declared_symbols(TESTING_HEADER):
+        assert hasattr(lib, name), f"{name} declared in a header but not exported"
 
 
-def test_binding_covers_the_header():
+def test_binding_covers_the_headers():
     assert set(_ffi.EXPORTED_SYMBOLS) == set(declared_symbols())
+    assert set(_ffi.TESTING_SYMBOLS) == set(declared_symbols(TESTING_HEADER))
+    # the public header carries no process-wide knobs
+    assert not any("tuning" in n or "testing" in n for n in declared_symbols())
 
 
 def test_version_and_strerror():
