@@ -793,6 +793,33 @@ def run_e2e(ctx: Ctx, args, sset: ShardedSet, what: str):
             "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies); bytes per step are this rank's"}
 
 
+def run_reduce_record(ctx: Ctx, steps):
+    """Axis reductions (the caller-side absmax / range step) on a 64 x 4096 x 4096 tensor: algorithmic GB/s (the
+    input is read once, the output is small) along the first axis (the contiguous axis is kept and vectorised) and
+    along the last, contiguous one."""
+    from cubek_b200 import ElemType, TensorHandleRef
+    from cubek_b200.reduce import ReduceInst, reduce
+
+    torch, H = ctx.torch, TensorHandleRef.from_torch
+    peak, _ = measured_peak()
+    out = {}
+    for name, tdt, elem in (("f32", torch.float32, ElemType.F32), ("bf16", torch.bfloat16, ElemType.BF16)):
+        x = torch.empty((64, 4096, 4096), dtype=tdt, device=ctx.dev).normal_(0.0, 1.0)
+        for axis in (0, 2):
+            shape = list(x.shape)
+            shape[axis] = 1
+            y = torch.empty(shape, dtype=tdt, device=ctx.dev)
+            for inst in ReduceInst:
+                fn = lambda: reduce(ctx.client, H(x), H(y), axis, None, inst, elem)
+                fn()
+                ms = ctx.time_steps(fn, steps)
+                nbytes = x.numel() * x.element_size() + y.numel() * y.element_size()
+                out[f"{inst.name}_{name}_axis{axis}"] = {"gbs": round(nbytes / ms / 1e6, 1), "frac_of_measured": round(nbytes / ms / 1e6 / peak, 4)}
+        del x
+        torch.cuda.empty_cache()
+    return {"shape": [64, 4096, 4096], "results": out}
+
+
 def run_gpu(args):
     from cubek_b200.synthetic import WORKLOADS
 
@@ -808,7 +835,7 @@ def run_gpu(args):
         w = WORKLOADS[args.workload]
         main = run_single_config(ctx, args, w, args.batch, headline=True)
         e2e_set, e2e_what = main["sets"][0][1], f"{min(args.e2e_tensors, args.batch)} of the {args.batch} tensors of a step"
-    e2e = run_e2e(ctx, args, e2e_set, e2e_what)
+    e2e = None if args.no_e2e else run_e2e(ctx, args, e2e_set, e2e_what)
 
     configs = {}
     if is_set and not args.no_configs:
@@ -821,6 +848,8 @@ def run_gpu(args):
             configs[name] = rec["summary"]
             del rec
             torch.cuda.empty_cache()
+        if ctx.world == 1:
+            configs["reduce_64x4096x4096"] = run_reduce_record(ctx, 5)
 
     if ctx.rank == 0:
         value = main["bytes"] / main["ms"] / 1e6
@@ -945,6 +974,7 @@ def main():
     ap.add_argument("--e2e-tensors", type=int, default=7)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-configs", action="store_true", help="skip the records of the single-tensor configurations")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host round trip (launch lists of the device steps only)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (A/B runs)")
     ap.add_argument("--tune", default="", help="library tuning keys for A/B runs, e.g. 11=2,8=1")

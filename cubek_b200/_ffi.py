@@ -46,6 +46,10 @@ class QkTensor(C.Structure):
                 ("strides", C.POINTER(C.c_int64)), ("elem_size", C.c_int32)]
 
 
+class QkReduceStrategy(C.Structure):
+    _fields_ = [("use_planes", C.c_int32), ("shared", C.c_int32)]
+
+
 class LaunchError(RuntimeError):
     """A launch failed (the reference's ``Err(LaunchError)``)."""
 
@@ -74,6 +78,7 @@ _SIGNATURES = {
     "qk_quantize_dynamic": (C.c_int, [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                                  C.c_size_t, C.c_void_p]),
     "qk_reduce_maxabs": (C.c_int, [C.POINTER(QkTensor)] * 2 + [C.c_int, C.c_int, C.c_void_p]),
+    "qk_reduce": (C.c_int, [C.POINTER(QkTensor)] * 2 + [C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "qk_quantize_dynamic_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                     C.c_size_t, C.c_void_p]),
     "qk_dequantize_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 3 + [C.POINTER(QkScheme), C.c_int, C.c_void_p]),

@@ -876,28 +876,43 @@ int qk_quantize_dynamic(const QkTensor *input, const QkTensor *output, const QkT
     return quantize_common(input, output, nullptr, out_scale, nullptr, true, gen_scales, scheme, input_dtype, stream);
 }
 
-int qk_reduce_maxabs(const QkTensor *input, const QkTensor *output, int axis, int dtype, void *stream)
+int qk_reduce(const QkTensor *input, const QkTensor *output, int axis, int inst, const QkReduceStrategy *strategy,
+              int dtype, void *stream_)
 {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!input || !output) return QK_ERR_NULL;
+    if (inst != QK_REDUCE_MAXABS && inst != QK_REDUCE_MAX && inst != QK_REDUCE_MIN) return QK_ERR_UNSUPPORTED_SCHEME;
     const int fsize = dtype_size(dtype);
     if (fsize == 0) return QK_ERR_DTYPE;
     int rc;
     if ((rc = check_tensor(input, fsize))) return rc;
     if ((rc = check_tensor(output, fsize))) return rc;
-    // validate_axis / valid_output_shape (crates/cubek-reduce/src/lib.rs:134-150)
+    // validate_axis / valid_output_shape (crates/cubek-reduce/src/lib.rs:134-160)
     if (axis < 0 || axis >= input->rank) return QK_ERR_SHAPE;
     if (output->rank != input->rank) return QK_ERR_SHAPE;
     for (int d = 0; d < input->rank; ++d)
         if (output->shape[d] != (d == axis ? 1 : input->shape[d])) return QK_ERR_SHAPE;
-    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_LAYOUT;
     long long outer = 1, inner = 1;
     for (int d = 0; d < axis; ++d) outer *= input->shape[d];
     for (int d = axis + 1; d < input->rank; ++d) inner *= input->shape[d];
     const long long len = input->shape[axis];
     if (outer * inner == 0) return QK_OK;
+    // `ReduceStrategy` (strategy.rs:7-16): shared -> a CTA per item, else planes -> a warp per item, else a thread
+    int units = 0;
+    if (strategy) units = strategy->shared ? 256 : (strategy->use_planes ? 32 : 1);
+    const LaunchCfg cfg = current_cfg();
     count_launch();
-    return cuda_status(launch_maxabs(dtype, input->ptr, output->ptr, outer, len, inner, current_cfg(),
-                                     static_cast<cudaStream_t>(stream)));
+    const int per16 = 16 / fsize;
+    const bool contiguous = is_contiguous(input) && is_contiguous(output);
+    const bool vectors_ok = inner == 1 || (inner % per16 == 0 && aligned(input->ptr, 16) && aligned(output->ptr, 16));
+    if (contiguous && vectors_ok && !g_tune[TUNE_FORCE_GENERAL].load())
+        return cuda_status(launch_reduce_contiguous(dtype, inst, input->ptr, output->ptr, outer, len, inner, units, cfg, stream));
+    return cuda_status(launch_reduce_strided(dtype, inst, input, output, axis, cfg, stream));
+}
+
+int qk_reduce_maxabs(const QkTensor *input, const QkTensor *output, int axis, int dtype, void *stream)
+{
+    return qk_reduce(input, output, axis, QK_REDUCE_MAXABS, nullptr, dtype, stream);
 }
 
 int qk_absmax_f32(const QkTensor *input, int input_dtype, float *absmax_out, void *stream)

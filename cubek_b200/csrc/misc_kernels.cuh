@@ -86,7 +86,10 @@ cudaError_t launch_absmax_strided(const GeneralLayout &layout, const void *in, i
                                   const LaunchCfg &cfg, cudaStream_t stream);
 
 // max |x| over `len` elements of stride `inner`, for every (outer, inner) position.
-cudaError_t launch_maxabs(int fdt, const void *in, void *out, long long outer, long long len, long long inner,
-                          const LaunchCfg &cfg, cudaStream_t stream);
+// Axis reductions (reduce.cu).  inst: 0 MaxAbs, 1 Max, 2 Min.
+cudaError_t launch_reduce_contiguous(int fdt, int inst, const void *in, void *out, long long outer, long long len,
+                                     long long inner, int units_per_item, const LaunchCfg &cfg, cudaStream_t stream);
+cudaError_t launch_reduce_strided(int fdt, int inst, const QkTensor *input, const QkTensor *output, int axis,
+                                  const LaunchCfg &cfg, cudaStream_t stream);
 
 }  // namespace qk

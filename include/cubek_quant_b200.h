@@ -129,11 +129,25 @@ int qk_compute_scales(const QkTensor *input, const QkTensor *scale, const QkSche
                       int input_dtype, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
- * max |x| along `axis`: `cubek_reduce::reduce::<R, MaxAbs>(client, input, output, axis, ..)`
- * (crates/cubek-reduce/src/lib.rs:93-131, instructions/maxabs.rs:31-87) for contiguous tensors.
- * `output` has the input's shape with extent 1 at `axis` and the input's element type
- * (the reference accumulates MaxAbs in the input type; the result is exact).
+ * Axis reductions: `cubek_reduce::reduce::<R, Inst>(client, input, output, axis, strategy, ..)`
+ * (crates/cubek-reduce/src/lib.rs:93-131) for the instructions MaxAbs, Max and Min
+ * (instructions/maxabs.rs:31-87, max.rs, min.rs).  `output` has the input's shape with extent 1 at `axis`
+ * (`valid_output_shape`, lib.rs:142-160) and the input's element type, which is also the accumulator type of these
+ * instructions in the reference; every result is one of the inputs, hence exact.  Max / Min start from the lowest /
+ * highest finite value of the type (their null accumulators).  Both tensors may be strided.
+ *
+ * `strategy` mirrors `ReduceStrategy { use_planes, shared }` (strategy.rs:7-16): shared = all threads of a CTA
+ * reduce one output item together; else use_planes = one warp per item; else one thread per item.  NULL lets the
+ * library choose by shape.  The result does not depend on it.
  */
+typedef enum { QK_REDUCE_MAXABS = 0, QK_REDUCE_MAX = 1, QK_REDUCE_MIN = 2 } QkReduceInst;
+typedef struct {
+    int32_t use_planes;
+    int32_t shared;
+} QkReduceStrategy;
+int qk_reduce(const QkTensor *input, const QkTensor *output, int axis, int inst, const QkReduceStrategy *strategy,
+              int dtype, void *stream);
+/* qk_reduce with QK_REDUCE_MAXABS and the default strategy: the absmax step callers of the quantize path run. */
 int qk_reduce_maxabs(const QkTensor *input, const QkTensor *output, int axis, int dtype, void *stream);
 
 /*
