@@ -356,9 +356,10 @@ static int check_scales_shape(const Geometry &g, const QkTensor *sc)
 }
 
 static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *scales, const QkTensor *out_scales,
-                        const QkTensor *data)
+                        const QkTensor *data, const QkTensor *values = nullptr)
 {
     L.data_contiguous = (!data || is_contiguous(data)) ? 1 : 0;
+    L.values_contiguous = (!values || is_contiguous(values)) ? 1 : 0;
     L.rank = g.rank;
     L.per_tensor = g.per_tensor ? 1 : 0;
     for (int d = 0; d < QK_MAX_RANK; ++d) {
@@ -367,8 +368,9 @@ static void fill_layout(GeneralLayout &L, const Geometry &g, const QkTensor *sca
         L.scale_strides[d] = (!g.per_tensor && scales && d < g.rank) ? scales->strides[d] : 0;
         L.out_scale_strides[d] = (!g.per_tensor && out_scales && d < g.rank) ? out_scales->strides[d] : 0;
         L.data_strides[d] = (data && d < g.rank) ? data->strides[d] : 0;
+        L.values_strides[d] = (values && d < g.rank) ? values->strides[d] : 0;
     }
-    finish_layout(L);
+    finish_layout(L, g.nq);
 }
 
 static int log2_exact(long long v)
@@ -393,6 +395,7 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
 {
     if (sub) *sub = 1;
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
+    if (!is_contiguous(out)) return -2;   // a strided quantized tensor (a transposed matmul operand): general kernels
     const int esz = dtype_size(fdt);
     if (!aligned(in->ptr, 16)) return -2;
     long long row_stride = 0;
@@ -448,6 +451,7 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
                               const QkTensor *params, int *out_bytes)
 {
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
+    if (!is_contiguous(values)) return -2;
     const int esz = dtype_size(fdt);
     if (!aligned(out->ptr, 16)) return -2;
     long long row_stride = 0;
@@ -480,10 +484,12 @@ static GeneralLayout strided_data_layout(const QkTensor *t)
     L.rank = t->rank;
     L.per_tensor = 1;
     L.data_contiguous = 0;
+    L.values_contiguous = 1;
     for (int d = 0; d < QK_MAX_RANK; ++d) {
         L.shape[d] = d < t->rank ? t->shape[d] : 1;
         L.data_strides[d] = d < t->rank ? t->strides[d] : 0;
         L.block[d] = 1;
+        L.values_strides[d] = 0;
         L.scale_strides[d] = L.out_scale_strides[d] = 0;
     }
     finish_layout(L);
@@ -1071,6 +1077,46 @@ void qk_testing_set_collective_hooks(int (*allreduce)(const void *, void *, size
     g_stream_query.store(set ? stream_query : nullptr);
 }
 
+int qk_into_contiguous_packed(const QkTensor *input, const QkTensor *output, const int64_t *shape, int rank, int packing,
+                              void *stream)
+{
+    if (!input || !output || !shape) return QK_ERR_NULL;
+    if (rank < 1 || rank > QK_MAX_RANK || input->rank != rank || output->rank != rank) return QK_ERR_SHAPE;
+    if (input->elem_size != output->elem_size || (input->elem_size != 4 && input->elem_size != 1)) return QK_ERR_DTYPE;
+    const int item_bits = input->elem_size * 8;
+    if (packing < 1 || item_bits % packing != 0) return QK_ERR_SHAPE;
+    int rc;
+    if ((rc = check_tensor(input, input->elem_size))) return rc;
+    if ((rc = check_tensor(output, output->elem_size))) return rc;
+    // The packing of the input runs along its contiguous dim (the last one of stride 1 among dims of extent > 1).
+    int packed_dim = rank - 1;
+    for (int d = rank - 1; d >= 0; --d)
+        if (input->strides[d] == 1 && input->shape[d] != 1) { packed_dim = d; break; }
+    RepackArgs a;
+    a.rank = rank;
+    a.packed_dim = packed_dim;
+    a.packing = packing;
+    a.bits = item_bits / packing;
+    a.item_bytes = input->elem_size;
+    a.nitems_out = 1;
+    for (int d = 0; d < QK_MAX_RANK; ++d) {
+        a.shape[d] = d < rank ? shape[d] : 1;
+        a.in_strides[d] = d < rank ? input->strides[d] : 0;
+        if (d >= rank) continue;
+        if (shape[d] < 0) return QK_ERR_SHAPE;
+        const long long in_want = (d == packed_dim) ? (shape[d] + packing - 1) / packing : shape[d];
+        const long long out_want = (d == rank - 1) ? (shape[d] + packing - 1) / packing : shape[d];
+        if (input->shape[d] != in_want || output->shape[d] != out_want) return QK_ERR_SHAPE;
+        a.nitems_out *= out_want;
+    }
+    if (!is_contiguous(output)) return QK_ERR_LAYOUT;
+    if (a.nitems_out == 0) return QK_OK;
+    a.in = input->ptr;
+    a.out = output->ptr;
+    count_launch();
+    return cuda_status(launch_repack(a, current_cfg(), static_cast<cudaStream_t>(stream)));
+}
+
 const char *qk_strerror(int status)
 {
     switch (status) {
@@ -1079,7 +1125,7 @@ const char *qk_strerror(int status)
     case QK_ERR_BLOCK_SIZE: return "block size must be non-zero, fit the tensor rank and be divisible by num_quants";
     case QK_ERR_SHAPE: return "shape mismatch (last dim must be a multiple of num_quants; scales must hold one value per block)";
     case QK_ERR_DTYPE: return "element size does not match the declared element type";
-    case QK_ERR_LAYOUT: return "the quantized tensor must be contiguous";
+    case QK_ERR_LAYOUT: return "tensor layout not supported by this entry point";
     case QK_ERR_ALIGN: return "pointer is not aligned to its element size";
     case QK_ERR_NULL: return "null argument";
     case QK_ERR_WORKSPACE: return "workspace missing or too small";
@@ -1138,9 +1184,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
     if (!g.per_tensor && g.B % g.nq != 0) return QK_ERR_BLOCK_SIZE;
     if (scale && (rc = check_scales_shape(g, scale))) return rc;
     if ((rc = check_scales_shape(g, out_scale))) return rc;
-    // The float tensor may be strided (the reference reads it through `linear_view`); the quantized
-    // tensor must be contiguous.
-    if (!is_contiguous(output)) return QK_ERR_LAYOUT;
+    // Both tensors may be strided: the reference reaches them through `linear_view` (quantize.rs:311, :316).
     if (g.n == 0) return QK_OK;
 
     float lo, hi;
@@ -1224,7 +1268,7 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
 
     // Transposed matrix views: units gathered across memory rows, coalesced over the logical rows.
     long long ld = 0;
-    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(input, &ld) && !g.blocks_2d &&
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_contiguous(output) && is_transposed_matrix(input, &ld) && !g.blocks_2d &&
         (g.per_tensor || (g.last_dim_blocks && is_contiguous(out_scale) && (!scale || is_contiguous(scale)))) &&
         !(dynamic && g.per_tensor)) {
         for (int ub = 64; ub >= 32; ub >>= 1) {
@@ -1296,9 +1340,9 @@ static int quantize_common(const QkTensor *input, const QkTensor *output, const 
         cudaError_t e = launch_general_scales(sa, cfg, stream);
         if (e != cudaSuccess) return cuda_status(e);
         scale_ptr = gen_scales;
-        fill_layout(a.layout, g, &staged, out_scale, input);
+        fill_layout(a.layout, g, &staged, out_scale, input, output);
     } else {
-        fill_layout(a.layout, g, scale, out_scale, input);
+        fill_layout(a.layout, g, scale, out_scale, input, output);
     }
     a.in = input->ptr;
     a.out = output->ptr;
@@ -1332,7 +1376,6 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     Geometry g;
     if ((rc = build_geometry(g, scheme, output, values))) return rc;
     if ((rc = check_scales_shape(g, params))) return rc;
-    if (!is_contiguous(values)) return QK_ERR_LAYOUT;   // the float output may be strided
     if (g.n == 0) return QK_OK;
 
     const LaunchCfg cfg = current_cfg();
@@ -1372,7 +1415,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     }
     if (batch && (rc = flush_dequant(*batch, cfg, stream))) return rc;
     long long ld = 0;
-    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_transposed_matrix(output, &ld) && !g.blocks_2d &&
+    if (!g_tune[TUNE_FORCE_GENERAL].load() && is_contiguous(values) && is_transposed_matrix(output, &ld) && !g.blocks_2d &&
         (g.per_tensor || (g.last_dim_blocks && is_contiguous(params)))) {
         for (int ob = 64; ob >= 32; ob >>= 1) {
             if (ob < min_dequant_bytes(output_dtype, g.kind)) break;
@@ -1409,7 +1452,7 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
         }
     }
     GeneralDequantArgs a;
-    fill_layout(a.layout, g, params, nullptr, output);
+    fill_layout(a.layout, g, params, nullptr, output, values);
     a.values = values->ptr;
     a.params = params->ptr;
     a.out = output->ptr;
@@ -1439,8 +1482,7 @@ static int try_quantize_tensor_coop(const QkTensor *input, const QkTensor *outpu
     Geometry g;
     if ((rc = build_geometry(g, scheme, input, output))) return rc;
     if ((rc = check_scales_shape(g, out_scale))) return rc;
-    if (!is_contiguous(output)) return QK_ERR_LAYOUT;
-    if (!is_contiguous(input)) return QK_ERR_TOO_LARGE;
+    if (!is_contiguous(input) || !is_contiguous(output)) return QK_ERR_TOO_LARGE;
     const int U = 64 / fsize;
     if (g.n == 0 || g.n % U != 0 || !aligned(input->ptr, 16) || !aligned(output->ptr, 16) || !aligned(workspace, 4))
         return QK_ERR_TOO_LARGE;

@@ -323,6 +323,34 @@ __device__ __forceinline__ long long data_index(const GeneralLayout &L, long lon
     return idx;
 }
 
+// Offset (stored items) of item `item` of the quantized tensor (linear index over the packed shape).
+__device__ __forceinline__ long long values_index(const GeneralLayout &L, long long item)
+{
+    if (L.values_contiguous) return item;
+    const int last = L.rank - 1;
+    if (L.fits31) {
+        unsigned offs = (unsigned)item;
+        unsigned q = fastdiv(offs, L.packed_last_div);
+        long long idx = (long long)(offs - q * L.packed_last_div.div) * L.values_strides[last];
+        offs = q;
+        for (int d = last - 1; d >= 0; --d) {
+            q = fastdiv(offs, L.shape_div[d]);
+            idx += (long long)(offs - q * L.shape_div[d].div) * L.values_strides[d];
+            offs = q;
+        }
+        return idx;
+    }
+    long long offs = item;
+    const long long plast = (long long)L.packed_last_div.div;
+    long long idx = (offs % plast) * L.values_strides[last];
+    offs /= plast;
+    for (int d = last - 1; d >= 0; --d) {
+        idx += (offs % L.shape[d]) * L.values_strides[d];
+        offs /= L.shape[d];
+    }
+    return idx;
+}
+
 // Native element encode of an integral, clamped value.
 __device__ __forceinline__ uint32_t encode_native(int kind, float c)
 {
@@ -358,14 +386,14 @@ __global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuan
                 const float c = round_clamp(t, a.lo, a.hi);
                 word |= ((uint32_t)(int)c & mask) << (i * bits);
             }
-            static_cast<uint32_t *>(a.out)[item] = word;
+            static_cast<uint32_t *>(a.out)[values_index(a.layout, item)] = word;
         } else if (a.kind == KIND_E2M1) {
             const float c0 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
             const float c1 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0 + dstep), s)), a.lo, a.hi);
-            static_cast<uint8_t *>(a.out)[item] = (uint8_t)cvt_e2m1x2(c0, c1);
+            static_cast<uint8_t *>(a.out)[values_index(a.layout, item)] = (uint8_t)cvt_e2m1x2(c0, c1);
         } else {
             const float c = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
-            static_cast<uint8_t *>(a.out)[item] = (uint8_t)encode_native(a.kind, c);
+            static_cast<uint8_t *>(a.out)[values_index(a.layout, item)] = (uint8_t)encode_native(a.kind, c);
         }
     }
 }
@@ -384,19 +412,19 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
         const long long d0 = data_index(a.layout, pos);
         const long long dstep = a.layout.data_contiguous ? 1 : a.layout.data_strides[a.layout.rank - 1];
         if (a.kind <= KIND_PACK2) {
-            const uint32_t word = static_cast<const uint32_t *>(a.values)[item];
+            const uint32_t word = static_cast<const uint32_t *>(a.values)[values_index(a.layout, item)];
             for (int i = 0; i < a.nq; ++i) {
                 const int raw = (int)((word >> (i * bits)) & mask);
                 const int q = raw - (raw >= sign_bit ? two_pow_n : 0);
                 store_dyn(a.out, a.fdt, d0 + i * dstep, s * (float)q);
             }
         } else if (a.kind == KIND_E2M1) {
-            uint32_t h2 = cvt_f16x2_from_e2m1x2(static_cast<const uint8_t *>(a.values)[item]);
+            uint32_t h2 = cvt_f16x2_from_e2m1x2(static_cast<const uint8_t *>(a.values)[values_index(a.layout, item)]);
             float2 f = __half22float2(*reinterpret_cast<__half2 *>(&h2));
             store_dyn(a.out, a.fdt, d0, s * f.x);
             store_dyn(a.out, a.fdt, d0 + dstep, s * f.y);
         } else {
-            const uint32_t b = static_cast<const uint8_t *>(a.values)[item];
+            const uint32_t b = static_cast<const uint8_t *>(a.values)[values_index(a.layout, item)];
             float q;
             if (a.kind == KIND_I8) q = (float)(int)(int8_t)b;
             else {
@@ -448,7 +476,7 @@ __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScales
     }
 }
 
-void finish_layout(GeneralLayout &L)
+void finish_layout(GeneralLayout &L, int nq)
 {
     long long n = 1;
     bool ok = true;
@@ -461,6 +489,8 @@ void finish_layout(GeneralLayout &L)
         L.shape_div[d] = make_fastdiv((ok && d < L.rank) ? (unsigned)L.shape[d] : 1u);
         L.block_div[d] = make_fastdiv((ok && d < L.rank) ? (unsigned)L.block[d] : 1u);
     }
+    const long long plast = (L.rank >= 1 && nq >= 1) ? L.shape[L.rank - 1] / nq : 1;
+    L.packed_last_div = make_fastdiv((plast >= 1 && plast < (1ll << 31)) ? (unsigned)plast : 1u);
 }
 
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)

@@ -20,6 +20,12 @@ struct GeneralLayout {
     // dequantize.  The reference reaches it through `linear_view`, which honours strides.
     long long data_strides[QK_MAX_RANK];
     int data_contiguous;
+    // strides (stored items) of the quantized tensor, whose shape is `shape` with the last dim divided by
+    // num_quants.  The reference writes / reads it through `linear_view(.., 1)` (quantize.rs:316), so it may be a
+    // strided view too (a transposed matmul operand).
+    long long values_strides[QK_MAX_RANK];
+    int values_contiguous;
+    FastDiv packed_last_div;   // shape[rank - 1] / num_quants
     // Tensors of fewer than 2^31 elements take 32-bit index arithmetic with one multiply-high per
     // division (the 64-bit div/mod chain costs several hundred instructions per stored item).
     int fits31;
@@ -27,8 +33,8 @@ struct GeneralLayout {
     FastDiv block_div[QK_MAX_RANK];
 };
 
-// Fills fits31 / shape_div / block_div from rank, shape and block.
-void finish_layout(GeneralLayout &layout);
+// Fills fits31 / shape_div / block_div / packed_last_div from rank, shape, block and num_quants.
+void finish_layout(GeneralLayout &layout, int nq = 1);
 
 struct GeneralQuantArgs {
     GeneralLayout layout;
@@ -86,6 +92,17 @@ cudaError_t launch_absmax_strided(const GeneralLayout &layout, const void *in, i
                                   const LaunchCfg &cfg, cudaStream_t stream);
 
 // max |x| over `len` elements of stride `inner`, for every (outer, inner) position.
+// `into_contiguous_packed` (repack.cu): gathers the fields of a packed tensor whose packing runs along `packed_dim`
+// into a contiguous row-major tensor packed along the last dim.
+struct RepackArgs {
+    int rank, packed_dim, packing, bits, item_bytes;
+    long long shape[QK_MAX_RANK];        // logical (unpacked) shape
+    long long in_strides[QK_MAX_RANK];   // strides of the packed input (items)
+    const void *in;
+    void *out;
+    long long nitems_out;
+};
+cudaError_t launch_repack(const RepackArgs &a, const LaunchCfg &cfg, cudaStream_t stream);
 // Axis reductions (reduce.cu).  inst: 0 MaxAbs, 1 Max, 2 Min.
 cudaError_t launch_reduce_contiguous(int fdt, int inst, const void *in, void *out, long long outer, long long len,
                                      long long inner, int units_per_item, const LaunchCfg &cfg, cudaStream_t stream);

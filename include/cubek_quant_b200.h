@@ -76,7 +76,7 @@ enum {
     QK_ERR_BLOCK_SIZE = 2,         /* lib.rs:28-31 */
     QK_ERR_SHAPE = 3,              /* last dim not a multiple of num_quants, or shapes that disagree */
     QK_ERR_DTYPE = 4,              /* elem_size does not match the declared element type */
-    QK_ERR_LAYOUT = 5,             /* non-contiguous quantized tensor */
+    QK_ERR_LAYOUT = 5,             /* a tensor this entry point needs contiguous is not */
     QK_ERR_ALIGN = 6,              /* pointer not aligned to its element / word size */
     QK_ERR_NULL = 7,
     QK_ERR_WORKSPACE = 8,          /* workspace missing or too small */
@@ -99,7 +99,9 @@ int qk_value_range(int value, float *lo, float *hi);
  *   input     float tensor of type `input_dtype`; may be strided (contiguous ones, and ones whose rows are
  *             contiguous and a constant 16-byte-aligned stride apart, take the fast kernels)
  *   output    quantized tensor: u32 words of shape [.., n/num_quants] (QK_STORE_U32), or
- *             1-byte items (QK_STORE_NATIVE: i8, e4m3, e5m2; fp4 pairs of shape [.., n/2])
+ *             1-byte items (QK_STORE_NATIVE: i8, e4m3, e5m2; fp4 pairs of shape [.., n/2]); may be strided (the
+ *             reference writes it through `linear_view(output, 1)`, quantize.rs:316): contiguous ones take the
+ *             fast kernels
  *   scale     scales typed `input_dtype`: shape [1] per tensor, else one per block
  *             (its strides are honoured)
  *   out_scale receives the scales cast to the param type; same shape/strides rules
@@ -110,7 +112,7 @@ int qk_quantize(const QkTensor *input, const QkTensor *output, const QkTensor *s
 
 /*
  * Replaces `cubek_quant::dequantize::launch_ref` (dequantize.rs:171-229), same argument order.
- *   values  quantized tensor (as written by qk_quantize)
+ *   values  quantized tensor (as written by qk_quantize); may be strided
  *   output  float tensor of type `output_dtype`, shape = unpacked shape; may be strided
  *   params  scales typed as the scheme's param
  */
@@ -257,6 +259,22 @@ int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTens
                       const QkTensor *restored, const QkScheme *scheme, int input_dtype,
                       void *staging, size_t staging_bytes, int device);
 size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *scheme, int input_dtype);
+
+/*
+ * Rewrites a packed quantized tensor whose packing does not run along its last dim as a contiguous row-major tensor
+ * packed along the last dim: `into_contiguous_packed(client, data, shape, packing, ..)` as called by
+ * `MatmulInputHandleRef::into_contiguous` for quantized operands (crates/cubek-matmul/src/base.rs:489-541; packing =
+ * num_quants for QK_STORE_U32, 2 for native e2m1x2).  A column-major operand - the transposed view of a tensor
+ * quantized along its rows, which the matmul addresses as `(row / packing, col)`
+ * (crates/cubek-matmul/src/components/global/memory/layout.rs:131-134) - becomes the row-major operand addressed as
+ * `(row, col / packing)`.
+ *   input   packed tensor, any strides; its packing runs along its contiguous dim (stride 1); that dim's extent is
+ *           ceil(shape[d] / packing), the others equal `shape`; elem_size 4 (u32 words) or 1 (e2m1x2 bytes)
+ *   output  contiguous, `shape` with the last dim ceil-divided by `packing`, same elem_size
+ *   shape   the logical (unpacked) shape, `rank` entries
+ */
+int qk_into_contiguous_packed(const QkTensor *input, const QkTensor *output, const int64_t *shape, int rank, int packing,
+                              void *stream);
 
 const char *qk_strerror(int status);
 const char *qk_version(void);

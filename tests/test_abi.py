@@ -100,10 +100,14 @@ def test_dtype_layout_alignment_and_null():
         quantize.launch_ref(CLIENT, fake((4, 32), 4), args["output"], args["scale"], args["out_scale"], sch,
                             ElemType.BF16)
     assert e.value.status == _ffi.QK_ERR_DTYPE
-    with pytest.raises(LaunchError) as e:  # the quantized tensor must be contiguous (the float one may be strided)
-        quantize.launch_ref(CLIENT, fake((4, 32), 4), fake((4, 8), 4, strides=(1, 4)), args["scale"],
-                            args["out_scale"], sch, ElemType.F32)
-    assert e.value.status == _ffi.QK_ERR_LAYOUT
+    # the repack's output is the one tensor that must be contiguous
+    import ctypes as C2
+    src, dst = _ffi.c_tensors(fake((8, 16), 4, strides=(1, 8)), fake((32, 4), 4, strides=(1, 32)))
+    shape = (C2.c_int64 * 2)(32, 16)
+    assert _ffi.lib().qk_into_contiguous_packed(src.ref(), dst.ref(), shape, 2, 4, None) == _ffi.QK_ERR_LAYOUT
+    # ... and its shapes must be the packed forms of `shape`
+    src, dst = _ffi.c_tensors(fake((8, 16), 4, strides=(1, 8)), fake((32, 5), 4))
+    assert _ffi.lib().qk_into_contiguous_packed(src.ref(), dst.ref(), shape, 2, 4, None) == _ffi.QK_ERR_SHAPE
     with pytest.raises(LaunchError) as e:
         quantize.launch_ref(CLIENT, fake((4, 32), 4, addr=0x10002), args["output"], args["scale"],
                             args["out_scale"], sch, ElemType.F32)

@@ -82,7 +82,8 @@ def test_null_accumulators_and_nan_elements():
         assert got.tolist() == [lowest, 3.0, lowest, -2.0]
     half = np.full((2, 16), np.inf, dtype=np.float16)
     do = empty_device((2, 1), np.float16)
-    reduce(ComputeClient.current(), H(to_device(half)), H(do), 1, None, ReduceInst.Min, elem_of(np.float16))
+    dhalf = to_device(half)
+    reduce(ComputeClient.current(), H(dhalf), H(do), 1, None, ReduceInst.Min, elem_of(np.float16))
     torch.cuda.synchronize()
     assert to_numpy(do, np.float16).reshape(-1).tolist() == [65504.0, 65504.0]
 
@@ -91,7 +92,8 @@ def test_null_accumulators_and_nan_elements():
 def test_maxabs_shortcut():
     x = random_tensor((33, 777), np.float32, 63)
     do = empty_device((33, 1), np.float32)
-    reduce_maxabs(ComputeClient.current(), H(to_device(x)), H(do), 1, elem_of(np.float32))
+    dx = to_device(x)
+    reduce_maxabs(ComputeClient.current(), H(dx), H(do), 1, elem_of(np.float32))
     torch.cuda.synchronize()
     assert_bits_equal(to_numpy(do, np.float32), numpy_reduce(x, 1, ReduceInst.MaxAbs), "maxabs")
 

@@ -73,3 +73,105 @@ def test_tile_schemes_on_gpu(fname, shape, block):
         assert_bits_equal(d_codes, codes, "codes (fused)")
         assert_bits_equal(d_out_scale, out_scale, "out_scale (fused)")
         assert_bits_equal(gpu_dequantize(codes, out_scale, scheme, F), O.dequantize(codes, out_scale, scheme, F), "restored")
+
+
+def unpack_fields(items, bits):
+    """[.., n] items -> [.., n * per] raw fields (element 0 in the least significant bits)."""
+    per = items.dtype.itemsize * 8 // bits
+    shifts = (np.arange(per) * bits).astype(np.uint32)
+    f = (items.astype(np.uint32)[..., None] >> shifts) & np.uint32((1 << bits) - 1)
+    return f.reshape(items.shape[:-1] + (items.shape[-1] * per,))
+
+
+def pack_fields(fields, bits, dtype):
+    per = np.dtype(dtype).itemsize * 8 // bits
+    f = fields.reshape(fields.shape[:-1] + (fields.shape[-1] // per, per)).astype(np.uint32)
+    shifts = (np.arange(per) * bits).astype(np.uint32)
+    return (f << shifts).sum(axis=-1).astype(np.uint32).astype(dtype)
+
+
+def test_column_major_contract_checks():
+    scheme = QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([32, 32]))
+    # logical (64, 128), packed along the rows: data [64 / 8, 128] with stride 1 on the row dim
+    data = TensorHandleRef.from_raw_parts(0x1000, (8, 128), 4, strides=(1, 8))
+    scale = TensorHandleRef.from_raw_parts(0x2000, (2, 4), 4)
+    h = MatmulInputHandleRef.quantized(data, scale, (64, 128), scheme)
+    assert h.col_major
+    with pytest.raises(ValueError):     # the row block must hold whole stored items
+        MatmulInputHandleRef.quantized(data, TensorHandleRef.from_raw_parts(0x2000, (16, 4), 4), (64, 128),
+                                       QuantScheme(value=QuantValue.Q4S, level=QuantLevel.block([4, 32])))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fname", list(FLOATS))
+@pytest.mark.parametrize("value,store", [(QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4S, QuantStore.U32),
+                                         (QuantValue.Q2F, QuantStore.U32), (QuantValue.E2M1, QuantStore.Native),
+                                         (QuantValue.Q8S, QuantStore.Native)])
+def test_strided_quantized_tensors(fname, value, store):
+    """The quantized tensor as a transposed view (memory laid out [n / num_quants, rows]): quantize writes it and
+    dequantize reads it through the strides, like the reference's `linear_view(output, 1)`."""
+    import torch
+
+    from cubek_b200 import ComputeClient, dequantize, quantize
+    from tests._util import assert_bits_equal, code_dtype, elem_of, empty_device, to_device, to_numpy
+
+    F = FLOATS[fname]
+    H = TensorHandleRef.from_torch
+    for level in (QuantLevel.Tensor, QuantLevel.block([32])):
+        scheme = QuantScheme(value=value, store=store, level=level)
+        x = random_tensor((48, 256), F, 8, "normal")
+        scale = O.compute_scales(x, scheme)
+        want_codes, want_scale = O.quantize(x, scale, scheme)
+        packed = scheme.packed_shape(x.shape)
+        memory = empty_device((packed[1], packed[0]), code_dtype(scheme))
+        view = memory.t()                                   # shape `packed`, strides (1, rows)
+        assert tuple(view.shape) == tuple(packed) and not view.is_contiguous()
+        dos = empty_device(scale.shape, np.float32)
+        client = ComputeClient.current()
+        dx, dscale = to_device(x), to_device(scale)        # kept alive: handles only borrow
+        quantize.launch_ref(client, H(dx), H(view), H(dscale), H(dos), scheme, elem_of(F))
+        torch.cuda.synchronize()
+        assert_bits_equal(np.ascontiguousarray(to_numpy(memory, code_dtype(scheme)).T), want_codes, "codes through strides")
+        assert_bits_equal(to_numpy(dos, np.float32), want_scale, "out_scale")
+        out = empty_device(x.shape, F)
+        dequantize.launch_ref(client, H(view), H(out), H(dos), scheme, elem_of(F))
+        torch.cuda.synchronize()
+        assert_bits_equal(to_numpy(out, F), O.dequantize(want_codes, want_scale, scheme, F), "restored through strides")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("value,store", [(QuantValue.Q8S, QuantStore.U32), (QuantValue.Q4S, QuantStore.U32),
+                                         (QuantValue.Q2S, QuantStore.U32), (QuantValue.E2M1, QuantStore.Native),
+                                         (QuantValue.E4M3, QuantStore.Native)])
+@pytest.mark.parametrize("batch", [(), (3,)])
+def test_column_major_operand_into_contiguous(value, store, batch):
+    """W is quantized as its transpose (rows of W^T are columns of W), handed over as a column-major operand and
+    re-packed along the columns; field for field it must be the oracle's codes, transposed."""
+    import torch
+
+    from cubek_b200 import ComputeClient
+    from tests._util import assert_bits_equal, code_dtype, empty_device, gpu_quantize_dynamic, to_device, to_numpy
+
+    rows, cols = 96, 160
+    scheme = QuantScheme(value=value, store=store, level=QuantLevel.block([32]))
+    nq, bits = scheme.num_quants(), scheme.value.size_bits()
+    cdt = code_dtype(scheme)
+    wt = random_tensor(batch + (cols, rows), np.float32, 9, "normal")               # W^T, contiguous
+    codes_t, scales_t = gpu_quantize_dynamic(wt, scheme)                            # [.., cols, rows / nq]
+    o_codes_t, _ = O.quantize_dynamic(wt, scheme)
+    assert_bits_equal(codes_t, o_codes_t, "codes of the transpose")
+    d_codes_t = to_device(codes_t)
+    d_scales_t = to_device(scales_t)
+    data = TensorHandleRef.from_torch(d_codes_t.transpose(-1, -2))                  # [.., rows / nq, cols], stride 1 on rows
+    scale = TensorHandleRef.from_torch(d_scales_t.transpose(-1, -2))                # [.., rows / 32, cols]
+    operand_scheme = QuantScheme(value=value, store=store, level=QuantLevel.block([32, 1]))
+    h = MatmulInputHandleRef.quantized(data, scale, batch + (rows, cols), operand_scheme)
+    assert h.col_major
+    out = empty_device(batch + (rows, cols // nq), cdt)
+    h2 = h.into_contiguous(ComputeClient.current(), TensorHandleRef.from_torch(out))
+    torch.cuda.synchronize()
+    assert not h2.col_major
+    fields_t = unpack_fields(codes_t.view(np.uint8) if cdt.itemsize == 1 else codes_t, bits)      # [.., cols, rows]
+    want = pack_fields(np.swapaxes(fields_t, -1, -2), bits, np.uint8 if cdt.itemsize == 1 else np.uint32)
+    got = to_numpy(out, cdt)
+    assert_bits_equal(got.view(np.uint8) if cdt.itemsize == 1 else got, want, "re-packed codes")
