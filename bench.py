@@ -557,6 +557,28 @@ def check_against_oracle(ctx: Ctx, sset: ShardedSet, rows_per_tensor=4, max_tens
             "scale_bits_agree_across_ranks": int(t[2]) == 0}
 
 
+def count_ties(ctx: Ctx, sset: ShardedSet, max_elements=1 << 27):
+    """How many quotients x / scale, rounded to the input type as the kernels do, fall on an exact half: the only
+    inputs on which the rounding rule of the reference's back end (half to even here, half away from zero in the
+    alternative build) changes a code.  Counted with torch on the first tensors of this rank, after a step."""
+    torch = ctx.torch
+    ties = seen = 0
+    for x, sc in zip(sset.xs, sset.scales):
+        if seen >= max_elements:
+            break
+        s = sc.to(x.dtype)
+        if not sset.per_tensor:
+            s = s.repeat_interleave(sset.scheme.level.block_size.as_slice()[-1], dim=-1)
+        q = (x / s).float().abs()
+        ties += int(((q - q.floor()) == 0.5).sum().item())
+        seen += x.numel()
+        del q, s
+    t = torch.tensor([ties, seen], dtype=torch.int64, device=ctx.dev)
+    if ctx.world > 1:
+        ctx.dist.all_reduce(t)
+    return {"ties": int(t[0]), "elements_examined": int(t[1]), "fraction": float(t[0]) / max(int(t[1]), 1)}
+
+
 def llama_input(ctx):
     torch = ctx.torch
 
@@ -657,6 +679,7 @@ def run_weight_set(ctx: Ctx, args):
         s.step()
         ctx.torch.cuda.synchronize()
         parity[label] = check_against_oracle(ctx, s, rows_per_tensor=4)
+        parity[label]["rounding_ties"] = count_ties(ctx, s)
     table = phase_table(ctx, sets, max(args.steps // 2, 2))
     per_scheme = {}
     for label, s in sets:
@@ -686,6 +709,7 @@ def run_single_config(ctx: Ctx, args, workload, batch, headline):
     sset.step()
     ctx.torch.cuda.synchronize()
     parity = check_against_oracle(ctx, sset, rows_per_tensor=6, max_tensors=2)
+    parity["rounding_ties"] = count_ties(ctx, sset)
     table = phase_table(ctx, [("batch", sset)], steps) if not flush else {}
     if flush:
         for name, fn, nbytes in sset.phases():
@@ -715,7 +739,7 @@ def run_single_config(ctx: Ctx, args, workload, batch, headline):
         "two_call_flow_per_tensor": two_call,
         "l2": "flushed between steps (read-only pass over 512 MB, outside the event pairs)" if flush
               else "per-rank inputs of a step exceed twice the L2",
-        "parity_checked": parity["ok"],
+        "parity_checked": parity["ok"], "rounding_ties": parity["rounding_ties"],
     }
     rec.update(summary=summary, kernels=table, parity={"batch": parity}, sets=[("batch", sset)])
     return rec

@@ -9,4 +9,4 @@ from .scheme import (BlockSize, ElemType, Flex32, QuantLevel, QuantMode, QuantPa
                      QuantStore, QuantValue)
 from .tensor import ComputeClient, TensorHandleRef  # noqa: F401
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"

@@ -12,6 +12,8 @@ from .scheme import QuantScheme
 from .tensor import TensorHandleRef
 
 LIB_PATH = Path(__file__).resolve().parent / "libcubek_quant_b200.so"
+# the build that rounds halves away from zero (`python -m cubek_b200.build --round-half-away`)
+LIB_PATH_HALF_AWAY = Path(__file__).resolve().parent / "libcubek_quant_b200_half_away.so"
 
 QK_OK = 0
 QK_ERR_UNSUPPORTED_SCHEME = 1
@@ -118,19 +120,24 @@ EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 TESTING_SYMBOLS = tuple(_TESTING_SIGNATURES)
 
 
+def load(path: Path) -> C.CDLL:
+    """Load one build of the library and bind every entry point.  Raises ``OSError`` with a build hint when the
+    file is missing (there is no CPU fallback)."""
+    if not Path(path).exists():
+        raise OSError(f"{path} not found: build it with `python -m cubek_b200.build` (there is no CPU fallback)")
+    handle = C.CDLL(str(path))
+    for name, (res, args) in {**_SIGNATURES, **_TESTING_SIGNATURES}.items():
+        fn = getattr(handle, name)
+        fn.restype = res
+        fn.argtypes = args
+    return handle
+
+
 def lib() -> C.CDLL:
-    """Load the library once.  Raises ``OSError`` with a build hint when it is missing."""
+    """The library (round-half-to-even build), loaded once."""
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
-            raise OSError(f"{LIB_PATH} not found: build it with `python -m cubek_b200.build` "
-                          "(there is no CPU fallback)")
-        handle = C.CDLL(str(LIB_PATH))
-        for name, (res, args) in {**_SIGNATURES, **_TESTING_SIGNATURES}.items():
-            fn = getattr(handle, name)
-            fn.restype = res
-            fn.argtypes = args
-        _lib = handle
+        _lib = load(LIB_PATH)
     return _lib
 
 

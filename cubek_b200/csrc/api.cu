@@ -1139,7 +1139,11 @@ const char *qk_strerror(int status)
     }
 }
 
-const char *qk_version(void) { return "cubek-quant-b200 0.1.0 (sm_100a)"; }
+#ifdef QK_ROUND_HALF_AWAY
+const char *qk_version(void) { return "cubek-quant-b200 0.2.0 (sm_100a, round half away from zero)"; }
+#else
+const char *qk_version(void) { return "cubek-quant-b200 0.2.0 (sm_100a)"; }
+#endif
 
 uint64_t qk_launch_count(void) { return g_launches.load(); }
 

@@ -177,10 +177,19 @@ __device__ __forceinline__ float fmax3(float a, float b, float c)
 
 // ---- scale arithmetic -----------------------------------------------------------------
 
-// clamp(round(t)) with round-half-to-even; a NaN quotient (0/0) gives code 0.
+// `Line::round` of the reference (crates/cubek-quant/src/quantize.rs:27) is lowered by its external JIT back end.
+// The default here is round-half-to-even; a build with -DQK_ROUND_HALF_AWAY rounds halves away from zero instead
+// (every unit then takes the reference-arithmetic route: the shortcut arithmetic is built on half-to-even).
+#ifdef QK_ROUND_HALF_AWAY
+#define QK_ROUND(t) roundf(t)
+#else
+#define QK_ROUND(t) rintf(t)
+#endif
+
+// clamp(round(t)); a NaN quotient (0/0) gives code 0.
 __device__ __forceinline__ float round_clamp(float t, float lo, float hi)
 {
-    float r = rintf(t);
+    float r = QK_ROUND(t);
     r = fminf(fmaxf(r, lo), hi);
     return (t != t) ? 0.0f : r;
 }

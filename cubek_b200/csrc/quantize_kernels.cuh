@@ -204,7 +204,14 @@ __device__ __forceinline__ bool scale_is_safe(float s)
 // Every kind takes the shortcuts.  E5M2 clamps at +-57344, beyond the window of the integer kinds: for
 // 16-bit inputs the half-precision shortcut was checked on the host up to |x/s| = 2^18, overflow of
 // f16 to infinity included (the clamp then gives the bound either way).
-template <int FDT, int KIND> __host__ __device__ constexpr bool kind_allows_fast() { return true; }
+template <int FDT, int KIND> __host__ __device__ constexpr bool kind_allows_fast()
+{
+#ifdef QK_ROUND_HALF_AWAY
+    return false;   // the shortcuts round halves to even
+#else
+    return true;
+#endif
+}
 
 // ---- packing of integral f32 values -----------------------------------------------------------
 // `c` holds integral (or to-be-rounded, already clamped) f32 values in element order.

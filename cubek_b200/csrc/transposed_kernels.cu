@@ -142,7 +142,8 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const QuantArg
             const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
             const float sc = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
             uint32_t w[OW];
-            if (!a.force_exact && scale_is_safe(sc)) quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], sc, a.lo, a.hi, w);
+            if (kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(sc))
+                quantize_unit_fast<FDT, KIND, UB, CLAMP, DYN>(raw[k], sc, a.lo, a.hi, w);
             else quantize_unit_exact<FDT, KIND, UB>(raw[k], sc, a.lo, a.hi, w);
 #pragma unroll
             for (int j = 0; j < OW; ++j) codes_s[lane * NR + k][warp * OW + j] = w[j];

@@ -13,7 +13,9 @@
  * and :272-283).  The oracle is therefore pinned against (1) that tolerance contract on
  * the reference's 24 test cases, and (2) an independent NumPy/ml_dtypes restatement.
  * The choices the reference leaves to its JIT back end are fixed here as:
- *   - `Line::round` is round-half-to-even (nearbyintf in the default rounding mode);
+ *   - `Line::round` is round-half-to-even (nearbyintf in the default rounding mode); built with
+ *     -DOQ_ROUND_HALF_AWAY (liboracle_half_away.so) it rounds halves away from zero instead, the one
+ *     other lowering a back end could plausibly choose;
  *   - arithmetic on f16 / bf16 lines is the correctly rounded result in that type
  *     (computed as the f32 operation followed by one round-to-nearest-even narrowing;
  *     f32 carries >= 2p+2 bits for both types, so the double rounding is innocuous);
@@ -277,7 +279,11 @@ static int64_t numel(const int64_t *shape, int rank)
 static inline float quantize_value(float x, float s, int fdt, float lo, float hi)
 {
     float t = round_to(fdt, x / s);
+#ifdef OQ_ROUND_HALF_AWAY
+    float r = roundf(t);        /* the other plausible lowering of `Line::round`: halves away from zero */
+#else
     float r = nearbyintf(t);
+#endif
     if (!(r == r)) return 0.f;
     r = r < lo ? lo : r;
     r = r > hi ? hi : r;

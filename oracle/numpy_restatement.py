@@ -46,7 +46,14 @@ def compute_scales(x: np.ndarray, scheme: QuantScheme) -> np.ndarray:
     return out
 
 
-def _quantize_values(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme):
+def _round(t, rounding):
+    if rounding == "even":
+        return np.rint(t)
+    # halves away from zero; the sum is formed in f64, where it is exact for every f32 `t`
+    return np.float32(np.copysign(np.floor(np.abs(np.float64(t)) + 0.5), t)) if np.isfinite(t) else t
+
+
+def _quantize_values(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme, rounding: str = "even"):
     """Integral clamped values (float32) and out_scale."""
     F = x.dtype
     lo, hi = scheme.value.range()
@@ -58,13 +65,13 @@ def _quantize_values(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme):
         for idx in itertools.product(*[range(s) for s in x.shape]):
             s = s_f[0] if blk is None else s_f[_scale_index(idx, blk)]
             t = (np.float32(x[idx]) / np.float32(s)).astype(F).astype(np.float32)
-            r = np.rint(t)
+            r = _round(t, rounding)
             c[idx] = 0.0 if np.isnan(r) else min(max(r, np.float32(lo)), np.float32(hi))
     return c, s_fs
 
 
-def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme):
-    c, s_fs = _quantize_values(x, scale, scheme)
+def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme, rounding: str = "even"):
+    c, s_fs = _quantize_values(x, scale, scheme, rounding)
     nq = scheme.num_quants()
     flat = c.reshape(-1, nq)
     if scheme.store == QuantStore.U32:

@@ -18,6 +18,7 @@ from cubek_b200.scheme import ElemType, QuantParam, QuantScheme, QuantStore, Qua
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "liboracle.so"
+LIB_PATH_HALF_AWAY = HERE / "liboracle_half_away.so"
 
 bfloat16 = ml_dtypes.bfloat16
 
@@ -39,20 +40,24 @@ def elem_type(dtype) -> ElemType:
 
 def build(force: bool = False) -> Path:
     src = HERE / "cubek_quant_oracle.c"
-    if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < src.stat().st_mtime:
-        subprocess.run(["make", "-C", str(HERE), "-B", "liboracle.so"], check=True, capture_output=True)
+    for path in (LIB_PATH, LIB_PATH_HALF_AWAY):
+        if force or not path.exists() or path.stat().st_mtime < src.stat().st_mtime:
+            subprocess.run(["make", "-C", str(HERE), "-B", path.name], check=True, capture_output=True)
     return LIB_PATH
 
 
-_lib = None
+_libs = {}
 
 
-def lib() -> C.CDLL:
-    global _lib
-    if _lib is None:
-        if not LIB_PATH.exists():
+def lib(rounding: str = "even") -> C.CDLL:
+    """The oracle library: ``rounding="even"`` (the default restatement) or ``"away"`` (halves away from zero)."""
+    if rounding not in ("even", "away"):
+        raise ValueError(rounding)
+    if rounding not in _libs:
+        path = LIB_PATH if rounding == "even" else LIB_PATH_HALF_AWAY
+        if not path.exists():
             build()
-        h = C.CDLL(str(LIB_PATH))
+        h = C.CDLL(str(path))
         i64p, u8p = C.POINTER(C.c_int64), C.POINTER(C.c_uint8)
         h.oq_compute_scales.restype = C.c_int
         h.oq_compute_scales.argtypes = [C.c_void_p, C.c_int, i64p, C.c_int, C.c_int, C.c_int, u8p, C.c_int,
@@ -71,8 +76,8 @@ def lib() -> C.CDLL:
         for name in ("oq_e2m1_to_f32", "oq_e4m3_to_f32", "oq_e5m2_to_f32"):
             getattr(h, name).restype = C.c_float
             getattr(h, name).argtypes = [C.c_uint8]
-        _lib = h
-    return _lib
+        _libs[rounding] = h
+    return _libs[rounding]
 
 
 class OracleError(AssertionError):
@@ -128,7 +133,7 @@ def compute_scales(x: np.ndarray, scheme: QuantScheme, out: np.ndarray | None = 
 
 
 def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme, out: np.ndarray | None = None,
-             out_scale: np.ndarray | None = None) -> Tuple[np.ndarray, np.ndarray]:
+             out_scale: np.ndarray | None = None, rounding: str = "even") -> Tuple[np.ndarray, np.ndarray]:
     """``quantize::launch_ref``: returns (quantized tensor, out_scale typed as the param)."""
     x = np.ascontiguousarray(x)
     fdt = elem_type(x.dtype)
@@ -140,7 +145,7 @@ def quantize(x: np.ndarray, scale: np.ndarray, scheme: QuantScheme, out: np.ndar
     out = _buffer(out, tuple(scheme.packed_shape(x.shape)), code_dtype(scheme))
     out_scale = _buffer(out_scale, tuple(scale.shape), np_dtype(int(scheme.param)))
     strides = _elem_strides(scale) if level else [0] * x.ndim
-    _check(lib().oq_quantize(x.ctypes.data, int(fdt), _i64(x.shape), x.ndim, scale.ctypes.data, _i64(strides),
+    _check(lib(rounding).oq_quantize(x.ctypes.data, int(fdt), _i64(x.shape), x.ndim, scale.ctypes.data, _i64(strides),
                              int(scheme.value), int(scheme.store), int(scheme.param), level, blk, brank,
                              out.ctypes.data, out_scale.ctypes.data))
     return out, out_scale
@@ -162,9 +167,9 @@ def dequantize(values: np.ndarray, params: np.ndarray, scheme: QuantScheme, out_
     return out
 
 
-def quantize_dynamic(x: np.ndarray, scheme: QuantScheme):
+def quantize_dynamic(x: np.ndarray, scheme: QuantScheme, rounding: str = "even"):
     """compute_scales followed by quantize."""
-    return quantize(x, compute_scales(x, scheme), scheme)
+    return quantize(x, compute_scales(x, scheme), scheme, rounding=rounding)
 
 
 def max_threads() -> int:

@@ -40,6 +40,10 @@ def _built_libraries():
         from cubek_b200.build import build
 
         build()
+    if not _ffi.LIB_PATH_HALF_AWAY.exists():
+        from cubek_b200.build import build
+
+        build(half_away=True)
     from oracle import oracle
 
     oracle.build()
