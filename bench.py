@@ -762,15 +762,14 @@ def run_e2e(ctx: Ctx, args, sset: ShardedSet, what: str):
     h_scales = [torch.empty_like(sset.scales[i], device="cpu").pin_memory() for i in take]
     h_out = [torch.empty_like(sset.outs[i], device="cpu").pin_memory() for i in take]
     H = TensorHandleRef.from_torch
-    cin, ccodes, cscales, cout = ([_ffi.CTensor(H(t)) for t in ts] for ts in (h_in, h_codes, h_scales, h_out))
+    cin, ccodes, cscales, cout = (_ffi.CTensorArray([H(t) for t in ts]) for ts in (h_in, h_codes, h_scales, h_out))
     sch = _ffi.c_scheme(scheme)
-    need = max(int(lib.qk_host_roundtrip_staging_bytes(c.ref(), sch, int(elem))) for c in cin)
+    need = int(lib.qk_host_roundtrip_staging_bytes_batch(cin.count, cin.array, sch, int(elem)))
     staging = torch.empty(need, dtype=torch.uint8, device=ctx.dev)
 
     def step():
-        for i in range(len(take)):
-            _ffi.check(lib.qk_roundtrip_host(cin[i].ref(), ccodes[i].ref(), cscales[i].ref(), cout[i].ref(), sch,
-                                             int(elem), staging.data_ptr(), need, ctx.local_rank))
+        _ffi.check(lib.qk_roundtrip_host_batch(cin.count, cin.array, ccodes.array, cscales.array, cout.array, sch,
+                                               int(elem), staging.data_ptr(), need, ctx.local_rank))
 
     def wall(fn, reps):
         fn()
@@ -814,7 +813,8 @@ def run_e2e(ctx: Ctx, args, sset: ShardedSet, what: str):
                             "note": "the same host<->device copies with no kernels, both directions at once: the "
                                     "ceiling set by the host link and, with several ranks, by host memory"},
             "fraction_of_copy_ceiling": round(copy_secs / secs, 3),
-            "api": "qk_roundtrip_host (pinned host buffers, 4-slot pipelined copies); bytes per step are this rank's"}
+            "api": "qk_roundtrip_host_batch (pinned host buffers; the slices of all tensors pass through one ring of 4 "
+                   "staging slots, copies in both directions overlapping the kernels); bytes per step are this rank's"}
 
 
 def run_reduce_record(ctx: Ctx, steps):

@@ -99,6 +99,9 @@ _SIGNATURES = {
     "qk_roundtrip_host": (C.c_int, [C.POINTER(QkTensor)] * 4 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
                                                                C.c_size_t, C.c_int]),
     "qk_host_roundtrip_staging_bytes": (C.c_size_t, [C.POINTER(QkTensor), C.POINTER(QkScheme), C.c_int]),
+    "qk_roundtrip_host_batch": (C.c_int, [C.c_int] + [C.POINTER(QkTensor)] * 4 + [C.POINTER(QkScheme), C.c_int, C.c_void_p,
+                                                      C.c_size_t, C.c_int]),
+    "qk_host_roundtrip_staging_bytes_batch": (C.c_size_t, [C.c_int, C.POINTER(QkTensor), C.POINTER(QkScheme), C.c_int]),
     "qk_into_contiguous_packed": (C.c_int, [C.POINTER(QkTensor)] * 2 + [C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_void_p]),
     "qk_strerror": (C.c_char_p, [C.c_int]),
     "qk_version": (C.c_char_p, []),

@@ -387,8 +387,8 @@ static bool aligned(const void *p, unsigned a) { return (reinterpret_cast<uintpt
 // last dim, contiguous scales and vector-aligned bases.  Picks the unit (64 bytes when blocks
 // and the tensor allow, else the smallest unit of the kind); returns log2(units per block), -1
 // for per tensor, or -2 when the call has to take the layout-general kernels.
-// `*sub` (optional) is set to the blocks per unit: 2 when the fused form may run 16-bit blocks of 32 bytes as halves
-// of 64-byte units (f32 params, scales 8-byte aligned), else 1.
+// `*sub` (optional) is set to the blocks per unit: 2 when 16-bit blocks of 32 bytes may run as halves of 64-byte
+// units (f32 params, scales out 8-byte aligned, given scales 4-byte aligned), else 1.
 static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, const QkTensor *out,
                             const QkTensor *scale, const QkTensor *out_scale, int *unit_bytes, int *sub = nullptr,
                             bool fused = false, int param = QK_F32)
@@ -421,8 +421,8 @@ static int fast_quantize_lg(const Geometry &g, int fdt, const QkTensor *in, cons
         if (!aligned(out->ptr, out_align)) continue;
         *unit_bytes = ub;
         if (g.per_tensor) return -1;
-        if (sub && fused && ub == 64 && esz == 2 && U == 2 * g.B && !g.blocks_2d && !strided_rows && param == QK_F32 &&
-            32 >= min_unit_bytes(fdt, g.kind) && out_scale && aligned(out_scale->ptr, 8)) {
+        if (sub && (fused || (scale && aligned(scale->ptr, 4))) && ub == 64 && esz == 2 && U == 2 * g.B && !g.blocks_2d &&
+            !strided_rows && param == QK_F32 && 32 >= min_unit_bytes(fdt, g.kind) && out_scale && aligned(out_scale->ptr, 8)) {
             *sub = 2;
             return 0;
         }

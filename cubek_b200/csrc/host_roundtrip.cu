@@ -121,24 +121,57 @@ extern "C" {
 
 size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *scheme, int input_dtype)
 {
-    if (!scheme) return 0;
-    Plan p = make_plan(input, scheme, input_dtype);
-    if (!p.ok) return 0;
-    const int slots = p.sliced ? slot_count() : 1;
-    return p.slot_bytes * slots;
+    return qk_host_roundtrip_staging_bytes_batch(1, input, scheme, input_dtype);
+}
+
+size_t qk_host_roundtrip_staging_bytes_batch(int count, const QkTensor *inputs, const QkScheme *scheme, int input_dtype)
+{
+    if (!scheme || !inputs || count < 1) return 0;
+    size_t slot = 0;
+    bool sliced = false;
+    long long nslices = 0;
+    for (int i = 0; i < count; ++i) {
+        const Plan p = make_plan(&inputs[i], scheme, input_dtype);
+        if (!p.ok) return 0;
+        if (p.slot_bytes > slot) slot = p.slot_bytes;
+        sliced = sliced || p.sliced;
+        nslices += (p.rows + p.slice_rows - 1) / p.slice_rows;
+    }
+    const int slots = (nslices > 1) ? slot_count() : 1;
+    return slot * slots;
 }
 
 int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTensor *out_scale,
                       const QkTensor *restored, const QkScheme *scheme, int input_dtype, void *staging,
                       size_t staging_bytes, int device)
 {
-    if (!input || !codes || !out_scale || !restored || !scheme || !staging) return QK_ERR_NULL;
+    if (!input || !codes || !out_scale || !restored) return QK_ERR_NULL;
+    return qk_roundtrip_host_batch(1, input, codes, out_scale, restored, scheme, input_dtype, staging, staging_bytes, device);
+}
+
+int qk_roundtrip_host_batch(int count, const QkTensor *inputs, const QkTensor *codes, const QkTensor *out_scales,
+                            const QkTensor *restored, const QkScheme *scheme, int input_dtype, void *staging,
+                            size_t staging_bytes, int device)
+{
+    if (count < 0) return QK_ERR_SHAPE;
+    if (count == 0) return QK_OK;
+    if (!inputs || !codes || !out_scales || !restored || !scheme || !staging) return QK_ERR_NULL;
     if (device < 0 || device >= 64) return QK_ERR_SHAPE;
-    Plan p = make_plan(input, scheme, input_dtype);
-    if (!p.ok) return QK_ERR_SHAPE;
-    const int slots = p.sliced ? slot_count() : 1;
-    if (staging_bytes < p.slot_bytes * slots) return QK_ERR_WORKSPACE;
-    if (!input->ptr || !codes->ptr || !out_scale->ptr || !restored->ptr) return QK_ERR_NULL;
+    if (count > 4096) return QK_ERR_TOO_LARGE;
+    // Every tensor's slices pass through the same ring of staging slots, so the upload of one tensor's first slice
+    // overlaps the downloads of the previous tensor's last ones (tensors of one slice would otherwise run
+    // upload, kernels and download strictly one after the other).
+    size_t slot_bytes = 0;
+    long long nslices = 0;
+    for (int i = 0; i < count; ++i) {
+        const Plan p = make_plan(&inputs[i], scheme, input_dtype);
+        if (!p.ok) return QK_ERR_SHAPE;
+        if (!inputs[i].ptr || !codes[i].ptr || !out_scales[i].ptr || !restored[i].ptr) return QK_ERR_NULL;
+        if (p.slot_bytes > slot_bytes) slot_bytes = p.slot_bytes;
+        nslices += (p.rows + p.slice_rows - 1) / p.slice_rows;
+    }
+    const int slots = (nslices > 1) ? slot_count() : 1;
+    if (staging_bytes < slot_bytes * slots) return QK_ERR_WORKSPACE;
 
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return QK_ERR_CUDA + (int)e;
@@ -156,76 +189,80 @@ int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTens
         streams = ds.stream;
     }
 
-    const int rank = input->rank;
     const int fsize = dtype_size(input_dtype);
     const int psize = dtype_size(scheme->param);
     const int csize = scheme->store == QK_STORE_U32 ? 4 : 1;
     int status = QK_OK;
     long long slice = 0;
-    for (long long r0 = 0; r0 < p.rows && status == QK_OK; r0 += p.slice_rows, ++slice) {
-        const long long nr = (p.rows - r0 < p.slice_rows) ? p.rows - r0 : p.slice_rows;
-        const int slot = (int)(slice % slots);
-        cudaStream_t st = streams[slot];
-        char *base = static_cast<char *>(staging) + (size_t)slot * p.slot_bytes;
+    for (int ti = 0; ti < count && status == QK_OK; ++ti) {
+        const QkTensor *input = &inputs[ti];
+        const Plan p = make_plan(input, scheme, input_dtype);
+        const int rank = input->rank;
+        for (long long r0 = 0; r0 < p.rows && status == QK_OK; r0 += p.slice_rows, ++slice) {
+            const long long nr = (p.rows - r0 < p.slice_rows) ? p.rows - r0 : p.slice_rows;
+            const int slot = (int)(slice % slots);
+            cudaStream_t st = streams[slot];
+            char *base = static_cast<char *>(staging) + (size_t)slot * slot_bytes;
 
-        // The slot's previous work is ordered before this slice by stream order.
-        e = cudaMemcpyAsync(base + p.in_off, static_cast<const char *>(input->ptr) + (size_t)r0 * p.in_row,
-                            (size_t)nr * p.in_row, cudaMemcpyHostToDevice, st);
-        if (e != cudaSuccess) { status = QK_ERR_CUDA + (int)e; break; }
+            // The slot's previous work is ordered before this slice by stream order.
+            e = cudaMemcpyAsync(base + p.in_off, static_cast<const char *>(input->ptr) + (size_t)r0 * p.in_row,
+                                (size_t)nr * p.in_row, cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) { status = QK_ERR_CUDA + (int)e; break; }
 
-        // Device views of this slice.  A sliced tensor is [nr, cols]; a single slice keeps the
-        // caller's shape so that N-d blocks still apply.
-        int64_t shp_in[QK_MAX_RANK], shp_code[QK_MAX_RANK], shp_scale[QK_MAX_RANK];
-        int64_t str_in[QK_MAX_RANK], str_code[QK_MAX_RANK], str_scale[QK_MAX_RANK];
-        int vr;
-        QkScheme sch = *scheme;
-        if (!p.sliced) {
-            vr = rank;
-            for (int d = 0; d < rank; ++d) {
-                shp_in[d] = input->shape[d];
-                shp_code[d] = codes->shape[d];
+            // Device views of this slice.  A sliced tensor is [nr, cols]; a single slice keeps the
+            // caller's shape so that N-d blocks still apply.
+            int64_t shp_in[QK_MAX_RANK], shp_code[QK_MAX_RANK], shp_scale[QK_MAX_RANK];
+            int64_t str_in[QK_MAX_RANK], str_code[QK_MAX_RANK], str_scale[QK_MAX_RANK];
+            int vr;
+            QkScheme sch = *scheme;
+            if (!p.sliced) {
+                vr = rank;
+                for (int d = 0; d < rank; ++d) {
+                    shp_in[d] = input->shape[d];
+                    shp_code[d] = codes[ti].shape[d];
+                }
+                if (p.per_tensor) { shp_scale[0] = 1; }
+                else for (int d = 0; d < rank; ++d) shp_scale[d] = out_scales[ti].shape[d];
+            } else {
+                vr = 2;
+                shp_in[0] = nr; shp_in[1] = p.cols;
+                shp_code[0] = nr; shp_code[1] = p.cols / p.nq;
+                shp_scale[0] = nr; shp_scale[1] = p.scales_per_row;
+                sch.block_rank = 1;
+                sch.block[0] = scheme->block[scheme->block_rank - 1];
             }
-            if (p.per_tensor) { shp_scale[0] = 1; }
-            else for (int d = 0; d < rank; ++d) shp_scale[d] = out_scale->shape[d];
-        } else {
-            vr = 2;
-            shp_in[0] = nr; shp_in[1] = p.cols;
-            shp_code[0] = nr; shp_code[1] = p.cols / p.nq;
-            shp_scale[0] = nr; shp_scale[1] = p.scales_per_row;
-            sch.block_rank = 1;
-            sch.block[0] = scheme->block[scheme->block_rank - 1];
-        }
-        const int sr = p.per_tensor ? 1 : vr;
-        auto fill_strides = [](int64_t *str, const int64_t *shp, int r) {
-            int64_t acc = 1;
-            for (int d = r - 1; d >= 0; --d) { str[d] = acc; acc *= shp[d]; }
-        };
-        fill_strides(str_in, shp_in, vr);
-        fill_strides(str_code, shp_code, vr);
-        fill_strides(str_scale, shp_scale, sr);
-        QkTensor t_in{base + p.in_off, vr, shp_in, str_in, fsize};
-        QkTensor t_code{base + p.code_off, vr, shp_code, str_code, csize};
-        QkTensor t_scale{base + p.scale_off, sr, shp_scale, str_scale, psize};
-        QkTensor t_out{base + p.out_off, vr, shp_in, str_in, fsize};
+            const int sr = p.per_tensor ? 1 : vr;
+            auto fill_strides = [](int64_t *str, const int64_t *shp, int r) {
+                int64_t acc = 1;
+                for (int d = r - 1; d >= 0; --d) { str[d] = acc; acc *= shp[d]; }
+            };
+            fill_strides(str_in, shp_in, vr);
+            fill_strides(str_code, shp_code, vr);
+            fill_strides(str_scale, shp_scale, sr);
+            QkTensor t_in{base + p.in_off, vr, shp_in, str_in, fsize};
+            QkTensor t_code{base + p.code_off, vr, shp_code, str_code, csize};
+            QkTensor t_scale{base + p.scale_off, sr, shp_scale, str_scale, psize};
+            QkTensor t_out{base + p.out_off, vr, shp_in, str_in, fsize};
 
-        status = qk_quantize_dynamic(&t_in, &t_code, &t_scale, &sch, input_dtype, base + p.ws_off,
-                                     p.slot_bytes - p.ws_off, st);
-        if (status != QK_OK) break;
-        status = qk_dequantize(&t_code, &t_out, &t_scale, &sch, input_dtype, st);
-        if (status != QK_OK) break;
+            status = qk_quantize_dynamic(&t_in, &t_code, &t_scale, &sch, input_dtype, base + p.ws_off,
+                                         p.slot_bytes - p.ws_off, st);
+            if (status != QK_OK) break;
+            status = qk_dequantize(&t_code, &t_out, &t_scale, &sch, input_dtype, st);
+            if (status != QK_OK) break;
 
-        e = cudaMemcpyAsync(static_cast<char *>(codes->ptr) + (size_t)r0 * p.code_row, base + p.code_off,
-                            (size_t)nr * p.code_row, cudaMemcpyDeviceToHost, st);
-        if (e == cudaSuccess) {
-            const size_t sbytes = p.sliced ? (size_t)nr * p.scale_row : (size_t)p.slice_scales * psize;
-            const size_t soff = p.sliced ? (size_t)r0 * p.scale_row : 0;
-            e = cudaMemcpyAsync(static_cast<char *>(out_scale->ptr) + soff, base + p.scale_off, sbytes,
-                                cudaMemcpyDeviceToHost, st);
+            e = cudaMemcpyAsync(static_cast<char *>(codes[ti].ptr) + (size_t)r0 * p.code_row, base + p.code_off,
+                                (size_t)nr * p.code_row, cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) {
+                const size_t sbytes = p.sliced ? (size_t)nr * p.scale_row : (size_t)p.slice_scales * psize;
+                const size_t soff = p.sliced ? (size_t)r0 * p.scale_row : 0;
+                e = cudaMemcpyAsync(static_cast<char *>(out_scales[ti].ptr) + soff, base + p.scale_off, sbytes,
+                                    cudaMemcpyDeviceToHost, st);
+            }
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(static_cast<char *>(restored[ti].ptr) + (size_t)r0 * p.out_row, base + p.out_off,
+                                    (size_t)nr * p.out_row, cudaMemcpyDeviceToHost, st);
+            if (e != cudaSuccess) status = QK_ERR_CUDA + (int)e;
         }
-        if (e == cudaSuccess)
-            e = cudaMemcpyAsync(static_cast<char *>(restored->ptr) + (size_t)r0 * p.out_row, base + p.out_off,
-                                (size_t)nr * p.out_row, cudaMemcpyDeviceToHost, st);
-        if (e != cudaSuccess) status = QK_ERR_CUDA + (int)e;
     }
     for (int i = 0; i < slots; ++i) {
         e = cudaStreamSynchronize(streams[i]);

@@ -95,13 +95,15 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
 template <int FDT, int KIND, int UB>
 static cudaError_t launch_mode(bool dyn, bool clamp, int sub, const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
-    if (!dyn) return launch_one<FDT, KIND, UB, false, true>(args, cfg, stream);
     if constexpr (UB == 64 && FDT != QK_F32 && (UB / 2) >= min_unit_bytes(FDT, KIND)) {
-        if (sub == 2)
+        if (sub == 2) {
+            if (!dyn) return launch_one<FDT, KIND, UB, false, true, 2, true>(args, cfg, stream);
             return clamp ? launch_one<FDT, KIND, UB, true, true, 2, true>(args, cfg, stream)
                          : launch_one<FDT, KIND, UB, true, false, 2, true>(args, cfg, stream);
+        }
     }
     if (sub != 1) return cudaErrorInvalidValue;
+    if (!dyn) return launch_one<FDT, KIND, UB, false, true>(args, cfg, stream);
     if constexpr (UB == 64) {
         if (args.lg_units_per_block == 0)
             return clamp ? launch_one<FDT, KIND, UB, true, true, 1, true>(args, cfg, stream)

@@ -531,16 +531,16 @@ __device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTenso
 // The kernel.  DYN = true: scale from the block's own absmax (one pass, fused).
 // DYN = false: scale given (tensor of F, one per block) or derived from a device absmax.
 // -------------------------------------------------------------------------------------
-// Resident CTAs per SM the register allocation must allow: 3 (at most 85 registers), 4 for the two-blocks-per-unit
-// form, which fits 64 registers without spilling.
+// Resident CTAs per SM the register allocation must allow: 3 (at most 85 registers), 4 for the fused
+// two-blocks-per-unit form, which fits 64 registers with at most a few spilled words.
 #ifndef QK_GIVEN_MIN_CTAS
 #define QK_GIVEN_MIN_CTAS 3
 #endif
 #ifndef QK_SUB2_MIN_CTAS
 #define QK_SUB2_MIN_CTAS 4
 #endif
-#define QK_MIN_CTAS(DYN, SUB) ((SUB) == 2 ? QK_SUB2_MIN_CTAS : ((DYN) ? 3 : QK_GIVEN_MIN_CTAS))
-// SUB = 2 (fused form only): two blocks per unit.  LG0: one block per unit, known at compile time.
+#define QK_MIN_CTAS(DYN, SUB) ((DYN) ? ((SUB) == 2 ? QK_SUB2_MIN_CTAS : 3) : QK_GIVEN_MIN_CTAS)
+// SUB = 2: two blocks per unit (16-bit types).  LG0: one block per unit, known at compile time.
 // Units are walked in grid-wide passes (see PassSplit).
 template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false>
 __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(const QuantArgs a)
@@ -549,7 +549,6 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
     constexpr int RAW = UT::RAW;
     constexpr int UNR = (UB >= 64) ? 2 : 4;  // units in flight per thread (128 bytes; 64 for 16-byte units)
     using F = typename ElemOf<FDT>::type;
-    static_assert(SUB == 1 || DYN, "two blocks per unit: fused form only");
 
     const bool aligned32 = a.aligned32 != 0;
     const int lg = (LG0 || SUB == 2) ? 0 : a.lg_units_per_block;
@@ -568,13 +567,14 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
         long long lidx[UNR];
         // Given block scales are fetched together with the data, so that the two latencies overlap
         // (loaded after the data, they cost a second round trip per iteration: 5.6 -> 6.1 TB/s on f32 q4).
-        float given[UNR];
+        float given[UNR][SUB];
         long long given_idx[UNR];
         bool given_starts[UNR];
         const bool block_scales_given = !DYN && (lg >= 0 || a.b2.enabled);
 #pragma unroll
         for (int k = 0; k < UNR; ++k) {
-            given[k] = 1.0f;
+#pragma unroll
+            for (int j = 0; j < SUB; ++j) given[k][j] = 1.0f;
             given_idx[k] = 0;
             given_starts[k] = false;
             if (full || idx[k] < a.nunits) {
@@ -588,7 +588,14 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
                              (long long)((unsigned)lidx[k] - row * a.rs.units_per_row.div) * UB;
                 }
                 load_unit<UB>(raw[k], static_cast<const char *>(a.t[ti].in) + offset, aligned32);
-                if constexpr (!DYN) {
+                if constexpr (!DYN && SUB == 2) {
+                    // the unit's two scales are neighbours: one 32-bit load (16-bit types only)
+                    given_idx[k] = 2 * lidx[k];
+                    given_starts[k] = true;
+                    const uint32_t pair = __ldg(reinterpret_cast<const uint32_t *>(a.t[ti].scale_in) + lidx[k]);
+                    given[k][0] = h_lo_to_f32<FDT>(pair);
+                    given[k][SUB - 1] = h_hi_to_f32<FDT>(pair);
+                } else if constexpr (!DYN) {
                     if (block_scales_given) {
                         if (a.b2.enabled) {
                             given_idx[k] = blocks2d_scale_index(a.b2, (unsigned)lidx[k], &given_starts[k]);
@@ -596,7 +603,7 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
                             given_idx[k] = lidx[k] >> lg;
                             given_starts[k] = (lidx[k] & ((1ll << lg) - 1)) == 0;
                         }
-                        given[k] = static_cast<float>(static_cast<const F *>(a.t[ti].scale_in)[given_idx[k]]);
+                        given[k][0] = static_cast<float>(static_cast<const F *>(a.t[ti].scale_in)[given_idx[k]]);
                     }
                 }
             } else {
@@ -625,7 +632,7 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
                 sidx = LG0 ? li : (li >> lg);
                 starts = LG0 ? true : ((li & ((1ll << lg) - 1)) == 0);
                 scale_f[0] = fused_unit_scale<FDT, RAW, LG0>(raw[k], lg, a.range, a.inv_range);
-            } else if (lg < 0 && !a.b2.enabled) {
+            } else if (SUB == 1 && lg < 0 && !a.b2.enabled) {
                 if (scale_ti != tk[k]) {
                     scale_ti = tk[k];
                     tensor_scale = tensor_unit_scale<FDT>(a, T, scale_ti);
@@ -635,7 +642,8 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
             } else {
                 sidx = given_idx[k];
                 starts = given_starts[k];
-                scale_f[0] = given[k];
+#pragma unroll
+                for (int j = 0; j < SUB; ++j) scale_f[j] = given[k][j];
             }
             finish_unit<FDT, KIND, UB, DYN, CLAMP, SUB>(a, T, raw[k], scale_f, sidx, starts, li, valid, aligned32);
         }

@@ -57,3 +57,38 @@ def test_staging_too_small_is_rejected():
     staging = torch.empty(256, dtype=torch.uint8, device="cuda")
     rc = lib.qk_roundtrip_host(t.ref(), c.ref(), s.ref(), t.ref(), _ffi.c_scheme(scheme), 0, staging.data_ptr(), 256, 0)
     assert rc == _ffi.QK_ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("fname,scheme", [
+    ("bf16", QuantScheme(value=QuantValue.Q8S, level=QuantLevel.block([128]))),
+    ("f32", QuantScheme(value=QuantValue.Q8S)),                                      # per tensor: every tensor one slice
+])
+def test_host_roundtrip_batch_matches_oracle(fname, scheme):
+    """Tensors of several sizes (several slices, one slice, a single row) through one ring of staging slots."""
+    lib = _ffi.lib()
+    F = FLOATS[fname]
+    elem = elem_of(F)
+    shapes = [(9000, 4096), (64, 4096), (1, 128), (3000, 1024), (5, 256)]
+    xs = [random_tensor(sh, F, 30 + i) for i, sh in enumerate(shapes)]
+    codes = [np.zeros(scheme.packed_shape(x.shape), dtype=code_dtype(scheme)) for x in xs]
+    scales = [np.zeros(scheme.scales_shape(x.shape), dtype=np.float32) for x in xs]
+    restored = [np.zeros_like(x) for x in xs]
+
+    def handles(arrays):
+        return _ffi.CTensorArray([TensorHandleRef.from_raw_parts(a.ctypes.data, a.shape, a.itemsize) for a in arrays])
+
+    hi, hc, hs, ho = handles(xs), handles(codes), handles(scales), handles(restored)
+    sch = _ffi.c_scheme(scheme)
+    need = int(lib.qk_host_roundtrip_staging_bytes_batch(hi.count, hi.array, sch, int(elem)))
+    assert need > 0
+    staging = torch.empty(need, dtype=torch.uint8, device="cuda")
+    _ffi.check(lib.qk_roundtrip_host_batch(hi.count, hi.array, hc.array, hs.array, ho.array, sch, int(elem),
+                                           staging.data_ptr(), need, torch.cuda.current_device()))
+    for i, x in enumerate(xs):
+        o_codes, o_scales = O.quantize_dynamic(x, scheme)
+        assert_bits_equal(codes[i], o_codes, f"codes {i}")
+        assert_bits_equal(scales[i], o_scales, f"scales {i}")
+        assert_bits_equal(restored[i], O.dequantize(o_codes, o_scales, scheme, F), f"restored {i}")
+    # too little staging for the largest member
+    assert lib.qk_roundtrip_host_batch(hi.count, hi.array, hc.array, hs.array, ho.array, sch, int(elem),
+                                       staging.data_ptr(), 1024, torch.cuda.current_device()) == _ffi.QK_ERR_WORKSPACE
