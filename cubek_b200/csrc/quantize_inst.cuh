@@ -18,19 +18,19 @@ template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int th
     return n;
 }
 
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false>
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false, bool ONE_SITE = false>
 static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
     constexpr int UNR = (UB >= 64) ? 2 : 4;
     const int threads = cfg.threads;
-    static const int occ256 = resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP, SUB, LG0>, 256);
+    static const int occ256 = resident_ctas_per_sm(quantize_kernel<FDT, KIND, UB, DYN, CLAMP, SUB, LG0, ONE_SITE>, 256);
     const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm : occ256 * (cfg.quant_waves > 0 ? cfg.quant_waves : 1);
     long long need = (args.nunits + (long long)threads * UNR - 1) / ((long long)threads * UNR);
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
     // cfg.staged: 0 = units below 64 bytes, 1 = always, 2 = never
-    if constexpr (SUB == 1 && !LG0) {
+    if constexpr (SUB == 1 && !LG0 && !ONE_SITE) {
         if ((cfg.staged == 1 || (cfg.staged == 0 && UB < 64)) && threads == 256 && !args.rs.enabled) {
             // bulk-copy staged variant: cfg.stages x 16 KB stages + barriers per CTA, a whole number of waves
             const int nstages = cfg.stages < 2 ? 2 : (cfg.stages > QK_MAX_STAGES ? QK_MAX_STAGES : cfg.stages);
@@ -86,7 +86,7 @@ static cudaError_t launch_one(const QuantArgs &args, const LaunchCfg &cfg, cudaS
     }
     QuantArgs split_args = args;
     split_args.split = make_pass_split(args.nunits, need, threads, UNR);
-    return launch_kernel(quantize_kernel<FDT, KIND, UB, DYN, CLAMP, SUB, LG0>, (int)need, threads, stream, cfg.pdl != 0,
+    return launch_kernel(quantize_kernel<FDT, KIND, UB, DYN, CLAMP, SUB, LG0, ONE_SITE>, (int)need, threads, stream, cfg.pdl != 0,
                          split_args);
 }
 
@@ -103,7 +103,13 @@ static cudaError_t launch_mode(bool dyn, bool clamp, int sub, const QuantArgs &a
         }
     }
     if (sub != 1) return cudaErrorInvalidValue;
-    if (!dyn) return launch_one<FDT, KIND, UB, false, true>(args, cfg, stream);
+    if (!dyn) {
+        // per tensor from absmax cells, 16-bit inputs, 64-byte units: the one-site walk (see common.cuh)
+        if constexpr (UB == 64 && FDT != QK_F32) {
+            if (args.absmax != nullptr && cfg.staged != 1) return launch_one<FDT, KIND, UB, false, true, 1, false, true>(args, cfg, stream);
+        }
+        return launch_one<FDT, KIND, UB, false, true>(args, cfg, stream);
+    }
     if constexpr (UB == 64) {
         if (args.lg_units_per_block == 0)
             return clamp ? launch_one<FDT, KIND, UB, true, true, 1, true>(args, cfg, stream)

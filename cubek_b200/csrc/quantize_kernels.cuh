@@ -542,7 +542,8 @@ __device__ __forceinline__ void finish_unit(const QuantArgs &a, const QuantTenso
 #define QK_MIN_CTAS(DYN, SUB) ((DYN) ? ((SUB) == 2 ? QK_SUB2_MIN_CTAS : 3) : QK_GIVEN_MIN_CTAS)
 // SUB = 2: two blocks per unit (16-bit types).  LG0: one block per unit, known at compile time.
 // Units are walked in grid-wide passes (see PassSplit).
-template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false>
+// ONE_SITE: the pass body is inlined once instead of twice (see QK_WALK_PASSES_ONE_SITE).
+template <int FDT, int KIND, int UB, bool DYN, bool CLAMP, int SUB = 1, bool LG0 = false, bool ONE_SITE = false>
 __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(const QuantArgs a)
 {
     using UT = UnitT<FDT, KIND, UB>;
@@ -649,7 +650,8 @@ __global__ void __launch_bounds__(256, QK_MIN_CTAS(DYN, SUB)) quantize_kernel(co
         }
     };
 
-    QK_WALK_PASSES(a.split.full_passes, a.nunits, UNR, pass);
+    if constexpr (ONE_SITE) QK_WALK_PASSES_ONE_SITE(a.split.full_passes, a.nunits, UNR, pass);
+    else QK_WALK_PASSES(a.split.full_passes, a.nunits, UNR, pass);
 }
 
 // -------------------------------------------------------------------------------------
