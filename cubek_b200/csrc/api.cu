@@ -448,8 +448,9 @@ static Blocks2D make_blocks2d(const Geometry &g, int unit_elems, int lg)
 }
 
 static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values, const QkTensor *out,
-                              const QkTensor *params, int *out_bytes)
+                              const QkTensor *params, int *out_bytes, int *sub, int param)
 {
+    *sub = 1;
     if (g_tune[TUNE_FORCE_GENERAL].load()) return -2;
     if (!is_contiguous(values)) return -2;
     const int esz = dtype_size(fdt);
@@ -468,6 +469,12 @@ static int fast_dequantize_lg(const Geometry &g, int fdt, const QkTensor *values
         if (!aligned(values->ptr, in_words >= 4 ? 16 : 4 * in_words)) continue;
         *out_bytes = ob;
         if (g.per_tensor) return -1;
+        // 16-bit blocks of 32 bytes: two per 64-byte unit (f32 params fetched as one 8-byte load)
+        if (ob == 64 && esz == 2 && E == 2 * g.B && !g.blocks_2d && !strided_rows && param == QK_F32 &&
+            aligned(params->ptr, 8) && (E / kind_elems_per_u32(g.kind)) % 2 == 0) {
+            *sub = 2;
+            return 0;
+        }
         if (g.B % E != 0) continue;
         const int lg = log2_exact(g.B / E);
         if (lg < 0) continue;
@@ -582,7 +589,7 @@ struct QuantBatch {
 };
 struct DequantBatch {
     DequantArgs a;
-    int fdt = -1, kind = -1, out_bytes = 0;
+    int fdt = -1, kind = -1, out_bytes = 0, sub = 1;
     DequantBatch() { a.ntensors = 0; a.nunits = 0; a.b2.enabled = 0; a.rs.enabled = 0; a.tr.enabled = 0; }
 };
 
@@ -601,7 +608,7 @@ static int flush_dequant(DequantBatch &b, const LaunchCfg &cfg, cudaStream_t str
 {
     if (b.a.ntensors == 0) return QK_OK;
     count_launch();
-    const cudaError_t e = launch_dequantize(b.fdt, b.kind, b.out_bytes, b.a, cfg, stream);
+    const cudaError_t e = launch_dequantize(b.fdt, b.kind, b.out_bytes, b.sub, b.a, cfg, stream);
     b.a.ntensors = 0;
     b.a.nunits = 0;
     return cuda_status(e);
@@ -1383,8 +1390,8 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
     if (g.n == 0) return QK_OK;
 
     const LaunchCfg cfg = current_cfg();
-    int out_bytes = 0;
-    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params, &out_bytes);
+    int out_bytes = 0, sub = 1;
+    const int lg = fast_dequantize_lg(g, output_dtype, values, output, params, &out_bytes, &sub, scheme->param);
     if (lg >= -1) {
         DequantBatch local;
         DequantBatch &b = batch ? *batch : local;
@@ -1392,13 +1399,14 @@ static int dequantize_common(const QkTensor *values, const QkTensor *output, con
         const bool strided_rows = !is_contiguous(output) && is_row_strided(output, &row_stride);
         const bool joins = !g.blocks_2d && !b.a.b2.enabled && !strided_rows && !b.a.rs.enabled &&
                            b.a.ntensors > 0 && b.a.ntensors < QK_MAX_BATCH && b.fdt == output_dtype &&
-                           b.kind == g.kind && b.out_bytes == out_bytes && b.a.lg_units_per_block == lg &&
+                           b.kind == g.kind && b.out_bytes == out_bytes && b.sub == sub && b.a.lg_units_per_block == lg &&
                            b.a.param == scheme->param;
         if (!joins) {
             if ((rc = flush_dequant(b, cfg, stream))) return rc;
             b.fdt = output_dtype;
             b.kind = g.kind;
             b.out_bytes = out_bytes;
+            b.sub = sub;
             b.a.lg_units_per_block = lg;
             b.a.param = scheme->param;
             b.a.aligned32 = 1;

@@ -10,11 +10,11 @@ template <typename Kernel> static int resident_ctas_per_sm(Kernel kernel, int th
     return n;
 }
 
-template <int FDT, int KIND, int OB, bool TILES>
+template <int FDT, int KIND, int OB, bool TILES, int SUB = 1>
 static cudaError_t launch_tiles(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
     const int threads = cfg.threads;
-    static const int occ256 = resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB, TILES>, 256);
+    static const int occ256 = resident_ctas_per_sm(dequantize_kernel<FDT, KIND, OB, TILES, SUB>, 256);
     // The write-heavy kernel runs faster as many short CTAs than as one persistent wave (CTAs
     // drift apart, so loads, arithmetic and stores of different CTAs overlap): 12 waves by default
     // (bf16 q4 batch: 5750 GB/s as one wave, 6480 at 8 waves, 6540 at 12).
@@ -23,50 +23,54 @@ static cudaError_t launch_tiles(const DequantArgs &args, const LaunchCfg &cfg, c
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;
     if (need < 1) need = 1;
-    return launch_kernel(dequantize_kernel<FDT, KIND, OB, TILES>, (int)need, threads, stream, cfg.pdl != 0, args);
+    return launch_kernel(dequantize_kernel<FDT, KIND, OB, TILES, SUB>, (int)need, threads, stream, cfg.pdl != 0, args);
 }
 
 template <int FDT, int KIND, int OB>
-static cudaError_t launch_one(const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+static cudaError_t launch_one(int sub, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
+    if constexpr (OB == 64 && FDT != QK_F32 && DUnitT<FDT, KIND, 64>::IW % 2 == 0) {
+        if (sub == 2 && !args.b2.enabled) return launch_tiles<FDT, KIND, OB, false, 2>(args, cfg, stream);
+    }
+    if (sub != 1) return cudaErrorInvalidValue;
     return args.b2.enabled ? launch_tiles<FDT, KIND, OB, true>(args, cfg, stream)
                            : launch_tiles<FDT, KIND, OB, false>(args, cfg, stream);
 }
 
 template <int FDT, int KIND>
-static cudaError_t launch_unit(int out_bytes, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
+static cudaError_t launch_unit(int out_bytes, int sub, const DequantArgs &args, const LaunchCfg &cfg, cudaStream_t stream)
 {
     constexpr int MINB = min_dequant_bytes(FDT, KIND);
-    if (out_bytes == 64) return launch_one<FDT, KIND, 64>(args, cfg, stream);
+    if (out_bytes == 64) return launch_one<FDT, KIND, 64>(sub, args, cfg, stream);
     if constexpr (MINB < 64) {
-        if (out_bytes == MINB) return launch_one<FDT, KIND, MINB>(args, cfg, stream);
+        if (out_bytes == MINB) return launch_one<FDT, KIND, MINB>(sub, args, cfg, stream);
     }
     return cudaErrorInvalidValue;
 }
 
 template <int FDT>
-static cudaError_t launch_kind(int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+static cudaError_t launch_kind(int kind, int out_bytes, int sub, const DequantArgs &args, const LaunchCfg &cfg,
                                cudaStream_t stream)
 {
     switch (kind) {
-    case KIND_PACK8: return launch_unit<FDT, KIND_PACK8>(out_bytes, args, cfg, stream);
-    case KIND_PACK4: return launch_unit<FDT, KIND_PACK4>(out_bytes, args, cfg, stream);
-    case KIND_PACK2: return launch_unit<FDT, KIND_PACK2>(out_bytes, args, cfg, stream);
-    case KIND_I8: return launch_unit<FDT, KIND_I8>(out_bytes, args, cfg, stream);
-    case KIND_E2M1: return launch_unit<FDT, KIND_E2M1>(out_bytes, args, cfg, stream);
-    case KIND_E4M3: return launch_unit<FDT, KIND_E4M3>(out_bytes, args, cfg, stream);
-    case KIND_E5M2: return launch_unit<FDT, KIND_E5M2>(out_bytes, args, cfg, stream);
+    case KIND_PACK8: return launch_unit<FDT, KIND_PACK8>(out_bytes, sub, args, cfg, stream);
+    case KIND_PACK4: return launch_unit<FDT, KIND_PACK4>(out_bytes, sub, args, cfg, stream);
+    case KIND_PACK2: return launch_unit<FDT, KIND_PACK2>(out_bytes, sub, args, cfg, stream);
+    case KIND_I8: return launch_unit<FDT, KIND_I8>(out_bytes, sub, args, cfg, stream);
+    case KIND_E2M1: return launch_unit<FDT, KIND_E2M1>(out_bytes, sub, args, cfg, stream);
+    case KIND_E4M3: return launch_unit<FDT, KIND_E4M3>(out_bytes, sub, args, cfg, stream);
+    case KIND_E5M2: return launch_unit<FDT, KIND_E5M2>(out_bytes, sub, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
-cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, int sub, const DequantArgs &args, const LaunchCfg &cfg,
                               cudaStream_t stream)
 {
     switch (fdt) {
-    case QK_F32: return launch_kind<QK_F32>(kind, out_bytes, args, cfg, stream);
-    case QK_F16: return launch_kind<QK_F16>(kind, out_bytes, args, cfg, stream);
-    case QK_BF16: return launch_kind<QK_BF16>(kind, out_bytes, args, cfg, stream);
+    case QK_F32: return launch_kind<QK_F32>(kind, out_bytes, sub, args, cfg, stream);
+    case QK_F16: return launch_kind<QK_F16>(kind, out_bytes, sub, args, cfg, stream);
+    case QK_BF16: return launch_kind<QK_BF16>(kind, out_bytes, sub, args, cfg, stream);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -161,7 +161,9 @@ __device__ __forceinline__ void dequant_word(uint32_t w, float s, uint32_t s2, u
 
 // TILES selects the [rows, cols] tile scale indexing at compile time: folding it into the common
 // kernel costs 16 registers and with them one resident CTA per SM.
-template <int FDT, int KIND, int OB, bool TILES>
+// SUB = 2: the unit holds two blocks (16-bit types, blocks of 32 bytes, f32 params): its two scales are fetched with
+// one 8-byte load and each half of the unit is multiplied by its own.
+template <int FDT, int KIND, int OB, bool TILES, int SUB = 1>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
 {
     using DU = DUnitT<FDT, KIND, OB>;
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     constexpr int EPW = DU::EPW;
     constexpr int OREG_PER_WORD = EPW * DU::ESZ / 4;
     constexpr int UNR = 4;
+    static_assert(SUB == 1 || (IW % 2 == 0 && !TILES), "two blocks per unit need an even number of words");
 
     const int lg = a.lg_units_per_block;
     const bool aligned32 = a.aligned32 != 0;
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     for (long long base = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x; base - threadIdx.x < a.nunits;
          base += stride) {
         uint32_t w[UNR][IW];
-        float s[UNR];
+        float s[UNR][SUB];
         char *dst[UNR];
         const bool full = base - threadIdx.x + (long long)blockDim.x * UNR <= a.nunits;
 #pragma unroll
@@ -214,19 +217,26 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
                     }
                 }
                 // cast<F>(scale): the param-typed scale narrowed (or widened) to F.
-                long long si;
-                if constexpr (TILES) {
-                    bool unused;
-                    si = (long long)blocks2d_scale_index(a.b2, (unsigned)li, &unused);
+                if constexpr (SUB == 2) {
+                    const float2 p = __ldg(reinterpret_cast<const float2 *>(T.params) + li);
+                    s[k][0] = round_to<FDT>(p.x);
+                    s[k][SUB - 1] = round_to<FDT>(p.y);
                 } else {
-                    si = (lg < 0) ? 0 : (li >> lg);
+                    long long si;
+                    if constexpr (TILES) {
+                        bool unused;
+                        si = (long long)blocks2d_scale_index(a.b2, (unsigned)li, &unused);
+                    } else {
+                        si = (lg < 0) ? 0 : (li >> lg);
+                    }
+                    if (a.param == QK_F32) s[k][0] = round_to<FDT>(__ldg(static_cast<const float *>(T.params) + si));
+                    else s[k][0] = round_to<FDT>(load_dyn(T.params, a.param, si));
                 }
-                if (a.param == QK_F32) s[k] = round_to<FDT>(__ldg(static_cast<const float *>(T.params) + si));
-                else s[k] = round_to<FDT>(load_dyn(T.params, a.param, si));
             } else {
 #pragma unroll
                 for (int j = 0; j < IW; ++j) w[k][j] = 0u;
-                s[k] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < SUB; ++j) s[k][j] = 0.0f;
                 dst[k] = nullptr;
             }
         }
@@ -235,10 +245,18 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
             const long long idx = base + (long long)k * blockDim.x;
             if (!(full || idx < a.nunits)) continue;
             uint32_t o[DU::OREG];
-            uint32_t s2 = 0;
-            if constexpr (FDT != QK_F32) s2 = h2_pack<FDT>(s[k], s[k]);
+            uint32_t s2[SUB];
 #pragma unroll
-            for (int j = 0; j < IW; ++j) dequant_word<FDT, KIND>(w[k][j], s[k], s2, o + j * OREG_PER_WORD);
+            for (int j = 0; j < SUB; ++j) {
+                s2[j] = 0;
+                if constexpr (FDT != QK_F32) s2[j] = h2_pack<FDT>(s[k][j], s[k][j]);
+            }
+#pragma unroll
+            for (int j = 0; j < IW; ++j) {
+                constexpr int HALF = (SUB == 2) ? IW / 2 : IW;
+                const int b = (SUB == 2 && j >= HALF) ? SUB - 1 : 0;
+                dequant_word<FDT, KIND>(w[k][j], s[k][b], s2[b], o + j * OREG_PER_WORD);
+            }
             if (aligned32) {
 #pragma unroll
                 for (int v = 0; v < OB / 32; ++v) {
@@ -260,7 +278,8 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantArgs a)
     }
 }
 
-cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
+// `sub`: blocks per unit, 1 or 2.
+cudaError_t launch_dequantize(int fdt, int kind, int out_bytes, int sub, const DequantArgs &args, const LaunchCfg &cfg,
                               cudaStream_t stream);
 cudaError_t launch_dequantize_transposed(int fdt, int kind, int out_bytes, const DequantArgs &args, const LaunchCfg &cfg,
                                          cudaStream_t stream);

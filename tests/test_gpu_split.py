@@ -97,3 +97,22 @@ def test_batch_members_that_end_inside_a_row_of_units():
         assert_bits_equal(to_numpy(codes[i], np.uint32), o_codes, f"codes {i}")
         assert_bits_equal(to_numpy(scales[i], np.float32), o_scale, f"scales {i}")
         assert_bits_equal(to_numpy(outs[i], F), O.dequantize(o_codes, o_scale, scheme, F), f"restored {i}")
+
+
+def test_two_blocks_per_unit_dequantize_with_params_off_the_8_byte_boundary():
+    """The dequantize kernel fetches the two scales of a unit with one 8-byte load; params that start 4 bytes off
+    take the one-block-per-unit kernel.  Same bits either way."""
+    scheme = QuantScheme(value=QuantValue.E2M1, store=QuantStore.Native, level=QuantLevel.block([16]))
+    x = random_tensor((512, 1024), np.float16, 45, "rowscaled")
+    codes, scales = O.quantize_dynamic(x, scheme)
+    want = O.dequantize(codes, scales, scheme, np.float16)
+    dcodes = to_device(codes)
+    pool = torch.zeros(scales.size + 1, dtype=torch.float32, device="cuda")
+    dparams = pool[1:].view(scales.shape)
+    dparams.copy_(to_device(scales))
+    assert dparams.data_ptr() % 8 == 4
+    for params in (dparams, to_device(scales)):
+        out = empty_device(x.shape, np.float16)
+        dequantize.launch_ref(ComputeClient.current(), H(dcodes), H(out), H(params), scheme, ElemType.F16)
+        torch.cuda.synchronize()
+        assert_bits_equal(to_numpy(out, np.float16), want, "restored")
