@@ -43,16 +43,22 @@ L2_BYTES = 126 << 20
 SUB_CONFIGS = ("q8_tensor_f32_4096x4096", "q4_block32_bf16_14336x4096", "e2m1_block16_f16_8192x4096",
                "e2m1_block32_f16_8192x4096", "q2_block64_f32_65536x4096")
 
-# DRAM traffic of one launch, modelled from one ncu capture of each kernel on a reduced number of rows (still larger
-# than L2; summaries in the files named here): dram__bytes_read.sum was 1.000 x the algorithmic reads in every
-# capture, and dram__bytes_write.sum fell short of the algorithmic writes by what was still dirty in L2 when the
-# kernel ended - an amount bounded by the L2, not proportional to the launch.  traffic(launch) = algorithmic reads
-# + max(0, algorithmic writes - residue).
+# dram__bytes_read.sum + dram__bytes_write.sum of one step of the default workload on ONE GPU, per kernel, from an ncu
+# capture of the full-size step (the two counters take one pass per launch; summary and command in the file named
+# here).  Row-sharded over N ranks every launch moves 1/N of it.  Reads equal the algorithmic reads; writes fall
+# short by the 50-60 MB per launch that are still dirty in L2 when a kernel ends.
+NCU_STEP_DRAM_BYTES = {
+    "llama3_8b_q8": {"dequantize": 44812.2e6, "quantize_dynamic": 22629.6e6, "absmax": 15010.1e6,
+                     "quantize_from_absmax": 22394.0e6},
+}
+NCU_STEP_DRAM_SOURCE = "profiles/bench_dram_traffic_llama3_8b_q8.md"
+# Single-tensor configurations: modelled from a capture of each kernel on a reduced number of rows (still larger than
+# L2): traffic(launch) = algorithmic bytes - the write residue still dirty in L2 at kernel end.
 NCU_WRITE_RESIDUE_BYTES = {
-    ("dequantize", "q8_block128_bf16"): (268.4e6 - 214.6e6, "profiles/dequantize_kernel_q8_block128_bf16.md"),
-    ("quantize_dynamic", "q8_block128_bf16"): (138.4e6 - 108.3e6, "profiles/quantize_kernel_q8_block128_bf16.md"),
-    ("dequantize", "q4_block32_bf16"): (154.1e6 - 130.4e6, "profiles/dequantize_kernel_q4_block32_bf16.md"),
-    ("quantize_dynamic", "q4_block32_bf16"): (154.1e6 - 145.2e6, "profiles/quantize_kernel_q4_block32_bf16.md"),
+    ("dequantize", "q8_block128_bf16"): (268.4e6 - 215.1e6, "profiles/dequantize_kernel_q8_block128_bf16.md"),
+    ("quantize_dynamic", "q8_block128_bf16"): (138.4e6 - 108.7e6, "profiles/quantize_kernel_q8_block128_bf16.md"),
+    ("dequantize", "q4_block32_bf16"): (268.4e6 - 215.0e6, "profiles/dequantize_kernel_q4_block32_bf16.md"),
+    ("quantize_dynamic", "q4_block32_bf16"): (83.9e6 - 62.5e6, "profiles/quantize_kernel_q4_block32_bf16.md"),
 }
 
 
@@ -891,10 +897,13 @@ def run_gpu(args):
         achieved = round(g["bytes"] / g["ms"] / 1e6 / ctx.world, 1)
         d = {"avg_launch_ms": round(g["ms"] / max(g["launches"], 1), 5) if g["launches"] else None,
              "bytes_per_launch": int(g["bytes"] / ctx.world / max(g["launches"], 1)) if g["launches"] else None}
-        traffic = None
+        traffic, traffic_source = None, None
+        step_dram = NCU_STEP_DRAM_BYTES.get(args.workload, {}).get(dom)
         tk = NCU_WRITE_RESIDUE_BYTES.get((dom, main.get("traffic_key", "")))
-        if tk and d["bytes_per_launch"]:
-            traffic = int(max(d["bytes_per_launch"] - tk[0], 0))
+        if step_dram and g["launches"]:
+            traffic, traffic_source = int(step_dram / ctx.world / g["launches"]), NCU_STEP_DRAM_SOURCE
+        elif tk and d["bytes_per_launch"]:
+            traffic, traffic_source = int(max(d["bytes_per_launch"] - tk[0], 0)), tk[1]
         dom = f"{dom} ({' + '.join(g['phases'])})"
         parity_ok = all(p["ok"] for p in main["parity"].values())
         out = {
@@ -906,7 +915,7 @@ def run_gpu(args):
             "pct_of_measured_peak_per_gpu": round(100 * value / ctx.world / peak, 1),
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "frac_of_spec": round(achieved / SPEC_PEAK_GBS, 4),
-                         "traffic": traffic, "traffic_source": tk[1] if tk else None,
+                         "traffic": traffic, "traffic_source": traffic_source,
                          "avg_launch_ms": d.get("avg_launch_ms"), "bytes_per_launch": d.get("bytes_per_launch"),
                          "peak_source": f"{peak_kind} copy bandwidth (a plain copy: a lower bound of the peak, so a "
                                         "fraction may read slightly above 1)",
