@@ -82,8 +82,8 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 // ---- process-wide knobs (measurement only) and counters ------------------------------------
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
        TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_SLICE_KIB = 9,
-       TUNE_SLOTS = 10, TUNE_STAGES = 11, TUNE_COUNT = 12 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}, {2}};
+       TUNE_SLOTS = 10, TUNE_STAGES = 11, TUNE_TENSOR_SMEM_ROWS = 12, TUNE_COOP_MAX_MIB = 13, TUNE_COUNT = 14 };
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}, {2}, {-1}, {256}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 
@@ -125,6 +125,7 @@ static LaunchCfg current_cfg()
     c.quant_waves = g_tune[TUNE_QUANT_WAVES].load();
     c.staged = g_tune[TUNE_STAGED].load();
     c.stages = g_tune[TUNE_STAGES].load();
+    c.tensor_smem_rows = g_tune[TUNE_TENSOR_SMEM_ROWS].load();
     c.dequant_waves = g_tune[TUNE_DEQUANT_WAVES].load();
     c.sm_count = sm_count_of_current_device();
     return c;
@@ -1498,8 +1499,9 @@ static int try_quantize_tensor_coop(const QkTensor *input, const QkTensor *outpu
     const int U = 64 / fsize;
     if (g.n == 0 || g.n % U != 0 || !aligned(input->ptr, 16) || !aligned(output->ptr, 16) || !aligned(workspace, 4))
         return QK_ERR_TOO_LARGE;
-    // Beyond the L2 the second pass comes from HBM anyway and the barrier only costs.
-    if ((size_t)g.n * fsize > (size_t)100 << 20) return QK_ERR_TOO_LARGE;
+    // Measured against absmax + quantize as two launches: 24 vs 32 us at 64 MiB, 50 vs 53 at 112 MiB, 91 vs 95 at
+    // 256 MiB, 217 vs 212 at 512 MiB (the second pass comes from HBM there and the two-launch route has more CTAs).
+    if ((size_t)g.n * fsize > (size_t)g_tune[TUNE_COOP_MAX_MIB].load() << 20) return QK_ERR_TOO_LARGE;
     float lo, hi;
     qk_value_range(scheme->value, &lo, &hi);
     const LaunchCfg cfg = current_cfg();

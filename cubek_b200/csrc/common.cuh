@@ -407,6 +407,7 @@ struct LaunchCfg {
     int pdl;          // 1: launch with programmatic stream serialization
     int staged;       // 1: quantize reads its input through the shared-memory bulk-copy pipeline
     int stages;       // ring depth of that pipeline (2..4 tiles of 16 KB per CTA)
+    int tensor_smem_rows;  // rows the one-launch per-tensor kernel keeps in shared memory; < 0 = as many as fit
 };
 
 }  // namespace qk

@@ -150,20 +150,57 @@ static cudaError_t launch_quantize_t(int kind, int unit_bytes, bool dyn, bool cl
     }
 }
 
-template <int FDT, int KIND>
-static cudaError_t launch_tensor_one(QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
+template <int FDT, int KIND, bool CLAMP>
+static cudaError_t launch_tensor_clamp(QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg,
                                      cudaStream_t stream)
 {
-    constexpr int UNR = 2;
-    static const int occ = resident_ctas_per_sm(quantize_tensor_kernel<FDT, KIND, 64>, 256);
-    long long need = (args.nunits + 256ll * UNR - 1) / (256ll * UNR);
+    constexpr int MAX_SMEM = QK_TENSOR_SMEM_ROWS * QK_TENSOR_ROW_BYTES;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    // The opt-in to more than 48 KiB of dynamic shared memory is a per-device attribute of the kernel.
+    static int occupancy[64];
+    static std::mutex occupancy_mutex;
+    int occ;
+    {
+        std::lock_guard<std::mutex> lock(occupancy_mutex);
+        if (occupancy[dev] == 0) {
+            int n = 0;
+            if (cudaFuncSetAttribute(quantize_tensor_kernel<FDT, KIND, 64, CLAMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM) !=
+                    cudaSuccess ||
+                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_tensor_kernel<FDT, KIND, 64, CLAMP>, 256, MAX_SMEM) != cudaSuccess ||
+                n < 1) {
+                (void)cudaGetLastError();
+                n = -1;
+            }
+            occupancy[dev] = n;
+        }
+        occ = occupancy[dev];
+    }
+    if (occ < 1) return cudaErrorInvalidValue;
+    long long need = (args.nunits + 256ll * 2 - 1) / (256ll * 2);
     const long long cap = (long long)cfg.sm_count * occ;   // all CTAs must be resident (grid barrier)
     if (need > cap) need = cap;
     if (need < 1) need = 1;
     if (need > partials_capacity) return cudaErrorInvalidValue;
+    // the same row arithmetic as the kernel's
+    const long long row_units = need * 256;
+    const int nrows = (int)((args.nunits + row_units - 1) / row_units);
+    const int reg_row = nrows - 4;
+    int smem_rows = cfg.tensor_smem_rows >= 0 ? cfg.tensor_smem_rows : QK_TENSOR_SMEM_ROWS;
+    if (smem_rows > QK_TENSOR_SMEM_ROWS) smem_rows = QK_TENSOR_SMEM_ROWS;
+    if (smem_rows > reg_row) smem_rows = reg_row > 0 ? reg_row : 0;
+    args.smem_rows = smem_rows;
     void *params[] = {&args};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(quantize_tensor_kernel<FDT, KIND, 64>), dim3((unsigned)need),
-                                       dim3(256), params, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(quantize_tensor_kernel<FDT, KIND, 64, CLAMP>), dim3((unsigned)need),
+                                       dim3(256), params, (size_t)smem_rows * QK_TENSOR_ROW_BYTES, stream);
+}
+
+template <int FDT, int KIND>
+static cudaError_t launch_tensor_one(QuantTensorArgs &args, int partials_capacity, const LaunchCfg &cfg, cudaStream_t stream)
+{
+    const bool clamp = need_clamp(FDT, KIND, true, args.lo == -args.hi, args.param);
+    return clamp ? launch_tensor_clamp<FDT, KIND, true>(args, partials_capacity, cfg, stream)
+                 : launch_tensor_clamp<FDT, KIND, false>(args, partials_capacity, cfg, stream);
 }
 
 template <int FDT>

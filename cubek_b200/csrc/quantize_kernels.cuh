@@ -145,6 +145,32 @@ __device__ __forceinline__ void mul2(float a0, float a1, float b, float &o0, flo
 #endif
 }
 
+// Two fused multiply-adds / sums with one packed instruction each (IEEE per lane, like the scalar forms).
+__device__ __forceinline__ void fma2(float a0, float a1, float b0, float b1, float c0, float c1, float &o0, float &o1)
+{
+#ifdef QK_NO_F32X2
+    o0 = __fmaf_rn(a0, b0, c0);
+    o1 = __fmaf_rn(a1, b1, c1);
+#else
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(o0), "=f"(o1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+#endif
+}
+__device__ __forceinline__ void add2(float a0, float a1, float b, float &o0, float &o1)
+{
+#ifdef QK_NO_F32X2
+    o0 = a0 + b;
+    o1 = a1 + b;
+#else
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tadd.rn.f32x2 rc, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(o0), "=f"(o1)
+        : "f"(a0), "f"(a1), "f"(b));
+#endif
+}
+
 template <int FDT> __device__ __forceinline__ float h_lo_to_f32(uint32_t p)
 {
     if constexpr (FDT == QK_BF16) return bf16_lo_to_f32(p);
@@ -224,7 +250,12 @@ template <int KIND, int U> __device__ __forceinline__ void pack_from_f32(const f
         for (int w = 0; w < OW; ++w) {
             uint32_t b[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) b[i] = __float_as_uint(c[4 * w + i] + QK_MAGIC);
+            for (int i = 0; i < 4; i += 2) {
+                float m0, m1;
+                if constexpr (U >= 16) add2(c[4 * w + i], c[4 * w + i + 1], QK_MAGIC, m0, m1);
+                else m0 = c[4 * w + i] + QK_MAGIC, m1 = c[4 * w + i + 1] + QK_MAGIC;
+                b[i] = __float_as_uint(m0), b[i + 1] = __float_as_uint(m1);
+            }
             const uint32_t l = __byte_perm(b[0], b[1], 0x0040);
             const uint32_t h = __byte_perm(b[2], b[3], 0x0040);
             outw[w] = __byte_perm(l, h, 0x5410);
@@ -310,16 +341,30 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
 
     if constexpr (FDT == QK_F32) {
         float c[U];
+        const float ms = -s;
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const float x = __uint_as_float(raw[i]);
-            float q0 = x * r;
-            if constexpr (!BOUNDED) q0 = fminf(fmaxf(q0, lo - 2.0f), hi + 2.0f);
-            const float t = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+        for (int i = 0; i < U; i += 2) {
+            const float x0 = __uint_as_float(raw[i]), x1 = __uint_as_float(raw[i + 1]);
+            float q0, q1, e0, e1, t0, t1;
+            constexpr bool PACKED = (UB >= 64);   // the packed forms want register pairs: smaller units have none to spare
+            if constexpr (PACKED) mul2(x0, x1, r, q0, q1);
+            else q0 = x0 * r, q1 = x1 * r;
+            if constexpr (!BOUNDED) {
+                q0 = fminf(fmaxf(q0, lo - 2.0f), hi + 2.0f);
+                q1 = fminf(fmaxf(q1, lo - 2.0f), hi + 2.0f);
+            }
+            if constexpr (PACKED) {
+                fma2(ms, ms, q0, q1, x0, x1, e0, e1);
+                fma2(e0, e1, r, r, q0, q1, t0, t1);
+            } else {
+                e0 = __fmaf_rn(ms, q0, x0), e1 = __fmaf_rn(ms, q1, x1);
+                t0 = __fmaf_rn(e0, r, q0), t1 = __fmaf_rn(e1, r, q1);
+            }
             // The 4- and 2-bit packs add shifted bit patterns: a NaN would carry into the fields of its neighbours, so
             // the unclamped form still takes the minimum with the upper bound (which a NaN does not survive).
             constexpr bool ADDS = (KIND == KIND_PACK4 || KIND == KIND_PACK2);
-            c[i] = CLAMP ? fminf(fmaxf(t, lo), hi) : (ADDS ? fminf(t, hi) : t);
+            c[i] = CLAMP ? fminf(fmaxf(t0, lo), hi) : (ADDS ? fminf(t0, hi) : t0);
+            c[i + 1] = CLAMP ? fminf(fmaxf(t1, lo), hi) : (ADDS ? fminf(t1, hi) : t1);
         }
         pack_from_f32<KIND, U>(c, outw);
     } else if constexpr (KIND == KIND_E4M3 || KIND == KIND_E5M2) {
@@ -821,9 +866,15 @@ __global__ void __launch_bounds__(256) quantize_staged_kernel(const QuantArgs a,
 // Per tensor, fused in ONE cooperative launch: absmax over the whole tensor, a grid-wide
 // barrier, then quantize.  Every CTA leaves its partial absmax in `partials[blockIdx.x]`
 // (no atomics, nothing to clear), and after the barrier every CTA reduces those partials.
-// The second pass walks the tensor in the opposite direction, so it starts on the data the
-// first pass read last, which is still in the 126 MB L2: a 64 MB tensor is read from HBM
-// once instead of twice.  Results are bit-identical to absmax_kernel + quantize_kernel.
+//
+// The tensor is walked in rows of gridDim.x * 256 units; a thread owns one unit of every row.
+// The first pass has four rows (256 bytes per thread) in flight.  What a thread read last it
+// keeps for the second pass: the final four rows in registers, the `smem_rows` rows before
+// them in shared memory (a thread-private spill area, laid out [row][16-byte chunk][thread],
+// so the accesses are conflict free).  With 2 CTAs per SM and 5 x 16 KiB of shared memory
+// each, 9 of the 14 rows of a 64 MiB tensor never leave the SM.  The other rows are read
+// again newest first (the likeliest to be in the 126 MB L2), two rows ahead of the
+// arithmetic.  Results are bit-identical to absmax_kernel + quantize_kernel.
 // Must be launched cooperatively with a grid that is resident all at once.
 // -------------------------------------------------------------------------------------
 struct QuantTensorArgs {
@@ -836,42 +887,61 @@ struct QuantTensorArgs {
     float lo, hi, range, inv_range;
     int force_exact;
     int aligned32;
+    int smem_rows;       // rows kept in dynamic shared memory (16 KiB each)
 };
 
-template <int FDT, int KIND, int UB>
-__global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorArgs a)
+// More shared memory than this leaves the L1 too small to track the loads in flight (7 rows: first pass 25 % slower).
+constexpr int QK_TENSOR_SMEM_ROWS = 5;
+constexpr int QK_TENSOR_ROW_BYTES = 256 * 64;
+
+template <int FDT, int KIND, int UB, bool CLAMP>
+__global__ void __launch_bounds__(256, 2) quantize_tensor_kernel(const QuantTensorArgs a)
 {
+    static_assert(UB == 64, "64-byte units");
     using UT = UnitT<FDT, KIND, UB>;
     constexpr int RAW = UT::RAW;
     constexpr int OW = UT::OW;
-    constexpr int UNR = (UB >= 64) ? 2 : 4;
+    extern __shared__ uint4 kept_rows[];
     const char *in = static_cast<const char *>(a.in);
     uint32_t *out = static_cast<uint32_t *>(a.out);
     const bool aligned32 = a.aligned32 != 0;
-    const long long stride = (long long)gridDim.x * blockDim.x * UNR;
-    const long long first = (long long)blockIdx.x * blockDim.x * UNR + threadIdx.x;
-    const long long niter = (a.nunits + stride - 1) / stride;
+    const long long row_units = (long long)gridDim.x * 256;
+    const long long first = (long long)blockIdx.x * 256 + threadIdx.x;
+    const int nrows = (int)((a.nunits + row_units - 1) / row_units);   // >= 1; units of rows >= nrows are out of range
+    // Rows are taken four at a time, counted so that the last four end the tensor: the first group starts at a
+    // negative row when nrows is not a multiple of 4.
+    const int reg_row = nrows - 4;                                              // rows reg_row .. reg_row + 3 stay in registers
+    const int start_row = -((4 - (nrows & 3)) & 3);
+    const int kept_row = reg_row > a.smem_rows ? reg_row - a.smem_rows : (reg_row > 0 ? 0 : reg_row);   // rows [kept_row, reg_row) stay in shared memory
 
-    // ---- pass 1: absmax.  The units of the last iteration stay in registers for pass 2. -----------
+    auto fetch = [&](uint32_t (&raw)[RAW], int row) {
+        const long long idx = (long long)row * row_units + first;
+        if (row >= 0 && idx < a.nunits) {
+            load_unit<UB>(raw, in + idx * UB, aligned32);
+        } else {
+#pragma unroll
+            for (int i = 0; i < RAW; ++i) raw[i] = 0u;
+        }
+    };
+
+    // ---- pass 1: absmax ---------------------------------------------------------------------------
     float amax = 0.0f;
-    uint32_t last[UNR][RAW];
-    for (long long it = 0; it < niter; ++it) {
-        const long long base = it * stride + first;
+    uint32_t held[4][RAW];
+    for (int row = start_row; row <= reg_row; row += 4) {
 #pragma unroll
-        for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            if (idx < a.nunits) {
-                load_unit<UB>(last[k], in + idx * UB, aligned32);
-            } else {
+        for (int k = 0; k < 4; ++k) fetch(held[k], row + k);
 #pragma unroll
-                for (int i = 0; i < RAW; ++i) last[k][i] = 0u;
+        for (int k = 0; k < 4; ++k) {
+            amax = fmaxf(amax, unit_absmax<FDT, RAW>(held[k]));
+            if (row < reg_row && row + k >= kept_row) {
+                uint4 *slot = kept_rows + (size_t)(row + k - kept_row) * (RAW / 4) * 256 + threadIdx.x;
+#pragma unroll
+                for (int j = 0; j < RAW / 4; ++j)
+                    slot[j * 256] = make_uint4(held[k][4 * j], held[k][4 * j + 1], held[k][4 * j + 2], held[k][4 * j + 3]);
             }
         }
-#pragma unroll
-        for (int k = 0; k < UNR; ++k) amax = fmaxf(amax, unit_absmax<FDT, RAW>(last[k]));
     }
     __shared__ float warp_max[8];
-    __shared__ float block_max;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
@@ -891,46 +961,57 @@ __global__ void __launch_bounds__(256) quantize_tensor_kernel(const QuantTensorA
     for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) v = fmaxf(v, __ldcg(a.partials + i));
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    if (lane == 0) warp_max[warp] = v;   // no warp reads the first round's values after the grid barrier
     __syncthreads();
-    if (lane == 0) warp_max[warp] = v;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = warp_max[0];
+    v = warp_max[lane & 7];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) t = fmaxf(t, warp_max[i]);
-        block_max = t;
-    }
-    __syncthreads();
-    const float scale_f = round_to<FDT>(div_by_range(2.0f * block_max, a.range, a.inv_range));
+    for (int m = 4; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    const float scale_f = round_to<FDT>(div_by_range(2.0f * v, a.range, a.inv_range));
     const float s_fs = (a.param == QK_F32) ? scale_f : round_to_dyn(a.param, scale_f);
     const float s = (a.param == QK_F32) ? scale_f : round_to<FDT>(s_fs);
     if (blockIdx.x == 0 && threadIdx.x == 0) store_dyn(a.out_scale, a.param, 0, s_fs);
     const bool fast = kind_allows_fast<FDT, KIND>() && !a.force_exact && scale_is_safe(s);
 
-    // ---- pass 2: quantize, last iteration first (its units are still in registers; the ones
-    // before it are the most recently read, hence the most likely to be in L2) ----------------------
-    for (long long it = niter - 1; it >= 0; --it) {
-        const long long base = it * stride + first;
-        if (it != niter - 1) {
+    auto emit = [&](const uint32_t (&raw)[RAW], int row) {
+        const long long idx = (long long)row * row_units + first;
+        uint32_t w[OW];
+        if (fast) quantize_unit_fast<FDT, KIND, UB, CLAMP, true>(raw, s, a.lo, a.hi, w);
+        else quantize_unit_exact<FDT, KIND, UB>(raw, s, a.lo, a.hi, w);
+        if (row >= 0 && idx < a.nunits) store_words<OW>(out + idx * OW, w, aligned32);
+    };
+
+    // ---- pass 2: quantize, newest data first ------------------------------------------------------
+    emit(held[3], reg_row + 3);
+    emit(held[2], reg_row + 2);
+    // the newest rows that were not kept come from L2 while the kept ones are worked on
+    int next_row = kept_row - 1;
+    fetch(held[2], next_row);
+    fetch(held[3], next_row - 1);
+    emit(held[1], reg_row + 1);
+    emit(held[0], reg_row);
+    for (int row = reg_row - 1; row >= kept_row; --row) {
+        const uint4 *slot = kept_rows + (size_t)(row - kept_row) * (RAW / 4) * 256 + threadIdx.x;
 #pragma unroll
-            for (int k = 0; k < UNR; ++k) {
-                const long long idx = base + (long long)k * blockDim.x;
-                if (idx < a.nunits) {
-                    load_unit<UB>(last[k], in + idx * UB, aligned32);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < RAW; ++i) last[k][i] = 0u;
-                }
-            }
+        for (int j = 0; j < RAW / 4; ++j) {
+            const uint4 q = slot[j * 256];
+            held[0][4 * j] = q.x, held[0][4 * j + 1] = q.y, held[0][4 * j + 2] = q.z, held[0][4 * j + 3] = q.w;
         }
-#pragma unroll
-        for (int k = 0; k < UNR; ++k) {
-            const long long idx = base + (long long)k * blockDim.x;
-            uint32_t w[OW];
-            if (fast) quantize_unit_fast<FDT, KIND, UB, true, true>(last[k], s, a.lo, a.hi, w);   // clamped: a NaN stays in its own code
-            else quantize_unit_exact<FDT, KIND, UB>(last[k], s, a.lo, a.hi, w);
-            if (idx < a.nunits) store_words<OW>(out + idx * OW, w, aligned32);
-        }
+        emit(held[0], row);
+    }
+    while (next_row >= 0) {   // the two register pairs take turns
+        int row = next_row;
+        next_row -= 2;
+        fetch(held[0], next_row);
+        fetch(held[1], next_row - 1);
+        emit(held[2], row);
+        emit(held[3], row - 1);
+        if (next_row < 0) break;
+        row = next_row;
+        next_row -= 2;
+        fetch(held[2], next_row);
+        fetch(held[3], next_row - 1);
+        emit(held[0], row);
+        emit(held[1], row - 1);
     }
 }
 

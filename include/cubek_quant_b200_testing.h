@@ -17,7 +17,8 @@ extern "C" {
  * dequantize kernels in waves, 7 cooperative per-tensor kernel on/off, 8 staging of the quantize input through
  * shared memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never, 9 / 10 input KiB per slice and
  * staging slots (1..8) of qk_roundtrip_host; change them only between calls, and size the staging area after,
- * 11 ring depth (2..4 tiles of 16 KB) of the staged quantize variant).  They exist so that tests can force every
+ * 11 ring depth (2..4 tiles of 16 KB) of the staged quantize variant, 12 rows the one-launch per-tensor kernel keeps
+ * in shared memory (< 0: as many as fit), 13 largest tensor in MiB that takes that kernel).  They exist so that tests can force every
  * route onto the same inputs and measurements can compare routes; they change behaviour for every thread of the
  * process. */
 void qk_set_tuning(int key, int value);
