@@ -75,12 +75,16 @@ def assign_round_robin(sizes: Sequence[int], world: int) -> List[List[int]]:
     return owned
 
 
-def allreduce_absmax(absmax, group=None) -> None:
-    """In-place MAX all-reduce of a tensor of absmax scalars (one per row-sharded tensor)."""
+def allreduce_absmax(absmax, group=None, async_op: bool = False):
+    """In-place MAX all-reduce of a tensor of absmax scalars (one per row-sharded tensor).  With ``async_op`` the
+    collective is only started: the returned handle's ``wait()`` makes the current stream wait for it (the host
+    does not block), so kernels enqueued in between run while the exchange is in flight.  ``None`` is returned
+    when there is nothing to wait for."""
     import torch.distributed as dist
 
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=group)
+        return dist.all_reduce(absmax, op=dist.ReduceOp.MAX, group=group, async_op=async_op)
+    return None
 
 
 def quantize_per_tensor_sharded(client: ComputeClient, shard: TensorHandleRef, output: TensorHandleRef,
@@ -123,6 +127,16 @@ class ShardedPerTensorSet:
     def exchange(self) -> None:
         """Phase 2: the only collective of the path, MAX over the ranks of one f32 per tensor."""
         allreduce_absmax(self._absmax, self._group)
+
+    def exchange_begin(self) -> None:
+        """Phase 2 started, not awaited: independent work enqueued before ``exchange_end`` overlaps it."""
+        self._pending = allreduce_absmax(self._absmax, self._group, async_op=True)
+
+    def exchange_end(self) -> None:
+        """The current stream waits for the exchange started by ``exchange_begin``."""
+        pending, self._pending = getattr(self, "_pending", None), None
+        if pending is not None:
+            pending.wait()
 
     def quantize(self) -> None:
         """Phase 3: quantize every shard with the scale derived on the device from its (global) absmax cell."""
