@@ -232,6 +232,28 @@ __device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi)
     asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// f16x2 -> two fp8 codes in the low 16 bits (low half -> low byte), round to nearest even, saturating.
+__device__ __forceinline__ uint32_t cvt_e4m3x2_from_f16x2(uint32_t p)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t cvt_e5m2x2_from_f16x2(uint32_t p)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(r) : "r"(p));
+    return r;
+}
+// Both halves of an f16x2 rounded to integers (ties to even); the sign of a zero result is kept.
+__device__ __forceinline__ uint32_t f16x2_rint(uint32_t p)
+{
+    uint32_t r;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.rni.f16.f16 l, l;\n\tcvt.rni.f16.f16 h, h;\n\tmov.b32 %0, {l, h};\n\t}"
+        : "=r"(r)
+        : "r"(p));
+    return r;
+}
 __device__ __forceinline__ uint32_t cvt_f16x2_from_e4m3x2(uint32_t two_bytes)
 {
     uint32_t r;

@@ -18,7 +18,12 @@ static cudaError_t launch_tiles(const DequantArgs &args, const LaunchCfg &cfg, c
     // The write-heavy kernel runs faster as many short CTAs than as one persistent wave (CTAs
     // drift apart, so loads, arithmetic and stores of different CTAs overlap): 12 waves by default
     // (bf16 q4 batch: 5750 GB/s as one wave, 6480 at 8 waves, 6540 at 12).
-    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm : occ256 * (cfg.dequant_waves > 0 ? cfg.dequant_waves : 1);
+    // Short launches (the shards of an 8-way split: 0.5 GB of output per launch) want fewer, longer CTAs: at least
+    // one and a half rounds of 4 units per thread, down to 4 waves (6100 GB/s at 12 waves, 6350 at 6, 6390 at 4).
+    int waves = cfg.dequant_waves > 0 ? cfg.dequant_waves : 1;
+    const long long fit = args.nunits / ((long long)cfg.sm_count * occ256 * threads * 6);
+    if (fit < waves) waves = (int)(fit > 4 ? fit : (waves < 4 ? waves : 4));
+    const int per_sm = (cfg.ctas_per_sm > 0) ? cfg.ctas_per_sm : occ256 * waves;
     long long need = (args.nunits + (long long)threads * 4 - 1) / ((long long)threads * 4);
     const long long cap = (long long)cfg.sm_count * per_sm;
     if (need > cap) need = cap;

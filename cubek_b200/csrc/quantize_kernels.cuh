@@ -367,6 +367,29 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
             c[i + 1] = CLAMP ? fminf(fmaxf(t1, lo), hi) : (ADDS ? fminf(t1, hi) : t1);
         }
         pack_from_f32<KIND, U>(c, outw);
+    } else if constexpr ((KIND == KIND_E4M3 || KIND == KIND_E5M2) && FDT == QK_F16) {
+        // f16 quotients stay packed: clamp, round to integer and convert two at a time (the integer rounding comes
+        // before the cast, as in the reference; e4m3's bound 448 is inside the range of the magic-number rounding,
+        // e5m2's 57344 is not and takes cvt.rni).
+        const uint32_t lo2 = h2_const<FDT>(lo), hi2 = h2_const<FDT>(hi), magic = h2_const<FDT>(1536.0f);
+#pragma unroll
+        for (int w = 0; w < OW; ++w) {
+            uint32_t hw[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float q0, q1;
+                mul2(raw_elem<FDT>(raw, 4 * w + 2 * j), raw_elem<FDT>(raw, 4 * w + 2 * j + 1), r, q0, q1);
+                uint32_t p = h2_min<FDT>(h2_max<FDT>(h2_pack<FDT>(q0, q1), lo2), hi2);
+                if constexpr (KIND == KIND_E4M3) {
+                    const uint32_t q = h2_sub<FDT>(h2_add<FDT>(p, magic), magic);
+                    p = (q & 0x7fff7fffu) | (p & 0x80008000u);   // keep the sign of zero
+                    hw[j] = cvt_e4m3x2_from_f16x2(p);
+                } else {
+                    hw[j] = cvt_e5m2x2_from_f16x2(f16x2_rint(p));
+                }
+            }
+            outw[w] = __byte_perm(hw[0], hw[1], 0x5410);
+        }
     } else if constexpr (KIND == KIND_E4M3 || KIND == KIND_E5M2) {
         float c[U];
 #pragma unroll

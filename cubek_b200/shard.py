@@ -129,7 +129,9 @@ class ShardedPerTensorSet:
         allreduce_absmax(self._absmax, self._group)
 
     def exchange_begin(self) -> None:
-        """Phase 2 started, not awaited: independent work enqueued before ``exchange_end`` overlaps it."""
+        """Phase 2 started, not awaited: independent work enqueued before ``exchange_end`` overlaps it.  Not a gain
+        for this library's own kernels: the collective's resident CTAs take SM slots from their one-wave persistent
+        grids, and the displaced CTAs run as a second wave (measured on two GPUs: a step 23 % slower)."""
         self._pending = allreduce_absmax(self._absmax, self._group, async_op=True)
 
     def exchange_end(self) -> None:
