@@ -29,7 +29,10 @@ namespace qk {
 
 // A launch covers one tensor or a batch of tensors that share the scheme, float type and unit
 // geometry.  Units are numbered across the batch; `unit_end` is the running total.
-constexpr int QK_MAX_BATCH = 64;
+#ifndef QK_MAX_BATCH_TENSORS
+#define QK_MAX_BATCH_TENSORS 64
+#endif
+constexpr int QK_MAX_BATCH = QK_MAX_BATCH_TENSORS;
 
 struct QuantTensor {
     const void *in;        // F-typed input, contiguous
