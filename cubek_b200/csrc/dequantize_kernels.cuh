@@ -152,10 +152,23 @@ __device__ __forceinline__ void dequant_word(uint32_t w, float s, uint32_t s2, u
     } else {
         // bf16 8-bit codes (9-bit biased values do not fit a bf16 mantissa), bf16 fp4 and fp8:
         // decode to f32, multiply (exact product), narrow once.
-        float q[EPW];
-        decode_word_f32<KIND>(w, q);
+        if constexpr (KIND == KIND_PACK8 || KIND == KIND_I8) {
+            // the same decode as decode_word_f32, two elements per instruction (add / mul.rn.f32x2)
+            const uint32_t b = w ^ 0x80808080u;
 #pragma unroll
-        for (int i = 0; i < EPW; i += 2) o[i / 2] = h2_pack<FDT>(s * q[i], s * q[i + 1]);
+            for (int i = 0; i < 4; i += 2) {
+                float q0, q1, r0, r1;
+                add2(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7650 + i)), __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7651 + i)),
+                     -8388736.0f, q0, q1);
+                mul2(q0, q1, s, r0, r1);
+                o[i / 2] = h2_pack<FDT>(r0, r1);
+            }
+        } else {
+            float q[EPW];
+            decode_word_f32<KIND>(w, q);
+#pragma unroll
+            for (int i = 0; i < EPW; i += 2) o[i / 2] = h2_pack<FDT>(s * q[i], s * q[i + 1]);
+        }
     }
 }
 

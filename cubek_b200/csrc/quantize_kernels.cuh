@@ -451,8 +451,9 @@ __device__ __forceinline__ void quantize_unit_fast(const uint32_t *raw, float s,
                     uint32_t b[4];
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        b[2 * j] = __float_as_uint(bf16_lo_to_f32(p[j]) + QK_MAGIC);
-                        b[2 * j + 1] = __float_as_uint(bf16_hi_to_f32(p[j]) + QK_MAGIC);
+                        float m0, m1;
+                        add2(bf16_lo_to_f32(p[j]), bf16_hi_to_f32(p[j]), QK_MAGIC, m0, m1);
+                        b[2 * j] = __float_as_uint(m0), b[2 * j + 1] = __float_as_uint(m1);
                     }
                     const uint32_t l = __byte_perm(b[0], b[1], 0x0040);
                     const uint32_t h = __byte_perm(b[2], b[3], 0x0040);
