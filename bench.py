@@ -881,6 +881,7 @@ def run_reduce_record(ctx: Ctx, steps):
 
 def run_gpu(args):
     from cubek_b200.synthetic import WORKLOADS
+    from cubek_b200.weights import llama3_8b_shapes
 
     ctx = Ctx(args)
     torch = ctx.torch
@@ -888,8 +889,10 @@ def run_gpu(args):
     is_set = args.workload.startswith("llama3_8b_q8")
     if is_set:
         main = run_weight_set(ctx, args)
-        e2e_set, e2e_what = main["sets"][0][1], (f"the first {args.e2e_tensors} tensors of the set (one layer: q, k, v, o, gate, up, down = "
-                                                 "218 M of the 7505 M elements), scheme " + main["sets"][0][0])
+        shapes = llama3_8b_shapes()[:args.e2e_tensors]
+        e2e_set, e2e_what = main["sets"][0][1], (f"the first {len(shapes)} tensors of the set ({len(shapes) / 7:g} layers of q, k, v, o, gate, up, "
+                                                 f"down = {sum(r * c for _, r, c in shapes) / 1e6:.0f} M of the 7505 M elements), scheme "
+                                                 + main["sets"][0][0])
     else:
         w = WORKLOADS[args.workload]
         main = run_single_config(ctx, args, w, args.batch, headline=True)
@@ -1060,7 +1063,7 @@ def main():
                     help="llama3_8b_q8 (both schemes), llama3_8b_q8_block128, llama3_8b_q8_tensor, or a single-tensor configuration")
     ap.add_argument("--case-tensors", type=int, default=1, help="with --case: tensors per batched call (1 = the single-tensor calls)")
     ap.add_argument("--batch", type=int, default=8, help="distinct tensors per step of a single-tensor configuration")
-    ap.add_argument("--e2e-tensors", type=int, default=7)
+    ap.add_argument("--e2e-tensors", type=int, default=28)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-configs", action="store_true", help="skip the records of the single-tensor configurations")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host round trip (launch lists of the device steps only)")

@@ -29,6 +29,8 @@ namespace qk {
 
 // A launch covers one tensor or a batch of tensors that share the scheme, float type and unit
 // geometry.  Units are numbered across the batch; `unit_end` is the running total.
+// (128 per launch, a 6 KB kernel argument, was measured on 8-way shards of a 225-tensor set and on single-tensor
+// calls: no faster anywhere, 2 % slower on the shards.)
 #ifndef QK_MAX_BATCH_TENSORS
 #define QK_MAX_BATCH_TENSORS 64
 #endif
