@@ -27,7 +27,6 @@ import math
 import os
 import statistics
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -89,59 +88,94 @@ def algorithmic_bytes(workload, rows=None):
     return tensor_bytes((rows if rows is not None else r) * c, workload.elem.size, workload.scheme)
 
 
+_SAMPLER_SOURCE = r"""
+import sys, time
+import pynvml
+pynvml.nvmlInit()
+handle = pynvml.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+out = open(sys.argv[2], "w", buffering=1)
+out.write("max %d\n" % pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+while True:
+    try:
+        out.write("%.6f %d %d\n" % (time.time(), pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM),
+                                     int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))))
+    except Exception:
+        pass
+    time.sleep(0.002)
+"""
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons (read-only NVML queries) while the timed region
-    runs.  The timed region lasts milliseconds, so a thread polls NVML every ~2 ms instead of
-    going through nvidia-smi's 100 ms loop."""
+    """Samples SM clocks and throttle reasons (read-only NVML queries) while the timed region runs.  The timed
+    region lasts milliseconds, so NVML is polled every ~2 ms instead of going through nvidia-smi's 100 ms loop -
+    from a child process: a polling thread inside the benchmark process shares its interpreter lock and its driver
+    locks with the thread that launches the kernels, and starved it once steps were down to 2 ms (8 GPUs)."""
 
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.samples, self.reason_bits, self.max_mhz = [], 0, None
-        self._stop = threading.Event()
-        self.thread = None
-        self.nvml = None
+        self.proc = self.path = None
+        self.t0 = None
 
     def start(self):
-        try:
-            import pynvml
+        """Starts the child and waits (a few seconds at most) until it is sampling."""
+        import subprocess
+        import tempfile
 
-            pynvml.nvmlInit()
-            self.nvml = pynvml
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            index = self.gpu_index
-            if visible:
-                try:
-                    index = int(visible.split(",")[self.gpu_index])
-                except ValueError:
-                    pass
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
-        except Exception:
-            self.nvml = None
-            return
-        self.thread = threading.Thread(target=self._poll, daemon=True)
-        self.thread.start()
-
-    def _poll(self):
-        nv = self.nvml
-        while not self._stop.is_set():
+        index = self.gpu_index
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
             try:
-                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
-                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
-            except Exception:
+                index = int(visible.split(",")[self.gpu_index])
+            except ValueError:
                 pass
-            time.sleep(0.002)
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="qk_clocks_", suffix=".txt")
+            os.close(fd)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SOURCE, str(index), self.path],
+                                         stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+            return
+        deadline = time.time() + 10.0
+        while time.time() < deadline and self.proc.poll() is None:
+            try:
+                if os.path.getsize(self.path) > 40:
+                    break
+            except OSError:
+                pass
+            time.sleep(0.01)
+
+    def begin(self):
+        """Call when the timed region starts: samples taken before are dropped."""
+        self.t0 = time.time()
 
     def stop(self):
-        if not self.nvml:
+        if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self._stop.set()
-        self.thread.join(timeout=2)
-        reasons = sorted(name for name, bit in self.REASONS.items() if self.reason_bits & bit)
-        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
-                "reasons": reasons, "samples": len(self.samples)}
+        t1 = time.time()
+        time.sleep(0.005)
+        self.proc.terminate()          # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        samples, bits, max_mhz = [], 0, None
+        try:
+            for line in open(self.path):
+                f = line.split()
+                if len(f) == 2 and f[0] == "max":
+                    max_mhz = float(f[1])
+                elif len(f) == 3 and (self.t0 is None or self.t0 <= float(f[0]) <= t1):
+                    samples.append(float(f[1]))
+                    bits |= int(f[2])
+            os.unlink(self.path)
+        except (OSError, ValueError):
+            pass
+        reasons = sorted(name for name, bit in self.REASONS.items() if bits & bit)
+        return {"sm_mhz": statistics.median(samples) if samples else None, "sm_max_mhz": max_mhz,
+                "reasons": reasons, "samples": len(samples)}
 
 
 def torch_to_numpy(t):
@@ -636,12 +670,15 @@ def timed_region(ctx, step, args):
     """Warm-up, barrier, K timed steps between two events, barrier; returns (ms per step as the maximum over the
     ranks, kernel launches of this rank inside the region, clocks sampled on rank 0)."""
     torch = ctx.torch
-    for _ in range(args.warmup):
-        step()
-    ctx.barrier()
+    # The sampler starts before the warm-up: whatever a rank does between the barrier and its first launch is
+    # waited for by every other rank at the first collective of the timed region.
     sampler = ClockSampler(ctx.local_rank)
     if ctx.rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    ctx.barrier()
+    sampler.begin()
     before = ctx.lib.qk_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
