@@ -84,6 +84,13 @@ def _rank_main(rank, world, port, rows, cols, result_dir):
         want_codes, _ = O.quantize(full, want_scale, tensor_scheme)
         assert codes.tobytes() == want_codes[shard.row_start: shard.row_start + shard.rows].tobytes()
 
+        # the same exchange started and awaited separately
+        t2 = torch.tensor([local, np.float32(rank)], dtype=torch.float32)
+        pending = allreduce_absmax(t2, async_op=True)
+        assert pending is not None
+        pending.wait()
+        assert t2[0].item() == t.item() and t2[1].item() == world - 1
+
         # per block: no communication; the shard's result is a slice of the whole tensor's
         bcodes, bscale = O.quantize_dynamic(mine, block_scheme)
         wcodes, wscale = O.quantize_dynamic(full, block_scheme)
@@ -100,3 +107,13 @@ def test_two_cpu_ranks_reproduce_the_single_device_result(tmp_path):
     world, port = 2, _free_port()
     mp.spawn(_rank_main, args=(world, port, 96, 256, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def test_exchange_without_a_process_group_is_a_no_op():
+    import torch
+
+    from cubek_b200.shard import allreduce_absmax
+
+    t = torch.tensor([3.5], dtype=torch.float32)
+    assert allreduce_absmax(t) is None and allreduce_absmax(t, async_op=True) is None
+    assert t.item() == 3.5
