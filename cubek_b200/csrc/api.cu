@@ -83,7 +83,7 @@ cudaError_t launch_block_scales(int fdt, const void *in, void *scale_out, long l
 enum { TUNE_THREADS = 0, TUNE_CTAS_PER_SM = 1, TUNE_FORCE_EXACT = 2, TUNE_FORCE_GENERAL = 3, TUNE_PDL = 4,
        TUNE_QUANT_WAVES = 5, TUNE_DEQUANT_WAVES = 6, TUNE_COOP_TENSOR = 7, TUNE_STAGED = 8, TUNE_SLICE_KIB = 9,
        TUNE_SLOTS = 10, TUNE_STAGES = 11, TUNE_TENSOR_SMEM_ROWS = 12, TUNE_COOP_MAX_MIB = 13, TUNE_COUNT = 14 };
-static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {16384}, {4}, {2}, {-1}, {256}};
+static std::atomic<int> g_tune[TUNE_COUNT] = {{256}, {0}, {0}, {0}, {1}, {1}, {12}, {1}, {0}, {0}, {4}, {2}, {-1}, {256}};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_sm_count[64];
 

@@ -17,19 +17,35 @@ int *stage_error_flag();   // device address of the flag the staged kernels rais
 namespace {
 
 constexpr int kMaxSlots = 8;
-// Staging slots in flight (tuning key 10, default 4) and input bytes per slice (key 9, KiB, default 16 MiB).
-// Every slice costs about 20 us of copy set-up (one upload, three downloads), and the first slice's upload is
-// not overlapped with anything: on a 117 MB bf16 tensor 1 / 4 / 8 / 16 MiB slices took 5.8 / 4.2 / 3.7 / 3.6 ms,
-// against 3.3 ms for the downloads alone at the link's rate with both directions busy.
+// Staging slots in flight (tuning key 10, default 4) and input bytes per slice (key 9, KiB; 0, the default, sizes
+// slices by the call: a sixteenth of the input bytes of all its tensors, between 16 and 64 MiB).
+// Every slice costs about 30 us of copy set-up (one upload, three downloads), and the first slice's upload and the
+// last one's downloads are overlapped with nothing.  On a 117 MB bf16 tensor 1 / 4 / 8 / 16 MiB slices took
+// 5.8 / 4.2 / 3.7 / 3.6 ms, against 3.3 ms for the downloads alone at the link's rate with both directions busy;
+// on 1.74 GB (28 tensors) 16 / 32 / 64 MiB slices took 55.7 / 53.8 / 52.6 ms against 51.5 ms for the copies alone.
 int slot_count()
 {
     const int v = qk_get_tuning(10);
     return v < 1 ? 1 : (v > kMaxSlots ? kMaxSlots : v);
 }
-size_t slice_target_bytes()
+size_t slice_target_bytes(size_t total_input_bytes)
 {
     const int kib = qk_get_tuning(9);
-    return (size_t)(kib < 64 ? 64 : kib) << 10;
+    if (kib > 0) return (size_t)(kib < 64 ? 64 : kib) << 10;
+    const size_t lo = (size_t)16 << 20, hi = (size_t)64 << 20;
+    const size_t t = total_input_bytes / 16;
+    return t < lo ? lo : (t > hi ? hi : t);
+}
+size_t total_input_bytes(int count, const QkTensor *inputs, int fsize)
+{
+    size_t total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!inputs[i].shape || inputs[i].rank < 1 || inputs[i].rank > QK_MAX_RANK) continue;
+        size_t n = 1;
+        for (int d = 0; d < inputs[i].rank; ++d) n *= (size_t)(inputs[i].shape[d] > 0 ? inputs[i].shape[d] : 0);
+        total += n * (size_t)fsize;
+    }
+    return total;
 }
 
 struct DeviceStreams {
@@ -58,7 +74,7 @@ struct Plan {
 
 // Slices are whole rows; for block schemes the blocks must lie along the last dim and divide it,
 // so that no block straddles a slice.  Anything else runs as a single slice.
-Plan make_plan(const QkTensor *input, const QkScheme *scheme, int input_dtype)
+Plan make_plan(const QkTensor *input, const QkScheme *scheme, int input_dtype, size_t slice_target)
 {
     Plan p;
     const int fsize = dtype_size(input_dtype);
@@ -94,7 +110,7 @@ Plan make_plan(const QkTensor *input, const QkScheme *scheme, int input_dtype)
     p.scale_row = (size_t)p.scales_per_row * dtype_size(scheme->param);
     p.out_row = p.in_row;
     if (sliceable) {
-        p.slice_rows = (long long)(slice_target_bytes() / p.in_row);
+        p.slice_rows = (long long)(slice_target / p.in_row);
         if (p.slice_rows < 1) p.slice_rows = 1;
         if (p.slice_rows > p.rows) p.slice_rows = p.rows;
         p.slice_scales = p.scales_per_row * p.slice_rows;
@@ -130,8 +146,9 @@ size_t qk_host_roundtrip_staging_bytes_batch(int count, const QkTensor *inputs, 
     size_t slot = 0;
     bool sliced = false;
     long long nslices = 0;
+    const size_t slice_target = slice_target_bytes(total_input_bytes(count, inputs, dtype_size(input_dtype)));
     for (int i = 0; i < count; ++i) {
-        const Plan p = make_plan(&inputs[i], scheme, input_dtype);
+        const Plan p = make_plan(&inputs[i], scheme, input_dtype, slice_target);
         if (!p.ok) return 0;
         if (p.slot_bytes > slot) slot = p.slot_bytes;
         sliced = sliced || p.sliced;
@@ -163,8 +180,9 @@ int qk_roundtrip_host_batch(int count, const QkTensor *inputs, const QkTensor *c
     // upload, kernels and download strictly one after the other).
     size_t slot_bytes = 0;
     long long nslices = 0;
+    const size_t slice_target = slice_target_bytes(total_input_bytes(count, inputs, dtype_size(input_dtype)));
     for (int i = 0; i < count; ++i) {
-        const Plan p = make_plan(&inputs[i], scheme, input_dtype);
+        const Plan p = make_plan(&inputs[i], scheme, input_dtype, slice_target);
         if (!p.ok) return QK_ERR_SHAPE;
         if (!inputs[i].ptr || !codes[i].ptr || !out_scales[i].ptr || !restored[i].ptr) return QK_ERR_NULL;
         if (p.slot_bytes > slot_bytes) slot_bytes = p.slot_bytes;
@@ -196,7 +214,7 @@ int qk_roundtrip_host_batch(int count, const QkTensor *inputs, const QkTensor *c
     long long slice = 0;
     for (int ti = 0; ti < count && status == QK_OK; ++ti) {
         const QkTensor *input = &inputs[ti];
-        const Plan p = make_plan(input, scheme, input_dtype);
+        const Plan p = make_plan(input, scheme, input_dtype, slice_target);
         const int rank = input->rank;
         for (long long r0 = 0; r0 < p.rows && status == QK_OK; r0 += p.slice_rows, ++slice) {
             const long long nr = (p.rows - r0 < p.slice_rows) ? p.rows - r0 : p.slice_rows;

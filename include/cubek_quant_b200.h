@@ -261,7 +261,9 @@ int qk_roundtrip_host(const QkTensor *input, const QkTensor *codes, const QkTens
 size_t qk_host_roundtrip_staging_bytes(const QkTensor *input, const QkScheme *scheme, int input_dtype);
 /* The same for a set of tensors in host memory: the slices of all tensors share one ring of staging slots, so that
  * copies of neighbouring tensors overlap (small tensors - one slice each - would otherwise run upload, kernels and
- * download one after the other).  Results equal qk_roundtrip_host per tensor.  No reference counterpart. */
+ * download one after the other).  Slices hold a sixteenth of the call's input, between 16 and 64 MiB, and four of them
+ * are in flight: the staging buffer is 0.2 to 0.7 GB.  Results equal qk_roundtrip_host per tensor.  No reference
+ * counterpart. */
 int qk_roundtrip_host_batch(int count, const QkTensor *inputs, const QkTensor *codes, const QkTensor *out_scales,
                             const QkTensor *restored, const QkScheme *scheme, int input_dtype,
                             void *staging, size_t staging_bytes, int device);

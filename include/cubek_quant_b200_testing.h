@@ -15,7 +15,7 @@ extern "C" {
 /* Process-wide launch knobs (keys: 0 threads per CTA, 1 CTAs per SM, 2 force the reference-arithmetic route,
  * 3 force the layout-general kernels, 4 programmatic dependent launch on/off, 5 / 6 grid size of the quantize /
  * dequantize kernels in waves, 7 cooperative per-tensor kernel on/off, 8 staging of the quantize input through
- * shared memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never, 9 / 10 input KiB per slice and
+ * shared memory with bulk copies: 0 units below 64 bytes, 1 always, 2 never, 9 / 10 input KiB per slice (0: sized by the call, 16-64 MiB) and
  * staging slots (1..8) of qk_roundtrip_host; change them only between calls, and size the staging area after,
  * 11 ring depth (2..4 tiles of 16 KB) of the staged quantize variant, 12 rows the one-launch per-tensor kernel keeps
  * in shared memory (< 0: as many as fit), 13 largest tensor in MiB that takes that kernel).  They exist so that tests can force every

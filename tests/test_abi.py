@@ -137,9 +137,20 @@ def test_host_roundtrip_staging_size():
     t = _ffi.CTensor(fake((14336, 4096), 2))
     n = _ffi.lib().qk_host_roundtrip_staging_bytes(t.ref(), _ffi.c_scheme(sch), int(ElemType.BF16))
     lib = _ffi.lib()
-    slots, slice_bytes = lib.qk_get_tuning(_ffi.TUNE_SLOTS), lib.qk_get_tuning(_ffi.TUNE_SLICE_KIB) << 10
-    assert (slots, slice_bytes) == (4, 16 << 20)
+    slots, slice_kib = lib.qk_get_tuning(_ffi.TUNE_SLOTS), lib.qk_get_tuning(_ffi.TUNE_SLICE_KIB)
+    assert (slots, slice_kib) == (4, 0)                          # 0: slices sized by the call, 16 MiB for this one
+    slice_bytes = 16 << 20
     assert slots * slice_bytes < n < slots * 3 * slice_bytes     # input + codes + scales + restored per slot
+    # a call of many tensors takes larger slices (a sixteenth of its input, at most 64 MiB)
+    many = _ffi.CTensorArray([fake((14336, 4096), 2) for _ in range(16)])
+    n16 = lib.qk_host_roundtrip_staging_bytes_batch(many.count, many.array, _ffi.c_scheme(sch), int(ElemType.BF16))
+    assert slots * (64 << 20) < n16 < slots * 3 * (64 << 20)
+    try:
+        lib.qk_set_tuning(_ffi.TUNE_SLICE_KIB, 4096)             # an explicit size is taken as given
+        n4 = lib.qk_host_roundtrip_staging_bytes_batch(many.count, many.array, _ffi.c_scheme(sch), int(ElemType.BF16))
+        assert slots * (4 << 20) < n4 < slots * 3 * (4 << 20)
+    finally:
+        lib.qk_set_tuning(_ffi.TUNE_SLICE_KIB, 0)
 
 
 def test_device_header_probe_library_is_built():
