@@ -89,13 +89,14 @@ def algorithmic_bytes(workload, rows=None):
 
 
 _SAMPLER_SOURCE = r"""
-import sys, time
+import os, sys, time
 import pynvml
 pynvml.nvmlInit()
 handle = pynvml.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
 out = open(sys.argv[2], "w", buffering=1)
 out.write("max %d\n" % pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
-while True:
+parent, born = os.getppid(), time.time()
+while os.getppid() == parent and time.time() - born < 1800:   # never outlives the benchmark process
     try:
         out.write("%.6f %d %d\n" % (time.time(), pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM),
                                      int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))))
