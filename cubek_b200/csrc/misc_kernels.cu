@@ -367,10 +367,28 @@ __device__ __forceinline__ uint32_t encode_native(int kind, float c)
     return cvt_e5m2x2(c, 0.0f) & 0xFFu;
 }
 
-__global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuantArgs a)
+// One element: RN_F(x / s), round, clamp.  With a scale inside the window of the shortcuts the quotient comes from
+// the reciprocal like in the streaming kernels (f32: two correction steps, exactly rounded, first guess clamped so
+// that a huge quotient keeps its sign; 16-bit types: the f32 product narrowed to F), else from IEEE division.
+template <int FDT> __device__ __forceinline__ float general_quantize_one(float x, float s, float r, bool fast, float lo, float hi)
 {
+    if (!fast) return quantize_exact<FDT>(x, s, lo, hi);
+    float t;
+    if constexpr (FDT == QK_F32) {
+        const float q0 = fminf(fmaxf(x * r, lo - 2.0f), hi + 2.0f);
+        t = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+    } else {
+        t = round_to<FDT>(x * r);
+    }
+    return round_clamp(t, lo, hi);
+}
+
+template <int FDT> __global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuantArgs a)
+{
+    using F = typename ElemOf<FDT>::type;
     const int bits = kind_bits(a.kind);
     const uint32_t mask = (1u << bits) - 1u;
+    const F *in = static_cast<const F *>(a.in);
     for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < a.nitems;
          item += (long long)gridDim.x * blockDim.x) {
         const long long pos = item * a.nq;
@@ -378,59 +396,109 @@ __global__ void __launch_bounds__(256) general_quantize_kernel(const GeneralQuan
         long long sp_out;
         const long long sp = general_scale_pos(a.layout, pos, &is_start, &sp_out);
         float scale_f;
-        if (a.absmax) scale_f = round_to_dyn(a.fdt, __fdiv_rn(2.0f * (*a.absmax), a.range));
-        else scale_f = load_dyn(a.scale_in, a.fdt, sp);
+        if (a.absmax) scale_f = round_to<FDT>(__fdiv_rn(2.0f * (*a.absmax), a.range));
+        else scale_f = static_cast<float>(static_cast<const F *>(a.scale_in)[sp]);
         const float s_fs = round_to_dyn(a.param, scale_f);
         if (is_start) store_dyn(a.out_scale, a.param, sp_out, s_fs);
-        const float s = round_to_dyn(a.fdt, s_fs);
+        const float s = round_to<FDT>(s_fs);
+#ifdef QK_ROUND_HALF_AWAY
+        const bool fast = false;   // the shortcuts were proven for halves-to-even only
+#else
+        const bool fast = !a.force_exact && scale_is_safe(s);
+#endif
+        const float r = fast ? __frcp_rn(s) : 0.0f;
 
         // the nq elements of an item are consecutive along the last dim
         const long long d0 = data_index(a.layout, pos);
         const long long dstep = a.layout.data_contiguous ? 1 : a.layout.data_strides[a.layout.rank - 1];
         if (a.kind <= KIND_PACK2) {
             uint32_t word = 0;
-            for (int i = 0; i < a.nq; ++i) {
-                const float t = round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0 + i * dstep), s));
-                const float c = round_clamp(t, a.lo, a.hi);
-                word |= ((uint32_t)(int)c & mask) << (i * bits);
+            if (a.vector_bytes == 16) {
+                // contiguous, 16-byte aligned data: the item's elements arrive 16 bytes at a time
+                constexpr int PER = 16 / (int)sizeof(F);
+                const uint4 *p = reinterpret_cast<const uint4 *>(in + d0);
+                for (int c0 = 0; c0 < a.nq; c0 += PER) {
+                    const uint4 v = __ldg(p + c0 / PER);
+                    const uint32_t raw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) {
+                        const float c = general_quantize_one<FDT>(raw_elem<FDT>(raw, j), s, r, fast, a.lo, a.hi);
+                        word |= ((uint32_t)(int)c & mask) << ((c0 + j) * bits);
+                    }
+                }
+            } else if (a.vector_bytes == 8) {   // four 16-bit elements
+                const uint2 v = __ldg(reinterpret_cast<const uint2 *>(in + d0));
+                const uint32_t raw[2] = {v.x, v.y};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float c = general_quantize_one<FDT>(raw_elem<FDT>(raw, j), s, r, fast, a.lo, a.hi);
+                    word |= ((uint32_t)(int)c & mask) << (j * bits);
+                }
+            } else {
+                for (int i = 0; i < a.nq; ++i) {
+                    const float c = general_quantize_one<FDT>(static_cast<float>(in[d0 + i * dstep]), s, r, fast, a.lo, a.hi);
+                    word |= ((uint32_t)(int)c & mask) << (i * bits);
+                }
             }
             static_cast<uint32_t *>(a.out)[values_index(a.layout, item)] = word;
         } else if (a.kind == KIND_E2M1) {
-            const float c0 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
-            const float c1 = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0 + dstep), s)), a.lo, a.hi);
+            const float c0 = general_quantize_one<FDT>(static_cast<float>(in[d0]), s, r, fast, a.lo, a.hi);
+            const float c1 = general_quantize_one<FDT>(static_cast<float>(in[d0 + dstep]), s, r, fast, a.lo, a.hi);
             static_cast<uint8_t *>(a.out)[values_index(a.layout, item)] = (uint8_t)cvt_e2m1x2(c0, c1);
         } else {
-            const float c = round_clamp(round_to_dyn(a.fdt, __fdiv_rn(load_dyn(a.in, a.fdt, d0), s)), a.lo, a.hi);
+            const float c = general_quantize_one<FDT>(static_cast<float>(in[d0]), s, r, fast, a.lo, a.hi);
             static_cast<uint8_t *>(a.out)[values_index(a.layout, item)] = (uint8_t)encode_native(a.kind, c);
         }
     }
 }
 
-__global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDequantArgs a)
+template <int FDT> __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDequantArgs a)
 {
+    using F = typename ElemOf<FDT>::type;
     const int bits = kind_bits(a.kind);
     const uint32_t mask = (1u << bits) - 1u;
     const int sign_bit = 1 << (bits - 1), two_pow_n = 1 << bits;
+    F *out = static_cast<F *>(a.out);
     for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < a.nitems;
          item += (long long)gridDim.x * blockDim.x) {
         const long long pos = item * a.nq;
         bool is_start;
         const long long sp = general_scale_pos(a.layout, pos, &is_start);
-        const float s = round_to_dyn(a.fdt, load_dyn(a.params, a.param, sp));
+        const float s = round_to<FDT>(load_dyn(a.params, a.param, sp));
         const long long d0 = data_index(a.layout, pos);
         const long long dstep = a.layout.data_contiguous ? 1 : a.layout.data_strides[a.layout.rank - 1];
         if (a.kind <= KIND_PACK2) {
             const uint32_t word = static_cast<const uint32_t *>(a.values)[values_index(a.layout, item)];
-            for (int i = 0; i < a.nq; ++i) {
+            auto value = [&](int i) {
                 const int raw = (int)((word >> (i * bits)) & mask);
-                const int q = raw - (raw >= sign_bit ? two_pow_n : 0);
-                store_dyn(a.out, a.fdt, d0 + i * dstep, s * (float)q);
+                return s * (float)(raw - (raw >= sign_bit ? two_pow_n : 0));
+            };
+            if (a.vector_bytes == 16) {
+                // contiguous, 16-byte aligned output: the item's elements leave 16 bytes at a time
+                constexpr int PER = 16 / (int)sizeof(F);
+                uint4 *p = reinterpret_cast<uint4 *>(out + d0);
+                for (int c0 = 0; c0 < a.nq; c0 += PER) {
+                    uint32_t r[4];
+                    if constexpr (FDT == QK_F32) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) r[j] = __float_as_uint(value(c0 + j));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) r[j] = h2_pack<FDT>(value(c0 + 2 * j), value(c0 + 2 * j + 1));
+                    }
+                    p[c0 / PER] = make_uint4(r[0], r[1], r[2], r[3]);
+                }
+            } else if (a.vector_bytes == 8) {   // four 16-bit elements
+                if constexpr (FDT != QK_F32)
+                    *reinterpret_cast<uint2 *>(out + d0) = make_uint2(h2_pack<FDT>(value(0), value(1)), h2_pack<FDT>(value(2), value(3)));
+            } else {
+                for (int i = 0; i < a.nq; ++i) out[d0 + i * dstep] = static_cast<F>(value(i));
             }
         } else if (a.kind == KIND_E2M1) {
             uint32_t h2 = cvt_f16x2_from_e2m1x2(static_cast<const uint8_t *>(a.values)[values_index(a.layout, item)]);
             float2 f = __half22float2(*reinterpret_cast<__half2 *>(&h2));
-            store_dyn(a.out, a.fdt, d0, s * f.x);
-            store_dyn(a.out, a.fdt, d0 + dstep, s * f.y);
+            out[d0] = static_cast<F>(s * f.x);
+            out[d0 + dstep] = static_cast<F>(s * f.y);
         } else {
             const uint32_t b = static_cast<const uint8_t *>(a.values)[values_index(a.layout, item)];
             float q;
@@ -439,7 +507,7 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
                 uint32_t h2 = (a.kind == KIND_E4M3) ? cvt_f16x2_from_e4m3x2(b) : cvt_f16x2_from_e5m2x2(b);
                 q = __half22float2(*reinterpret_cast<__half2 *>(&h2)).x;
             }
-            store_dyn(a.out, a.fdt, d0, s * q);
+            out[d0] = static_cast<F>(s * q);
         }
     }
 }
@@ -447,8 +515,12 @@ __global__ void __launch_bounds__(256) general_dequantize_kernel(const GeneralDe
 // One thread per block of the scales tensor: absmax over the (possibly clipped) N-d block.  The block is
 // walked row by row (runs along the last dim) with an odometer over the other dims, so the element loop
 // has no division.
-__global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScalesArgs a)
+template <int FDT> __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScalesArgs a)
 {
+    using F = typename ElemOf<FDT>::type;
+    constexpr int PER = 16 / (int)sizeof(F);
+    const F *in = static_cast<const F *>(a.in);
+    const bool aligned_base = reinterpret_cast<uintptr_t>(a.in) % 16 == 0;
     const GeneralLayout &L = a.layout;
     const int last = L.rank - 1;
     for (long long bi = (long long)blockIdx.x * blockDim.x + threadIdx.x; bi < a.nblocks;
@@ -471,7 +543,17 @@ __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScales
         }
         float amax = 0.0f;
         for (long long r = 0; r < rows; ++r) {
-            for (int k = 0; k < ext[last]; ++k) amax = fmaxf(amax, fabsf(load_dyn(a.in, a.fdt, lin + k * stride[last])));
+            if (aligned_base && stride[last] == 1 && ext[last] % PER == 0 && lin % PER == 0) {
+                // a run of whole, aligned 16-byte chunks
+                const uint4 *p = reinterpret_cast<const uint4 *>(in + lin);
+                for (int k = 0; k < ext[last] / PER; ++k) {
+                    const uint4 v = __ldg(p + k);
+                    const uint32_t raw[4] = {v.x, v.y, v.z, v.w};
+                    amax = fmaxf(amax, unit_absmax<FDT, 4>(raw));
+                }
+            } else {
+                for (int k = 0; k < ext[last]; ++k) amax = fmaxf(amax, fabsf(static_cast<float>(in[lin + k * stride[last]])));
+            }
             // next row of the block: advance the odometer over dims last-1 .. 0
             for (int d = last - 1; d >= 0; --d) {
                 lin += stride[d];
@@ -480,7 +562,7 @@ __global__ void __launch_bounds__(256) general_scales_kernel(const GeneralScales
                 at[d] = 0;
             }
         }
-        store_dyn(a.scale_out, a.fdt, sp, __fdiv_rn(2.0f * amax, a.range));
+        static_cast<F *>(a.scale_out)[sp] = static_cast<F>(__fdiv_rn(2.0f * amax, a.range));
     }
 }
 
@@ -504,19 +586,62 @@ void finish_layout(GeneralLayout &L, int nq)
 cudaError_t launch_general_quantize(const GeneralQuantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nitems == 0) return cudaSuccess;
-    general_quantize_kernel<<<grid_for(a.nitems, 256, one_wave(cfg, general_quantize_kernel)), 256, 0, stream>>>(a);
+    GeneralQuantArgs args = a;
+    args.force_exact = cfg.force_exact;
+    // packed kinds on contiguous, 16-byte aligned data read an item's elements as 16-byte (or one 8-byte) vectors
+    const int item_bytes = a.nq * (a.fdt == QK_F32 ? 4 : 2);
+    args.vector_bytes = 0;
+    if (a.kind <= KIND_PACK2 && a.layout.data_contiguous && reinterpret_cast<uintptr_t>(a.in) % 16 == 0)
+        args.vector_bytes = (item_bytes % 16 == 0) ? 16 : (item_bytes == 8 ? 8 : 0);
+    switch (a.fdt) {
+    case QK_F32:
+        general_quantize_kernel<QK_F32><<<grid_for(a.nitems, 256, one_wave(cfg, general_quantize_kernel<QK_F32>)), 256, 0, stream>>>(args);
+        break;
+    case QK_F16:
+        general_quantize_kernel<QK_F16><<<grid_for(a.nitems, 256, one_wave(cfg, general_quantize_kernel<QK_F16>)), 256, 0, stream>>>(args);
+        break;
+    default:
+        general_quantize_kernel<QK_BF16><<<grid_for(a.nitems, 256, one_wave(cfg, general_quantize_kernel<QK_BF16>)), 256, 0, stream>>>(args);
+        break;
+    }
     return cudaGetLastError();
 }
 cudaError_t launch_general_dequantize(const GeneralDequantArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nitems == 0) return cudaSuccess;
-    general_dequantize_kernel<<<grid_for(a.nitems, 256, one_wave(cfg, general_dequantize_kernel)), 256, 0, stream>>>(a);
+    GeneralDequantArgs args = a;
+    // packed kinds into contiguous, 16-byte aligned output write an item's elements as 16-byte (or one 8-byte) vectors
+    const int item_bytes = a.nq * (a.fdt == QK_F32 ? 4 : 2);
+    args.vector_bytes = 0;
+    if (a.kind <= KIND_PACK2 && a.layout.data_contiguous && reinterpret_cast<uintptr_t>(a.out) % 16 == 0)
+        args.vector_bytes = (item_bytes % 16 == 0) ? 16 : (item_bytes == 8 ? 8 : 0);
+    switch (a.fdt) {
+    case QK_F32:
+        general_dequantize_kernel<QK_F32><<<grid_for(a.nitems, 256, one_wave(cfg, general_dequantize_kernel<QK_F32>)), 256, 0, stream>>>(args);
+        break;
+    case QK_F16:
+        general_dequantize_kernel<QK_F16><<<grid_for(a.nitems, 256, one_wave(cfg, general_dequantize_kernel<QK_F16>)), 256, 0, stream>>>(args);
+        break;
+    default:
+        general_dequantize_kernel<QK_BF16><<<grid_for(a.nitems, 256, one_wave(cfg, general_dequantize_kernel<QK_BF16>)), 256, 0, stream>>>(args);
+        break;
+    }
     return cudaGetLastError();
 }
 cudaError_t launch_general_scales(const GeneralScalesArgs &a, const LaunchCfg &cfg, cudaStream_t stream)
 {
     if (a.nblocks == 0) return cudaSuccess;
-    general_scales_kernel<<<grid_for(a.nblocks, 256, one_wave(cfg, general_scales_kernel)), 256, 0, stream>>>(a);
+    switch (a.fdt) {
+    case QK_F32:
+        general_scales_kernel<QK_F32><<<grid_for(a.nblocks, 256, one_wave(cfg, general_scales_kernel<QK_F32>)), 256, 0, stream>>>(a);
+        break;
+    case QK_F16:
+        general_scales_kernel<QK_F16><<<grid_for(a.nblocks, 256, one_wave(cfg, general_scales_kernel<QK_F16>)), 256, 0, stream>>>(a);
+        break;
+    default:
+        general_scales_kernel<QK_BF16><<<grid_for(a.nblocks, 256, one_wave(cfg, general_scales_kernel<QK_BF16>)), 256, 0, stream>>>(a);
+        break;
+    }
     return cudaGetLastError();
 }
 

@@ -46,6 +46,8 @@ struct GeneralQuantArgs {
     long long nitems;  // stored items (u32 words or native bytes)
     int nq, kind, fdt, param;
     float lo, hi, range;
+    int force_exact;   // 1: IEEE division for every element (filled by the launcher from the launch knobs)
+    int vector_bytes;  // 16 / 8: an item's elements are read as vectors of that size; 0: one by one (filled by the launcher)
 };
 
 struct GeneralDequantArgs {
@@ -55,6 +57,7 @@ struct GeneralDequantArgs {
     void *out;
     long long nitems;
     int nq, kind, fdt, param;
+    int vector_bytes;  // like GeneralQuantArgs::vector_bytes, for the stores
 };
 
 struct GeneralScalesArgs {
